@@ -1,0 +1,162 @@
+/*
+ * C ABI of the B200-native svox hot path: octree point query and
+ * differentiable volume rendering.
+ *
+ * Each entry point replaces one function of the reference's pybind11
+ * module `svox.csrc` (svox/csrc/svox.cpp:106-113).  All pointers are
+ * DEVICE pointers unless stated otherwise.  Outputs are caller-allocated;
+ * the library itself only takes a small per-call jump table over the top
+ * levels of the tree (<= 8 MB, normally 128 KB) from the CUDA stream-ordered
+ * pool and returns it on the same stream.  Every call is asynchronous on
+ * `stream` (a cudaStream_t passed as void*) and returns an svoxb_status.
+ *
+ * Layouts (identical to the reference's tensors, svox/svox.py:122-127):
+ *   data   (M, N, N, N, K) float32, a leaf record is K contiguous floats:
+ *          channel-major colour coefficients then the density
+ *   child  (M, N, N, N)    int32, 0 = leaf, otherwise child_node - node
+ *   offset, scaling (3)    float32 in device memory; tree-space position is
+ *          offset + scaling * world_position
+ */
+#ifndef SVOX_B200_H
+#define SVOX_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    SVOXB_OK = 0,
+    SVOXB_ERR_NULL = 1,        /* a required pointer is null                 */
+    SVOXB_ERR_SHAPE = 2,       /* a size is negative / inconsistent          */
+    SVOXB_ERR_FORMAT = 3,      /* data format not supported by this build    */
+    SVOXB_ERR_OPTION = 4,      /* invalid render option (e.g. step_size <= 0)*/
+    SVOXB_ERR_CUDA = 5,        /* a CUDA runtime call failed                 */
+    SVOXB_ERR_TREE = 6,        /* device status: descent left the node array */
+    SVOXB_ERR_MARCH = 7,       /* device status: a ray hit the step cap      */
+    SVOXB_ERR_TOO_LARGE = 8    /* size beyond a documented maximum           */
+} svoxb_status;
+
+/* Data formats (svox/csrc/include/data_spec.hpp:44-49). */
+enum { SVOXB_FORMAT_RGBA = 0, SVOXB_FORMAT_SH = 1, SVOXB_FORMAT_SG = 2, SVOXB_FORMAT_ASG = 3 };
+
+/* Replaces TreeSpec / PackedTreeSpec (svox/csrc/include/data_spec.hpp:66-89,
+ * data_spec_packed.cuh:56-81). */
+typedef struct {
+    const float* data;
+    const int32_t* child;
+    const float* offset;
+    const float* scaling;
+    int64_t M;  /* number of nodes (capacity)  */
+    int32_t N;  /* branching factor per axis   */
+    int32_t K;  /* floats per leaf record      */
+} svoxb_tree;
+
+/* Replaces RaysSpec (svox/csrc/include/data_spec.hpp:51-64): three (Q, 3)
+ * contiguous float arrays.  vdirs is used as given (not normalised). */
+typedef struct {
+    const float* origins;
+    const float* dirs;
+    const float* vdirs;
+    int64_t Q;
+} svoxb_rays;
+
+/* Replaces CameraSpec (svox/csrc/include/data_spec.hpp:91-104).  c2w points
+ * to a row-major (3 or 4, 4) camera-to-world matrix in device memory. */
+typedef struct {
+    const float* c2w;
+    float fx;
+    float fy;
+    int32_t width;
+    int32_t height;
+} svoxb_camera;
+
+/* Field for field the reference's RenderOptions
+ * (svox/csrc/include/data_spec.hpp:107-126); density_softplus is an int. */
+typedef struct {
+    float step_size;
+    float background_brightness;
+    int32_t format;
+    int32_t basis_dim;
+    int32_t ndc_width;
+    int32_t ndc_height;
+    float ndc_focal;
+    int32_t min_comp;
+    int32_t max_comp;
+    float sigma_thresh;
+    float stop_thresh;
+    int32_t density_softplus;
+    float rgb_padding;
+} svoxb_render_options;
+
+/* query_vertical (svox/csrc/svox_kernel.cu:120-143): for each of Q points
+ * (indices, (Q,3)) write the K values of the containing leaf to values_out
+ * (Q,K) and its packed id node*N^3 + u*N^2 + v*N + w to node_ids_out (Q).
+ * Either output may be null. */
+int svoxb_query_vertical(const svoxb_tree* tree, const float* indices, int64_t Q,
+                         float* values_out, int64_t* node_ids_out, void* stream);
+
+/* query_vertical_backward (svox/csrc/svox_kernel.cu:160-182): scatter-add
+ * grad_output (Q,Kg) into grad_data_out (M,N,N,N,Kg).  With zero_first != 0
+ * the output is cleared first (the reference returns a fresh zero tensor). */
+int svoxb_query_vertical_backward(const svoxb_tree* tree, const float* indices, int64_t Q,
+                                  const float* grad_output, int32_t Kg, float* grad_data_out,
+                                  int zero_first, void* stream);
+
+/* volume_render (svox/csrc/rt_kernel.cu:1019-1036): out is (Q, out_dim),
+ * out_dim = (K-1)/basis_dim, or K-1 for RGBA. */
+int svoxb_volume_render(const svoxb_tree* tree, const svoxb_rays* rays,
+                        const svoxb_render_options* opt, float* out, void* stream);
+
+/* volume_render_image (svox/csrc/rt_kernel.cu:1038-1057): out is
+ * (height, width, out_dim), pixel (ix, iy) at row iy. */
+int svoxb_volume_render_image(const svoxb_tree* tree, const svoxb_camera* cam,
+                              const svoxb_render_options* opt, float* out, void* stream);
+
+/* volume_render_backward (svox/csrc/rt_kernel.cu:1059-1083): scatter-add the
+ * gradient of sum(grad_output * out) w.r.t. data into grad_data_out (shaped
+ * like data).  As in the reference the gradient is that of the render
+ * WITHOUT sigma_thresh / stop_thresh.
+ * fwd_out: optional (may be null) output of the forward call for the same
+ * inputs; if given and both thresholds are zero, one march per ray is
+ * enough instead of the reference's two. */
+int svoxb_volume_render_backward(const svoxb_tree* tree, const svoxb_rays* rays,
+                                 const svoxb_render_options* opt, const float* grad_output,
+                                 const float* fwd_out, float* grad_data_out, int zero_first,
+                                 void* stream);
+
+/* volume_render_image_backward (svox/csrc/rt_kernel.cu:1085-1109). */
+int svoxb_volume_render_image_backward(const svoxb_tree* tree, const svoxb_camera* cam,
+                                       const svoxb_render_options* opt,
+                                       const float* grad_output, const float* fwd_out,
+                                       float* grad_data_out, int zero_first, void* stream);
+
+/* Device-side anomaly report.  The kernels bound every loop (the
+ * reference's descent and march are unbounded, svox/csrc/include/
+ * common.cuh:67-88, rt_kernel.cu:261) and record SVOXB_ERR_TREE /
+ * SVOXB_ERR_MARCH in a per-device status word instead of hanging.  This
+ * call synchronises `stream`, returns the word of the current device and
+ * optionally clears it. */
+int svoxb_device_status(int clear, void* stream);
+
+/* Text for a status code (replaces the reference's printf in
+ * CUDA_CHECK_ERRORS, svox/csrc/include/common.cuh:98-101). */
+const char* svoxb_strerror(int status);
+
+/* Text of the last CUDA runtime error seen by this library on the calling
+ * thread (empty string if none). */
+const char* svoxb_last_cuda_error(void);
+
+/* Experiment hook (no counterpart in the reference): key 0 = render block
+ * size (256 or 1024, 0 = automatic), key 1 = cap on the render jump-table
+ * level (-1 = automatic), key 2 = cap on the query jump-table level. */
+int svoxb_tune(int key, int value);
+
+/* Library version, "major.minor.patch". */
+const char* svoxb_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SVOX_B200_H */

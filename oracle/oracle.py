@@ -1,0 +1,217 @@
+"""ctypes front end of the C oracle (test infrastructure only).
+
+All arrays are numpy; float32 for coordinates and tree data, int32 for the
+child links, float64 for gradients.  See ``svox_oracle.c`` for what each
+function restates.
+"""
+import ctypes as C
+import numpy as np
+
+from .build import build_oracle
+
+FORMAT_RGBA, FORMAT_SH, FORMAT_SG, FORMAT_ASG = 0, 1, 2, 3
+
+
+class OrcTree(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("child", C.c_void_p), ("M", C.c_int64),
+                ("N", C.c_int32), ("K", C.c_int32),
+                ("offset", C.c_float * 3), ("scaling", C.c_float * 3)]
+
+
+class OrcOptions(C.Structure):
+    _fields_ = [("step_size", C.c_float), ("background_brightness", C.c_float),
+                ("format", C.c_int32), ("basis_dim", C.c_int32),
+                ("ndc_width", C.c_int32), ("ndc_height", C.c_int32),
+                ("ndc_focal", C.c_float), ("min_comp", C.c_int32),
+                ("max_comp", C.c_int32), ("sigma_thresh", C.c_float),
+                ("stop_thresh", C.c_float), ("density_softplus", C.c_int32),
+                ("rgb_padding", C.c_float)]
+
+
+CONTRACT_FIELDS = ["transform", "norm", "pos", "dda_root", "dda_leaf", "sh_dot",
+                   "color_pad", "out_acc", "bg_acc", "cam_xy", "cam_rot",
+                   "ndc_shift", "sh_basis"]
+
+
+class OrcContract(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in CONTRACT_FIELDS]
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = C.CDLL(build_oracle())
+        _lib.orc_trace_log.restype = C.c_int64
+    return _lib
+
+
+def get_contract():
+    c = OrcContract()
+    lib().orc_get_contract(C.byref(c))
+    return {n: getattr(c, n) for n in CONTRACT_FIELDS}
+
+
+def set_contract(**kw):
+    cur = get_contract()
+    cur.update(kw)
+    c = OrcContract(*[cur[n] for n in CONTRACT_FIELDS])
+    lib().orc_set_contract(C.byref(c))
+    return cur
+
+
+def num_threads():
+    return lib().orc_num_threads()
+
+
+def set_num_threads(n):
+    lib().orc_set_num_threads(int(n))
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _ptr(a):
+    return a.ctypes.data_as(C.c_void_p) if a is not None else None
+
+
+class Tree:
+    """Borrowed view of the tree arrays: data (M,N,N,N,K) f32, child (M,N,N,N) i32."""
+
+    def __init__(self, data, child, offset=(0, 0, 0), scaling=(1, 1, 1)):
+        self.data = _f32(data)
+        self.child = np.ascontiguousarray(child, dtype=np.int32)
+        assert self.data.ndim == 5 and self.child.ndim == 4
+        self.M, self.N = self.child.shape[0], self.child.shape[1]
+        self.K = self.data.shape[-1]
+        self.offset = [float(x) for x in np.asarray(offset, dtype=np.float32)]
+        self.scaling = [float(x) for x in np.asarray(scaling, dtype=np.float32)]
+        self.c = OrcTree(_ptr(self.data), _ptr(self.child), self.M, self.N, self.K,
+                         (C.c_float * 3)(*self.offset), (C.c_float * 3)(*self.scaling))
+
+    @classmethod
+    def from_n3tree(cls, tree, world=True):
+        """From any object with svox's N3Tree tensors (data, child, offset, invradius)."""
+        n = tree.n_internal if hasattr(tree, "n_internal") else tree.child.shape[0]
+        del n  # the kernels see the full capacity, as the reference's do
+        data = tree.data.detach().cpu().numpy()
+        child = tree.child.cpu().numpy()
+        if world:
+            return cls(data, child, tree.offset.cpu().numpy(), tree.invradius.cpu().numpy())
+        return cls(data, child)
+
+
+def options(step_size=1e-3, background_brightness=1.0, format=FORMAT_SH, basis_dim=1,
+            ndc_width=-1, ndc_height=-1, ndc_focal=0.0, min_comp=0, max_comp=None,
+            sigma_thresh=0.0, stop_thresh=0.0, density_softplus=False, rgb_padding=0.0):
+    if max_comp is None:
+        max_comp = basis_dim - 1
+    return OrcOptions(step_size, background_brightness, format, basis_dim, ndc_width,
+                      ndc_height, ndc_focal, min_comp, max_comp, sigma_thresh, stop_thresh,
+                      int(bool(density_softplus)), rgb_padding)
+
+
+def out_dim(tree, opt):
+    return (tree.K - 1) // opt.basis_dim if opt.format != FORMAT_RGBA else tree.K - 1
+
+
+def _check(rc, what):
+    if rc != 0:
+        raise RuntimeError(f"oracle {what}: corrupt tree (descent left the node array)")
+
+
+def query_vertical(tree, points):
+    pts = _f32(points)
+    Q = pts.shape[0]
+    vals = np.empty((Q, tree.K), np.float32)
+    ids = np.empty((Q,), np.int64)
+    _check(lib().orc_query_vertical(C.byref(tree.c), _ptr(pts), C.c_int64(Q), _ptr(vals),
+                                    _ptr(ids)), "query_vertical")
+    return vals, ids
+
+
+def query_vertical_backward(tree, points, grad_out):
+    pts = _f32(points)
+    g = _f32(grad_out)
+    Q, Kg = g.shape
+    grad = np.zeros((tree.M, tree.N, tree.N, tree.N, Kg), np.float64)
+    _check(lib().orc_query_vertical_backward(C.byref(tree.c), _ptr(pts), C.c_int64(Q), _ptr(g),
+                                             C.c_int32(Kg), _ptr(grad)),
+           "query_vertical_backward")
+    return grad
+
+
+def volume_render(tree, origins, dirs, vdirs, opt, want_counts=False):
+    o, d, v = _f32(origins), _f32(dirs), _f32(vdirs)
+    Q = o.shape[0]
+    out = np.zeros((Q, out_dim(tree, opt)), np.float32)
+    vis = np.zeros(Q, np.int32) if want_counts else None
+    con = np.zeros(Q, np.int32) if want_counts else None
+    _check(lib().orc_volume_render(C.byref(tree.c), _ptr(o), _ptr(d), _ptr(v), C.c_int64(Q),
+                                   C.byref(opt), _ptr(out), _ptr(vis), _ptr(con)),
+           "volume_render")
+    return (out, vis, con) if want_counts else out
+
+
+def trace_log(tree, origin, dir, vdir, opt, cap=4096):
+    o, d, v = _f32(origin), _f32(dir), _f32(vdir)
+    slots = np.zeros(cap, np.int64)
+    dts = np.zeros(cap, np.float32)
+    ts = np.zeros(cap, np.float32)
+    out = np.zeros(64, np.float32)
+    n = lib().orc_trace_log(C.byref(tree.c), _ptr(o), _ptr(d), _ptr(v), C.byref(opt),
+                            C.c_int32(cap), _ptr(slots), _ptr(dts), _ptr(ts), _ptr(out))
+    n = min(int(n), cap)
+    return slots[:n], dts[:n], ts[:n], out[:out_dim(tree, opt)]
+
+
+def volume_render_backward(tree, origins, dirs, vdirs, opt, grad_out, want_counts=False):
+    o, d, v, g = _f32(origins), _f32(dirs), _f32(vdirs), _f32(grad_out)
+    Q = o.shape[0]
+    grad = np.zeros(tree.data.shape, np.float64)
+    vis = np.zeros(Q, np.int32) if want_counts else None
+    con = np.zeros(Q, np.int32) if want_counts else None
+    _check(lib().orc_volume_render_backward(C.byref(tree.c), _ptr(o), _ptr(d), _ptr(v),
+                                            C.c_int64(Q), C.byref(opt), _ptr(g), _ptr(grad),
+                                            _ptr(vis), _ptr(con)), "volume_render_backward")
+    return (grad, vis, con) if want_counts else grad
+
+
+def _c2w34(c2w):
+    c = _f32(np.asarray(c2w)[:3, :4])
+    assert c.shape == (3, 4)
+    return c
+
+
+def volume_render_image(tree, c2w, fx, fy, width, height, opt, want_counts=False):
+    c = _c2w34(c2w)
+    out = np.zeros((height, width, out_dim(tree, opt)), np.float32)
+    Q = width * height
+    vis = np.zeros(Q, np.int32) if want_counts else None
+    con = np.zeros(Q, np.int32) if want_counts else None
+    _check(lib().orc_volume_render_image(C.byref(tree.c), _ptr(c), C.c_float(fx), C.c_float(fy),
+                                         C.c_int32(width), C.c_int32(height), C.byref(opt),
+                                         _ptr(out), _ptr(vis), _ptr(con)), "volume_render_image")
+    return (out, vis, con) if want_counts else out
+
+
+def volume_render_image_backward(tree, c2w, fx, fy, width, height, opt, grad_out):
+    c = _c2w34(c2w)
+    g = _f32(grad_out)
+    grad = np.zeros(tree.data.shape, np.float64)
+    _check(lib().orc_volume_render_image_backward(
+        C.byref(tree.c), _ptr(c), C.c_float(fx), C.c_float(fy), C.c_int32(width),
+        C.c_int32(height), C.byref(opt), _ptr(g), _ptr(grad)), "volume_render_image_backward")
+    return grad
+
+
+def pixel_rays(c2w, fx, fy, width, height):
+    c = _c2w34(c2w)
+    o = np.zeros((width * height, 3), np.float32)
+    d = np.zeros((width * height, 3), np.float32)
+    lib().orc_pixel_rays(_ptr(c), C.c_float(fx), C.c_float(fy), C.c_int32(width),
+                         C.c_int32(height), _ptr(o), _ptr(d))
+    return o, d

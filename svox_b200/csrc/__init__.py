@@ -1,0 +1,333 @@
+"""Host-side mirror of the reference's native module ``svox.csrc``.
+
+Same spec classes (``TreeSpec``, ``RaysSpec``, ``CameraSpec``,
+``RenderOptions``) and the same functions with the same arguments and
+results as the reference's pybind11 module (svox/csrc/svox.cpp:63-122), but
+implemented by the C-ABI library ``libsvox_b200.so`` (hand-written sm_100a
+kernels) loaded with ctypes.  Tensors are allocated by PyTorch and handed to
+the library as raw device pointers together with the current CUDA stream.
+
+There is no CPU implementation: if the library is missing or a tensor is
+not on a CUDA device, the call raises.
+"""
+import ctypes as C
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libsvox_b200.so")
+
+FORMAT_RGBA, FORMAT_SH, FORMAT_SG, FORMAT_ASG = 0, 1, 2, 3
+
+
+class _CTree(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("child", C.c_void_p), ("offset", C.c_void_p),
+                ("scaling", C.c_void_p), ("M", C.c_int64), ("N", C.c_int32), ("K", C.c_int32)]
+
+
+class _CRays(C.Structure):
+    _fields_ = [("origins", C.c_void_p), ("dirs", C.c_void_p), ("vdirs", C.c_void_p),
+                ("Q", C.c_int64)]
+
+
+class _CCamera(C.Structure):
+    _fields_ = [("c2w", C.c_void_p), ("fx", C.c_float), ("fy", C.c_float),
+                ("width", C.c_int32), ("height", C.c_int32)]
+
+
+class _COptions(C.Structure):
+    _fields_ = [("step_size", C.c_float), ("background_brightness", C.c_float),
+                ("format", C.c_int32), ("basis_dim", C.c_int32), ("ndc_width", C.c_int32),
+                ("ndc_height", C.c_int32), ("ndc_focal", C.c_float), ("min_comp", C.c_int32),
+                ("max_comp", C.c_int32), ("sigma_thresh", C.c_float),
+                ("stop_thresh", C.c_float), ("density_softplus", C.c_int32),
+                ("rgb_padding", C.c_float)]
+
+
+# ---------------------------------------------------------------------------
+# Spec objects: plain attribute bags with the reference's field names.
+
+class TreeSpec:
+    def __init__(self):
+        self.data = self.child = self.parent_depth = self.extra_data = None
+        self.offset = self.scaling = None
+        self._weight_accum = None
+        self._weight_accum_max = False
+
+
+class RaysSpec:
+    def __init__(self):
+        self.origins = self.dirs = self.vdirs = None
+
+
+class CameraSpec:
+    def __init__(self):
+        self.c2w = None
+        self.fx = self.fy = 0.0
+        self.width = self.height = 0
+
+
+class RenderOptions:
+    def __init__(self):
+        self.step_size = 1e-3
+        self.background_brightness = 1.0
+        self.format = FORMAT_RGBA
+        self.basis_dim = -1
+        self.ndc_width = -1
+        self.ndc_height = -1
+        self.ndc_focal = 0.0
+        self.min_comp = 0
+        self.max_comp = 0
+        self.sigma_thresh = 0.0
+        self.stop_thresh = 0.0
+        self.density_softplus = False
+        self.rgb_padding = 0.0
+
+    def _pack(self):
+        return _COptions(self.step_size, self.background_brightness, int(self.format),
+                         int(self.basis_dim), int(self.ndc_width), int(self.ndc_height),
+                         float(self.ndc_focal), int(self.min_comp), int(self.max_comp),
+                         self.sigma_thresh, self.stop_thresh, int(bool(self.density_softplus)),
+                         self.rgb_padding)
+
+
+# ---------------------------------------------------------------------------
+_lib = None
+
+
+def library():
+    """The loaded C-ABI library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"svox_b200: native library {LIB_PATH} not found; build it with "
+                "`python -m svox_b200.csrc.build` (needs nvcc). There is no CPU fallback.")
+        lib = C.CDLL(LIB_PATH)
+        for name in ("svoxb_strerror", "svoxb_last_cuda_error", "svoxb_version"):
+            getattr(lib, name).restype = C.c_char_p
+        _lib = lib
+    return _lib
+
+
+def is_built():
+    return os.path.exists(LIB_PATH)
+
+
+def _raise(status, what):
+    lib = library()
+    msg = lib.svoxb_strerror(int(status)).decode()
+    cuda = lib.svoxb_last_cuda_error().decode()
+    raise RuntimeError(f"svox_b200.{what}: {msg}" + (f" ({cuda})" if cuda else ""))
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check_input(x, name, dtype=torch.float32):
+    # mirrors CHECK_INPUT (svox/csrc/include/data_spec.hpp:37-42) plus the dtype
+    # check the reference leaves out
+    if not torch.is_tensor(x):
+        raise RuntimeError(f"{name} must be a tensor")
+    if not x.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not x.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    if x.dtype != dtype:
+        raise RuntimeError(f"{name} must be {dtype} (this build computes in float32 only)")
+
+
+def _pack_tree(tree):
+    for n in ("data", "offset", "scaling"):
+        _check_input(getattr(tree, n), n)
+    _check_input(tree.child, "child", torch.int32)
+    d = tree.data
+    if d.dim() != 5 or tree.child.dim() != 4 or tuple(tree.child.shape) != tuple(d.shape[:4]):
+        raise RuntimeError("data must be (M,N,N,N,K) and child (M,N,N,N)")
+    dev = d.device
+    for n in ("child", "offset", "scaling"):
+        if getattr(tree, n).device != dev:
+            raise RuntimeError(f"{n} must be on the same device as data")
+    if tree._weight_accum is not None and tree._weight_accum.numel():
+        raise RuntimeError("weight accumulation is not implemented by svox_b200")
+    return _CTree(d.data_ptr(), tree.child.data_ptr(), tree.offset.data_ptr(),
+                  tree.scaling.data_ptr(), d.shape[0], d.shape[1], d.shape[4])
+
+
+def _pack_rays(rays, dev):
+    for n in ("origins", "dirs", "vdirs"):
+        t = getattr(rays, n)
+        _check_input(t, n)
+        if t.dim() != 2 or t.shape[1] != 3:
+            raise RuntimeError(f"{n} must be (Q, 3)")
+        if t.device != dev:
+            raise RuntimeError(f"{n} must be on the same device as the tree")
+    Q = rays.origins.shape[0]
+    if rays.dirs.shape[0] != Q or rays.vdirs.shape[0] != Q:
+        raise RuntimeError("origins, dirs and vdirs must have the same length")
+    return _CRays(rays.origins.data_ptr(), rays.dirs.data_ptr(), rays.vdirs.data_ptr(), Q)
+
+
+def _pack_camera(cam, dev):
+    _check_input(cam.c2w, "c2w")
+    if cam.c2w.dim() != 2 or cam.c2w.shape[1] != 4 or cam.c2w.shape[0] not in (3, 4):
+        raise RuntimeError("c2w must be (3, 4) or (4, 4)")
+    if cam.c2w.device != dev:
+        raise RuntimeError("c2w must be on the same device as the tree")
+    return _CCamera(cam.c2w.data_ptr(), float(cam.fx), float(cam.fy), int(cam.width),
+                    int(cam.height))
+
+
+def _out_dim(opt, K):
+    # get_out_data_dim, svox/csrc/rt_kernel.cu:1009-1015
+    return (K - 1) // opt.basis_dim if opt.format != FORMAT_RGBA else K - 1
+
+
+def _check_indices(indices):
+    _check_input(indices, "indices")
+    if indices.dim() != 2 or indices.shape[1] != 3:
+        raise RuntimeError("indices must be (Q, 3)")
+
+
+# ---------------------------------------------------------------------------
+# Functions of the reference module
+
+def query_vertical(tree, indices):
+    """-> (values (Q, K) float32, node_ids (Q,) int64); svox_kernel.cu:120-143."""
+    lib = library()
+    ct = _pack_tree(tree)
+    _check_indices(indices)
+    with torch.cuda.device(indices.device):
+        Q = indices.shape[0]
+        values = torch.empty((Q, ct.K), dtype=indices.dtype, device=indices.device)
+        node_ids = torch.empty((Q,), dtype=torch.int64, device=tree.child.device)
+        st = lib.svoxb_query_vertical(C.byref(ct), C.c_void_p(indices.data_ptr()), C.c_int64(Q),
+                                      C.c_void_p(values.data_ptr()),
+                                      C.c_void_p(node_ids.data_ptr()), _stream())
+    if st:
+        _raise(st, "query_vertical")
+    return values, node_ids
+
+
+def query_vertical_backward(tree, indices, grad_output):
+    """-> gradient w.r.t. data, (M, N, N, N, Kg); svox_kernel.cu:160-182."""
+    lib = library()
+    ct = _pack_tree(tree)
+    _check_indices(indices)
+    _check_input(grad_output, "grad_output")
+    Q = indices.shape[0]
+    if grad_output.dim() != 2 or grad_output.shape[0] != Q:
+        raise RuntimeError("grad_output must be (Q, K)")
+    Kg = grad_output.shape[1]
+    with torch.cuda.device(indices.device):
+        grad = torch.empty((ct.M, ct.N, ct.N, ct.N, Kg), dtype=grad_output.dtype,
+                           device=grad_output.device)
+        st = lib.svoxb_query_vertical_backward(
+            C.byref(ct), C.c_void_p(indices.data_ptr()), C.c_int64(Q),
+            C.c_void_p(grad_output.data_ptr()), C.c_int32(Kg), C.c_void_p(grad.data_ptr()),
+            C.c_int(1), _stream())
+    if st:
+        _raise(st, "query_vertical_backward")
+    return grad
+
+
+def volume_render(tree, rays, opt):
+    """-> (Q, out_dim); svox/csrc/rt_kernel.cu:1019-1036."""
+    lib = library()
+    ct = _pack_tree(tree)
+    cr = _pack_rays(rays, tree.data.device)
+    co = opt._pack()
+    with torch.cuda.device(tree.data.device):
+        out = torch.empty((cr.Q, _out_dim(opt, ct.K)), dtype=torch.float32,
+                          device=tree.data.device)
+        st = lib.svoxb_volume_render(C.byref(ct), C.byref(cr), C.byref(co),
+                                     C.c_void_p(out.data_ptr()), _stream())
+    if st:
+        _raise(st, "volume_render")
+    return out
+
+
+def volume_render_image(tree, cam, opt):
+    """-> (height, width, out_dim); svox/csrc/rt_kernel.cu:1038-1057."""
+    lib = library()
+    ct = _pack_tree(tree)
+    cc = _pack_camera(cam, tree.data.device)
+    co = opt._pack()
+    with torch.cuda.device(tree.data.device):
+        out = torch.empty((cc.height, cc.width, _out_dim(opt, ct.K)), dtype=torch.float32,
+                          device=tree.data.device)
+        st = lib.svoxb_volume_render_image(C.byref(ct), C.byref(cc), C.byref(co),
+                                           C.c_void_p(out.data_ptr()), _stream())
+    if st:
+        _raise(st, "volume_render_image")
+    return out
+
+
+def _fwd_ptr(fwd_out, shape):
+    if fwd_out is None:
+        return C.c_void_p(0)
+    _check_input(fwd_out, "fwd_out")
+    if tuple(fwd_out.shape) != tuple(shape):
+        raise RuntimeError("fwd_out must have the shape of the forward output")
+    return C.c_void_p(fwd_out.data_ptr())
+
+
+def volume_render_backward(tree, rays, opt, grad_output, fwd_out=None):
+    """-> gradient w.r.t. data (like data); svox/csrc/rt_kernel.cu:1059-1083.
+
+    ``fwd_out`` (optional, not in the reference signature) is the forward
+    result for the same inputs; it lets the kernel march each ray once.
+    """
+    lib = library()
+    ct = _pack_tree(tree)
+    cr = _pack_rays(rays, tree.data.device)
+    co = opt._pack()
+    _check_input(grad_output, "grad_output")
+    shape = (cr.Q, _out_dim(opt, ct.K))
+    if tuple(grad_output.shape) != shape:
+        raise RuntimeError(f"grad_output must be {shape}")
+    with torch.cuda.device(tree.data.device):
+        grad = torch.empty_like(tree.data, memory_format=torch.contiguous_format)
+        st = lib.svoxb_volume_render_backward(
+            C.byref(ct), C.byref(cr), C.byref(co), C.c_void_p(grad_output.data_ptr()),
+            _fwd_ptr(fwd_out, shape), C.c_void_p(grad.data_ptr()), C.c_int(1), _stream())
+    if st:
+        _raise(st, "volume_render_backward")
+    return grad
+
+
+def volume_render_image_backward(tree, cam, opt, grad_output, fwd_out=None):
+    """-> gradient w.r.t. data; svox/csrc/rt_kernel.cu:1085-1109."""
+    lib = library()
+    ct = _pack_tree(tree)
+    cc = _pack_camera(cam, tree.data.device)
+    co = opt._pack()
+    _check_input(grad_output, "grad_output")
+    shape = (cc.height, cc.width, _out_dim(opt, ct.K))
+    if tuple(grad_output.shape) != shape:
+        raise RuntimeError(f"grad_output must be {shape}")
+    with torch.cuda.device(tree.data.device):
+        grad = torch.empty_like(tree.data, memory_format=torch.contiguous_format)
+        st = lib.svoxb_volume_render_image_backward(
+            C.byref(ct), C.byref(cc), C.byref(co), C.c_void_p(grad_output.data_ptr()),
+            _fwd_ptr(fwd_out, shape), C.c_void_p(grad.data_ptr()), C.c_int(1), _stream())
+    if st:
+        _raise(st, "volume_render_image_backward")
+    return grad
+
+
+def device_status(clear=True):
+    """Synchronise and return the device anomaly word (0 = none), see svox_b200.h."""
+    return int(library().svoxb_device_status(C.c_int(int(clear)), _stream()))
+
+
+def check_device_status():
+    st = device_status(clear=True)
+    if st:
+        _raise(st, "device_status")
+
+
+def version():
+    return library().svoxb_version().decode()

@@ -1,0 +1,111 @@
+// Point query kernels: query_vertical and its backward.
+//
+// Replaces query_single_kernel / query_single_kernel_backward of the
+// reference (svox/csrc/svox_kernel.cu:56-78).  The reference copies each
+// point's K-float record with a per-thread scalar loop, so every warp
+// instruction touches 32 different cache lines on both sides.  Here a thread
+// still descends for its own point, but the records of a warp's 32 points
+// are then moved by the whole warp: lane l handles elements l, l+32, ... of
+// the warp's contiguous (32, K) output block, so stores are fully coalesced
+// and loads walk each record contiguously.
+//
+// HBM roofline per point: 12 B in + K*4 B gathered + K*4 B written + 8 B id
+// (+ one 4-B child entry per level below the jump table, L2 resident).
+#pragma once
+
+#include "common.cuh"
+
+namespace svoxb {
+
+constexpr int kQueryBlock = 256;
+
+struct TreeArgs {
+    const float* __restrict__ data;
+    const int32_t* __restrict__ child;
+    const float* __restrict__ offset;
+    const float* __restrict__ scaling;
+    int64_t M;
+    int32_t N;
+    int32_t K;
+};
+
+static inline TreeArgs tree_args(const svoxb_tree* t) {
+    return TreeArgs{t->data, t->child, t->offset, t->scaling, t->M, t->N, t->K};
+}
+
+__device__ __forceinline__ int64_t locate_point(const TreeArgs& tr, const TopTable& top,
+                                                const float* __restrict__ pts, int64_t i) {
+    const float px = to_tree(__ldg(pts + 3 * i + 0), __ldg(tr.offset + 0), __ldg(tr.scaling + 0));
+    const float py = to_tree(__ldg(pts + 3 * i + 1), __ldg(tr.offset + 1), __ldg(tr.scaling + 1));
+    const float pz = to_tree(__ldg(pts + 3 * i + 2), __ldg(tr.offset + 2), __ldg(tr.scaling + 2));
+    LeafHit hit;
+    const bool ok = (tr.N == 2) ? descend2(tr.child, tr.M, top, px, py, pz, hit)
+                                : descendN(tr.child, tr.M, tr.N, px, py, pz, hit);
+    return ok ? hit.slot : -1;
+}
+
+// MODE 0: copy records out (forward).  MODE 1: scatter-add rows in (backward).
+template <int MODE>
+__global__ void __launch_bounds__(kQueryBlock)
+query_kernel(TreeArgs tr, TopTable top, const float* __restrict__ pts, int64_t Q,
+             float* __restrict__ values_out, int64_t* __restrict__ ids_out,
+             const float* __restrict__ grad_out, float* __restrict__ grad_data, int Kg) {
+    const int64_t i = (int64_t)blockIdx.x * kQueryBlock + threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    int64_t slot = -1;
+    if (i < Q) {
+        slot = locate_point(tr, top, pts, i);
+        if (MODE == 0 && ids_out != nullptr && slot >= 0) ids_out[i] = slot;
+    }
+    if (MODE == 0 && values_out == nullptr) return;
+
+    // Warp-cooperative record move.  `wb` is the first point of this warp.
+    const int64_t wb = i - lane;
+    if (wb >= Q) return;
+    const int K = (MODE == 0) ? tr.K : Kg;
+    const int nvalid = (int)((Q - wb) < 32 ? (Q - wb) : 32);
+    const int total = nvalid * K;
+    int p = 0, e = lane;  // element j = p*K + e of the warp's (nvalid, K) block
+    while (e >= K) { e -= K; ++p; }
+#pragma unroll 4
+    for (int base = 0; base < total; base += 32) {
+        const int j = base + lane;
+        const int src_lane = p < nvalid ? p : nvalid - 1;
+        const int64_t s = __shfl_sync(0xffffffffu, slot, src_lane);
+        if (j < total && s >= 0) {
+            if (MODE == 0) {
+                values_out[wb * K + j] = __ldg(tr.data + s * K + e);
+            } else {
+                atomicAdd(grad_data + s * K + e, __ldg(grad_out + wb * K + j));
+            }
+        }
+        e += 32;
+        while (e >= K) { e -= K; ++p; }
+    }
+}
+
+static int launch_query(int mode, const svoxb_tree* tree, const float* indices, int64_t Q,
+                        float* values_out, int64_t* ids_out, const float* grad_out,
+                        float* grad_data, int Kg, cudaStream_t stream) {
+    if (Q == 0) return SVOXB_OK;
+    if (!indices) return SVOXB_ERR_NULL;
+    if ((Q + kQueryBlock - 1) / kQueryBlock > 0x7fffffffLL) return SVOXB_ERR_TOO_LARGE;
+    TopScratch top;
+    const int max_level = g_tuning.query_top_level >= 0 ? g_tuning.query_top_level : 5;
+    int st = top.build(tree, max_level > 7 ? 7 : max_level, stream);
+    if (st) return st;
+    const TopTable tt{top.cells, top.level};
+    const unsigned grid = (unsigned)((Q + kQueryBlock - 1) / kQueryBlock);
+    if (mode == 0)
+        query_kernel<0><<<grid, kQueryBlock, 0, stream>>>(tree_args(tree), tt, indices, Q,
+                                                          values_out, ids_out, nullptr,
+                                                          nullptr, 0);
+    else
+        query_kernel<1><<<grid, kQueryBlock, 0, stream>>>(tree_args(tree), tt, indices, Q,
+                                                          nullptr, nullptr, grad_out,
+                                                          grad_data, Kg);
+    SVOXB_CUDA(cudaGetLastError());
+    return SVOXB_OK;
+}
+
+}  // namespace svoxb

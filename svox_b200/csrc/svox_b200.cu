@@ -1,0 +1,297 @@
+// C-ABI entry points of libsvox_b200 (see include/svox_b200.h) and the
+// dispatch from run-time record layouts to the templated sm_100a kernels.
+// The library is this single translation unit.
+#include "common.cuh"
+#include "host.cuh"
+#include "query.cuh"
+#include "render.cuh"
+
+namespace svoxb {
+
+struct RenderCall {
+    const svoxb_tree* tree;
+    svoxb_render_options opt;
+    int64_t Q;
+    // forward
+    float* out = nullptr;
+    // backward
+    bool backward = false;
+    const float* grad_out = nullptr;
+    const float* fwd_out = nullptr;
+    float* grad_data = nullptr;
+    cudaStream_t stream = nullptr;
+};
+
+static int out_dim_of(const svoxb_tree* t, const svoxb_render_options& o) {
+    // get_out_data_dim, svox/csrc/rt_kernel.cu:1009-1015
+    return o.format != SVOXB_FORMAT_RGBA ? (t->K - 1) / o.basis_dim : t->K - 1;
+}
+
+static int validate_options(const svoxb_tree* t, const svoxb_render_options& o) {
+    if (!(o.step_size >= 0.f)) return SVOXB_ERR_OPTION;
+    if (o.format == SVOXB_FORMAT_SG || o.format == SVOXB_FORMAT_ASG) return SVOXB_ERR_FORMAT;
+    if (o.format != SVOXB_FORMAT_RGBA && o.format != SVOXB_FORMAT_SH) return SVOXB_ERR_FORMAT;
+    if (o.format == SVOXB_FORMAT_SH) {
+        const int b = o.basis_dim;
+        if (b != 1 && b != 4 && b != 9 && b != 16 && b != 25) return SVOXB_ERR_FORMAT;
+        if (o.min_comp < 0 || o.max_comp >= b) return SVOXB_ERR_OPTION;
+        if (t->K - 1 < b) return SVOXB_ERR_SHAPE;
+    } else if (t->K < 2) {
+        return SVOXB_ERR_SHAPE;
+    }
+    const int od = out_dim_of(t, o);
+    if (od < 1) return SVOXB_ERR_SHAPE;
+    if (o.ndc_width >= 0 && (o.ndc_width == 0 || o.ndc_height <= 0)) return SVOXB_ERR_OPTION;
+    return SVOXB_OK;
+}
+
+template <class Kernel>
+static int persistent_grid(Kernel kernel, int block, size_t smem, int64_t n_gran, unsigned* grid) {
+    if (smem > 48 * 1024)
+        SVOXB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)smem));
+    int per_sm = 0;
+    SVOXB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, block, smem));
+    if (per_sm < 1) per_sm = 1;
+    int64_t g = (int64_t)sm_count() * per_sm;
+    const int64_t need = (n_gran * 32 + block - 1) / block;  // blocks that can get a granule each
+    if (g > need) g = need;
+    if (g < 1) g = 1;
+    *grid = (unsigned)g;
+    return SVOXB_OK;
+}
+
+template <int BD, bool VEC, int BLOCK, class Source>
+static int launch_sh(const RenderCall& c, const Source& src, const TopTable& top, bool in_smem,
+                     size_t smem) {
+    const TreeArgs tr = tree_args(c.tree);
+    const int64_t n_gran = (c.Q + 31) / 32;
+    unsigned grid = 1;
+    int st;
+    if (!c.backward) {
+        auto k = render_fwd_sh<BD, VEC, BLOCK, Source>;
+        if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
+        k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, in_smem, c.out, c.Q);
+    } else if (c.fwd_out != nullptr && c.opt.sigma_thresh == 0.f && c.opt.stop_thresh == 0.f) {
+        auto k = render_bwd_sh<BD, VEC, BLOCK, true, Source>;
+        if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
+        k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, in_smem, c.grad_out, c.fwd_out,
+                                          c.grad_data, c.Q);
+    } else {
+        auto k = render_bwd_sh<BD, VEC, BLOCK, false, Source>;
+        if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
+        k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, in_smem, c.grad_out, nullptr,
+                                          c.grad_data, c.Q);
+    }
+    SVOXB_CUDA(cudaGetLastError());
+    return SVOXB_OK;
+}
+
+template <int BLOCK, class Source>
+static int launch_generic(const RenderCall& c, const Source& src, const TopTable& top,
+                          bool in_smem, size_t smem) {
+    const TreeArgs tr = tree_args(c.tree);
+    const int64_t n_gran = (c.Q + 31) / 32;
+    const int od = out_dim_of(c.tree, c.opt);
+    if (od > kMaxGenericOut) return SVOXB_ERR_FORMAT;
+    unsigned grid = 1;
+    int st;
+    if (!c.backward) {
+        auto k = render_fwd_generic<BLOCK, Source>;
+        if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
+        k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, in_smem, c.out, c.Q, od);
+    } else {
+        auto k = render_bwd_generic<BLOCK, Source>;
+        if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
+        k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, in_smem, c.grad_out, c.grad_data,
+                                          c.Q, od);
+    }
+    SVOXB_CUDA(cudaGetLastError());
+    return SVOXB_OK;
+}
+
+template <int BLOCK, class Source>
+static int dispatch_layout(const RenderCall& c, const Source& src, const TopTable& top,
+                           bool in_smem, size_t smem) {
+    const svoxb_tree* t = c.tree;
+    const bool sh3 = c.opt.format == SVOXB_FORMAT_SH && t->K == 3 * c.opt.basis_dim + 1;
+    if (!sh3) return launch_generic<BLOCK>(c, src, top, in_smem, smem);
+    const bool aligned = ((uintptr_t)t->data % 16 == 0) &&
+                         (!c.backward || (uintptr_t)c.grad_data % 16 == 0);
+    const bool vec = aligned && (t->K % 4 == 0);
+    switch (c.opt.basis_dim) {
+        case 1:
+            return vec ? launch_sh<1, true, BLOCK>(c, src, top, in_smem, smem)
+                       : launch_sh<1, false, BLOCK>(c, src, top, in_smem, smem);
+        case 4: return launch_sh<4, false, BLOCK>(c, src, top, in_smem, smem);
+        case 9:
+            return vec ? launch_sh<9, true, BLOCK>(c, src, top, in_smem, smem)
+                       : launch_sh<9, false, BLOCK>(c, src, top, in_smem, smem);
+        case 16: return launch_sh<16, false, BLOCK>(c, src, top, in_smem, smem);
+        case 25:
+            return vec ? launch_sh<25, true, BLOCK>(c, src, top, in_smem, smem)
+                       : launch_sh<25, false, BLOCK>(c, src, top, in_smem, smem);
+    }
+    return SVOXB_ERR_FORMAT;
+}
+
+template <class Source>
+static int render_dispatch(const RenderCall& c, const Source& src) {
+    int st = validate_tree(c.tree);
+    if (st) return st;
+    if ((st = validate_options(c.tree, c.opt))) return st;
+    if (c.Q < 0) return SVOXB_ERR_SHAPE;
+    if (c.backward) {
+        if (!c.grad_data) return SVOXB_ERR_NULL;
+    }
+    if (c.Q == 0) return SVOXB_OK;
+    if (c.backward ? !c.grad_out : !c.out) return SVOXB_ERR_NULL;
+
+    TopScratch scratch;
+    const int max_level = g_tuning.render_top_level >= 0 ? g_tuning.render_top_level : 5;
+    if ((st = scratch.build(c.tree, max_level > 7 ? 7 : max_level, c.stream))) return st;
+    const TopTable top{scratch.cells, scratch.level};
+    // The table is staged in shared memory up to level 5 (128 KB).
+    const bool in_smem = scratch.level > 0 && scratch.level <= 5;
+    const size_t smem = in_smem ? ((size_t)4 << (3 * scratch.level)) : 0;
+    int block = g_tuning.render_block;
+    if (block == 0) block = (smem > 64 * 1024) ? 1024 : 256;
+    if (block >= 1024) return dispatch_layout<1024>(c, src, top, in_smem, smem);
+    return dispatch_layout<256>(c, src, top, in_smem, smem);
+}
+
+static int zero_grad(const svoxb_tree* t, float* grad, int K, cudaStream_t s) {
+    const size_t n = (size_t)t->M * t->N * t->N * t->N * (size_t)K;
+    SVOXB_CUDA(cudaMemsetAsync(grad, 0, n * sizeof(float), s));
+    return SVOXB_OK;
+}
+
+}  // namespace svoxb
+
+using namespace svoxb;
+
+extern "C" {
+
+int svoxb_query_vertical(const svoxb_tree* tree, const float* indices, int64_t Q,
+                         float* values_out, int64_t* node_ids_out, void* stream) {
+    int st = validate_tree(tree);
+    if (st) return st;
+    if (Q < 0) return SVOXB_ERR_SHAPE;
+    return launch_query(0, tree, indices, Q, values_out, node_ids_out, nullptr, nullptr, 0,
+                        (cudaStream_t)stream);
+}
+
+int svoxb_query_vertical_backward(const svoxb_tree* tree, const float* indices, int64_t Q,
+                                  const float* grad_output, int32_t Kg, float* grad_data_out,
+                                  int zero_first, void* stream) {
+    int st = validate_tree(tree);
+    if (st) return st;
+    if (Q < 0 || Kg < 1) return SVOXB_ERR_SHAPE;
+    if (!grad_data_out || (Q > 0 && !grad_output)) return SVOXB_ERR_NULL;
+    if (zero_first && (st = zero_grad(tree, grad_data_out, Kg, (cudaStream_t)stream))) return st;
+    return launch_query(1, tree, indices, Q, nullptr, nullptr, grad_output, grad_data_out, Kg,
+                        (cudaStream_t)stream);
+}
+
+int svoxb_volume_render(const svoxb_tree* tree, const svoxb_rays* rays,
+                        const svoxb_render_options* opt, float* out, void* stream) {
+    if (!tree || !rays || !opt) return SVOXB_ERR_NULL;
+    if (rays->Q > 0 && (!rays->origins || !rays->dirs || !rays->vdirs)) return SVOXB_ERR_NULL;
+    RenderCall c{tree, *opt, rays->Q};
+    c.out = out;
+    c.stream = (cudaStream_t)stream;
+    return render_dispatch(c, RayBatch{rays->origins, rays->dirs, rays->vdirs});
+}
+
+int svoxb_volume_render_image(const svoxb_tree* tree, const svoxb_camera* cam,
+                              const svoxb_render_options* opt, float* out, void* stream) {
+    if (!tree || !cam || !opt || !cam->c2w) return SVOXB_ERR_NULL;
+    if (cam->width < 0 || cam->height < 0) return SVOXB_ERR_SHAPE;
+    RenderCall c{tree, *opt, (int64_t)cam->width * cam->height};
+    c.out = out;
+    c.stream = (cudaStream_t)stream;
+    return render_dispatch(c, PixelRays{cam->c2w, cam->fx, cam->fy, cam->width, cam->height});
+}
+
+int svoxb_volume_render_backward(const svoxb_tree* tree, const svoxb_rays* rays,
+                                 const svoxb_render_options* opt, const float* grad_output,
+                                 const float* fwd_out, float* grad_data_out, int zero_first,
+                                 void* stream) {
+    if (!tree || !rays || !opt) return SVOXB_ERR_NULL;
+    if (rays->Q > 0 && (!rays->origins || !rays->dirs || !rays->vdirs)) return SVOXB_ERR_NULL;
+    int st = validate_tree(tree);
+    if (st) return st;
+    if (!grad_data_out) return SVOXB_ERR_NULL;
+    if (zero_first && (st = zero_grad(tree, grad_data_out, tree->K, (cudaStream_t)stream)))
+        return st;
+    RenderCall c{tree, *opt, rays->Q};
+    c.backward = true;
+    c.grad_out = grad_output;
+    c.fwd_out = fwd_out;
+    c.grad_data = grad_data_out;
+    c.stream = (cudaStream_t)stream;
+    return render_dispatch(c, RayBatch{rays->origins, rays->dirs, rays->vdirs});
+}
+
+int svoxb_volume_render_image_backward(const svoxb_tree* tree, const svoxb_camera* cam,
+                                       const svoxb_render_options* opt,
+                                       const float* grad_output, const float* fwd_out,
+                                       float* grad_data_out, int zero_first, void* stream) {
+    if (!tree || !cam || !opt || !cam->c2w) return SVOXB_ERR_NULL;
+    if (cam->width < 0 || cam->height < 0) return SVOXB_ERR_SHAPE;
+    int st = validate_tree(tree);
+    if (st) return st;
+    if (!grad_data_out) return SVOXB_ERR_NULL;
+    if (zero_first && (st = zero_grad(tree, grad_data_out, tree->K, (cudaStream_t)stream)))
+        return st;
+    RenderCall c{tree, *opt, (int64_t)cam->width * cam->height};
+    c.backward = true;
+    c.grad_out = grad_output;
+    c.fwd_out = fwd_out;
+    c.grad_data = grad_data_out;
+    c.stream = (cudaStream_t)stream;
+    return render_dispatch(c, PixelRays{cam->c2w, cam->fx, cam->fy, cam->width, cam->height});
+}
+
+int svoxb_device_status(int clear, void* stream) {
+    int word = 0;
+    SVOXB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    SVOXB_CUDA(cudaMemcpyFromSymbol(&word, g_status, sizeof(int)));
+    if (clear && word != 0) {
+        const int zero = 0;
+        SVOXB_CUDA(cudaMemcpyToSymbol(g_status, &zero, sizeof(int)));
+    }
+    return word;
+}
+
+const char* svoxb_strerror(int status) {
+    switch (status) {
+        case SVOXB_OK: return "ok";
+        case SVOXB_ERR_NULL: return "a required pointer is null";
+        case SVOXB_ERR_SHAPE: return "inconsistent or negative size";
+        case SVOXB_ERR_FORMAT: return "data format / record layout not supported";
+        case SVOXB_ERR_OPTION: return "invalid render option";
+        case SVOXB_ERR_CUDA: return "CUDA runtime error";
+        case SVOXB_ERR_TREE: return "corrupt tree: a descent left the node array";
+        case SVOXB_ERR_MARCH: return "a ray exceeded the marching step cap";
+        case SVOXB_ERR_TOO_LARGE: return "size beyond the supported maximum";
+    }
+    return "unknown status";
+}
+
+const char* svoxb_last_cuda_error(void) { return t_cuda_error; }
+
+const char* svoxb_version(void) { return "0.1.0"; }
+
+// Tuning hook for experiments: key 0 = render block size (256 | 1024, 0 auto),
+// 1 = render jump-table level cap (-1 auto), 2 = query jump-table level cap.
+int svoxb_tune(int key, int value) {
+    switch (key) {
+        case 0: g_tuning.render_block = value; return SVOXB_OK;
+        case 1: g_tuning.render_top_level = value; return SVOXB_OK;
+        case 2: g_tuning.query_top_level = value; return SVOXB_OK;
+    }
+    return SVOXB_ERR_OPTION;
+}
+
+}  // extern "C"

@@ -1,0 +1,182 @@
+"""Differentiable voxel-marching volume renderer with SH colour.
+
+Drop-in for the reference's ``svox.VolumeRenderer`` on CUDA trees
+(svox/renderer.py:57-89 autograd functions, :114-187 constructor, :189-288
+``forward``, :290-322 ``render_persp``, :387-426 ``persp_rays``, :432-469
+option packing).  Rendering runs in the native library's kernels; there is
+no CPU render path in this package.
+"""
+from collections import namedtuple
+from warnings import warn
+
+import torch
+from torch import autograd, nn
+
+from . import csrc as _C
+from .formats import DataFormat
+
+__all__ = ["VolumeRenderer", "NDCConfig", "Rays", "_VolumeRenderFunction",
+           "_VolumeRenderImageFunction"]
+
+NDCConfig = namedtuple("NDCConfig", ["width", "height", "focal"])
+Rays = namedtuple("Rays", ["origins", "dirs", "viewdirs"])
+
+
+def _rays_spec_from_rays(rays):
+    spec = _C.RaysSpec()
+    spec.origins = rays.origins
+    spec.dirs = rays.dirs
+    spec.vdirs = rays.viewdirs
+    return spec
+
+
+def _make_camera_spec(c2w, width, height, fx, fy):
+    spec = _C.CameraSpec()
+    spec.c2w = c2w
+    spec.width = width
+    spec.height = height
+    spec.fx = fx
+    spec.fy = fy
+    return spec
+
+
+def _single_march_ok(opt):
+    # The backward pass differentiates the render without thresholds
+    # (svox/csrc/rt_kernel.cu:377,441); the saved forward output equals that
+    # render only when both thresholds are off.
+    return opt.sigma_thresh == 0.0 and opt.stop_thresh == 0.0
+
+
+class _VolumeRenderFunction(autograd.Function):
+    """svox/renderer.py:57-72.  Additionally remembers the forward output and
+    the version of ``data`` so that the backward kernel can march once."""
+
+    @staticmethod
+    def forward(ctx, data, tree, rays, opt):
+        out = _C.volume_render(tree, rays, opt)
+        ctx.tree, ctx.rays, ctx.opt = tree, rays, opt
+        ctx.fwd = (out, data._version) if _single_march_ok(opt) else None
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        if not ctx.needs_input_grad[0]:
+            return None, None, None, None
+        fwd = None
+        if ctx.fwd is not None and ctx.fwd[1] == ctx.tree.data._version:
+            fwd = ctx.fwd[0]
+        return _C.volume_render_backward(ctx.tree, ctx.rays, ctx.opt, grad_out.contiguous(),
+                                         fwd), None, None, None
+
+
+class _VolumeRenderImageFunction(autograd.Function):
+    """svox/renderer.py:74-89."""
+
+    @staticmethod
+    def forward(ctx, data, tree, cam, opt):
+        out = _C.volume_render_image(tree, cam, opt)
+        ctx.tree, ctx.cam, ctx.opt = tree, cam, opt
+        ctx.fwd = (out, data._version) if _single_march_ok(opt) else None
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        if not ctx.needs_input_grad[0]:
+            return None, None, None, None
+        fwd = None
+        if ctx.fwd is not None and ctx.fwd[1] == ctx.tree.data._version:
+            fwd = ctx.fwd[0]
+        return _C.volume_render_image_backward(ctx.tree, ctx.cam, ctx.opt,
+                                               grad_out.contiguous(), fwd), None, None, None
+
+
+class VolumeRenderer(nn.Module):
+    def __init__(self, tree, step_size: float = 1e-3, background_brightness: float = 1.0,
+                 ndc: NDCConfig = None, min_comp: int = 0, max_comp: int = -1,
+                 density_softplus: bool = False, rgb_padding: float = 0.0):
+        super().__init__()
+        self.tree = tree
+        self.step_size = step_size
+        self.background_brightness = background_brightness
+        self.ndc_config = ndc
+        self.min_comp = min_comp
+        self.max_comp = max_comp
+        self.density_softplus = density_softplus
+        self.rgb_padding = rgb_padding
+        if isinstance(tree.data_format, DataFormat):
+            self._data_format = None
+        else:
+            warn("Legacy N3Tree (pre 0.2.18) without data_format, auto-infering SH deg")
+            ddim = tree.data_dim
+            self._data_format = DataFormat("") if ddim == 4 else DataFormat(f"SH{(ddim - 1) // 3}")
+        self.tree._weight_accum = None
+
+    @property
+    def data_format(self):
+        return self._data_format or self.tree.data_format
+
+    def _require_cuda(self, cuda):
+        if not cuda or not self.tree.data.is_cuda:
+            raise RuntimeError(
+                "svox_b200 has no CPU render path: move the tree to a CUDA device "
+                "(tree.cuda()) and call with cuda=True")
+
+    def forward(self, rays: Rays, cuda=True, fast=False):
+        """Render ``(B, 3)`` rays -> ``(B, rgb_dim)``.  Differentiable w.r.t. tree.data."""
+        self._require_cuda(cuda)
+        return _VolumeRenderFunction.apply(self.tree.data, self.tree._spec(),
+                                           _rays_spec_from_rays(rays), self._get_options(fast))
+
+    def render_persp(self, c2w, width=800, height=800, fx=1111.111, fy=None, cuda=True,
+                     fast=False):
+        """Render a perspective image -> ``(height, width, rgb_dim)``.  Differentiable."""
+        self._require_cuda(cuda)
+        if fy is None:
+            fy = fx
+        c2w = c2w.to(dtype=self.tree.data.dtype, device=self.tree.data.device).contiguous()
+        return _VolumeRenderImageFunction.apply(
+            self.tree.data, self.tree._spec(),
+            _make_camera_spec(c2w, width, height, fx, fy), self._get_options(fast))
+
+    @staticmethod
+    def persp_rays(c2w, width=800, height=800, fx=1111.111, fy=None):
+        """Row-major perspective rays for :meth:`forward` (svox/renderer.py:387-426)."""
+        if fy is None:
+            fy = fx
+        origins = c2w[None, :3, 3].expand(height * width, -1).contiguous()
+        yy, xx = torch.meshgrid(torch.arange(height, dtype=torch.float64, device=c2w.device),
+                                torch.arange(width, dtype=torch.float64, device=c2w.device),
+                                indexing="ij")
+        xx = (xx - width * 0.5) / float(fx)
+        yy = (yy - height * 0.5) / float(fy)
+        dirs = torch.stack((xx, -yy, -torch.ones_like(xx)), dim=-1)
+        dirs = (dirs / torch.norm(dirs, dim=-1, keepdim=True)).reshape(-1, 3)
+        dirs = torch.matmul(c2w[None, :3, :3].double(), dirs[..., None])[..., 0].float()
+        return Rays(origins=origins, dirs=dirs, viewdirs=dirs)
+
+    def _get_options(self, fast=False):
+        """RenderOptions with the reference's rules (svox/renderer.py:432-469):
+        ``max_comp < 0`` counts from the end, ``fast`` sets both thresholds to
+        1e-2, and attributes ``sigma_thresh`` / ``stop_thresh`` set on the
+        renderer override either."""
+        opts = _C.RenderOptions()
+        opts.step_size = self.step_size
+        opts.background_brightness = self.background_brightness
+        opts.format = self.data_format.format
+        opts.basis_dim = self.data_format.basis_dim
+        opts.min_comp = self.min_comp
+        opts.max_comp = self.max_comp + (opts.basis_dim if self.max_comp < 0 else 0)
+        opts.density_softplus = self.density_softplus
+        opts.rgb_padding = self.rgb_padding
+        if self.ndc_config is not None:
+            opts.ndc_width = self.ndc_config.width
+            opts.ndc_height = self.ndc_config.height
+            opts.ndc_focal = self.ndc_config.focal
+        else:
+            opts.ndc_width = -1
+        opts.sigma_thresh = opts.stop_thresh = 1e-2 if fast else 0.0
+        if hasattr(self, "sigma_thresh"):
+            opts.sigma_thresh = self.sigma_thresh
+        if hasattr(self, "stop_thresh"):
+            opts.stop_thresh = self.stop_thresh
+        return opts

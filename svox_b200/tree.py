@@ -1,0 +1,438 @@
+"""Sparse N^3-tree (N = 2: octree) storage with CUDA point queries.
+
+Drop-in for the reference's ``svox.N3Tree`` on the query / render path
+(svox/svox.py:57-155 constructor and tensors, :208-272 ``forward``,
+:636-705 ``refine``, :947-951 ``__getitem__``, :1015-1024 index packing,
+:1067-1071 ``world2tree``, :1084-1103 ``_spec``).
+
+Storage is three flat tensors, identical in name, shape and meaning to the
+reference so that ``state_dict`` and checkpoints stay interchangeable:
+
+* ``data``          ``(M, N, N, N, K)`` float32 ``nn.Parameter`` -- one record per slot,
+* ``child``         ``(M, N, N, N)`` int32 -- 0 for a leaf, else ``child_node - node``,
+* ``parent_depth``  ``(M, 2)`` int32 -- packed parent slot and depth (root: depth -1 ... 0).
+
+Point queries on a CUDA tree run the ``query_vertical`` kernels of the
+native library; there is no CPU implementation of the query in this
+package (a CPU tree raises).
+"""
+import math
+from warnings import warn
+
+import numpy as np
+import torch
+from torch import autograd, nn
+
+from . import csrc as _C
+from .formats import DataFormat, LocalIndex
+from .view import N3TreeView
+
+__all__ = ["N3Tree", "_QueryVerticalFunction"]
+
+
+class _QueryVerticalFunction(autograd.Function):
+    """Autograd boundary of the point query (svox/svox.py:38-54)."""
+
+    @staticmethod
+    def forward(ctx, data, tree_spec, indices):
+        out, node_ids = _C.query_vertical(tree_spec, indices)
+        ctx.mark_non_differentiable(node_ids)
+        ctx.tree_spec = tree_spec
+        ctx.save_for_backward(indices)
+        return out, node_ids
+
+    @staticmethod
+    def backward(ctx, grad_out, dummy):
+        if ctx.needs_input_grad[0]:
+            return _C.query_vertical_backward(ctx.tree_spec, ctx.saved_tensors[0],
+                                              grad_out.contiguous()), None, None
+        return None, None, None
+
+
+class N3Tree(nn.Module):
+    def __init__(self, N=2, data_dim=None, depth_limit=10, init_reserve=1, init_refine=0,
+                 geom_resize_fact=1.0, radius=0.5, center=(0.5, 0.5, 0.5), data_format="RGBA",
+                 extra_data=None, device="cpu", dtype=torch.float32, map_location=None):
+        super().__init__()
+        assert N >= 2
+        assert depth_limit >= 0
+        if map_location is not None:
+            warn("map_location has been renamed to device and may be removed")
+            device = map_location
+        assert dtype in (torch.float32, torch.float64), "Unsupported dtype"
+        self.N = N
+        self.data_format = DataFormat(data_format) if data_format is not None else None
+        self.data_dim = data_dim
+        self._maybe_auto_data_dim()
+
+        # one node per cell of every level that init_refine will create
+        init_reserve += sum((N ** i) ** 3 for i in range(1, init_refine + 1))
+
+        self.register_parameter("data", nn.Parameter(
+            torch.zeros(init_reserve, N, N, N, self.data_dim, dtype=dtype, device=device)))
+        self.register_buffer("child", torch.zeros(init_reserve, N, N, N, dtype=torch.int32,
+                                                  device=device))
+        self.register_buffer("parent_depth", torch.zeros(init_reserve, 2, dtype=torch.int32,
+                                                         device=device))
+        self.register_buffer("_n_internal", torch.tensor(1, device=device))
+        self.register_buffer("_n_free", torch.tensor(0, device=device))
+
+        if isinstance(radius, (int, float)):
+            radius = [radius] * 3
+        radius = torch.tensor(radius, dtype=dtype, device=device)
+        center = torch.tensor(list(center), dtype=dtype, device=device)
+        self.register_buffer("invradius", 0.5 / radius)
+        self.register_buffer("offset", 0.5 * (1.0 - center / radius))
+
+        self.depth_limit = depth_limit
+        self.geom_resize_fact = geom_resize_fact
+        if extra_data is not None:
+            assert isinstance(extra_data, torch.Tensor)
+            self.register_buffer("extra_data", extra_data.to(dtype=dtype, device=device))
+        else:
+            self.extra_data = None
+
+        self._ver = 0
+        self._invalidate()
+        self._lock_tree_structure = False
+        self._weight_accum = None
+        self._weight_accum_op = None
+        self.refine(repeats=init_refine)
+
+    # ------------------------------------------------------------------
+    # Point query (hot path)
+    def forward(self, indices, cuda=True, want_node_ids=False, world=True):
+        """Values (and packed leaf ids) of the leaves containing ``indices`` ``(Q, 3)``.
+
+        Differentiable w.r.t. ``data``.  Same contract as svox/svox.py:208-272;
+        the tree must live on a CUDA device.
+        """
+        assert not indices.requires_grad  # Grad wrt indices not supported
+        assert len(indices.shape) == 2
+        if not cuda or not self.data.is_cuda:
+            raise RuntimeError(
+                "svox_b200 has no CPU query path: move the tree to a CUDA device "
+                "(tree.cuda()) and call with cuda=True")
+        result, node_ids = _QueryVerticalFunction.apply(self.data, self._spec(world), indices)
+        return (result, node_ids) if want_node_ids else result
+
+    def __getitem__(self, key):
+        return N3TreeView(self, key)
+
+    def __setitem__(self, key, val):
+        N3TreeView(self, key).set(val)
+
+    def snap(self, indices):
+        return self[indices].corners
+
+    # ------------------------------------------------------------------
+    # Structure
+    def refine(self, repeats=1, sel=None):
+        """Split every selected leaf into N^3 children, ``repeats`` times.
+
+        Node numbering is part of the contract (leaf ids returned by queries
+        are ``node * N^3 + cell``): new nodes are appended in selector order,
+        the default selector lists leaves in row-major ``(node, u, v, w)``
+        order, and a repeat selects the new nodes' cells in the same order
+        (svox/svox.py:636-705).  Children inherit the parent's record.
+        Returns True iff ``data`` was re-allocated.
+        """
+        if self._lock_tree_structure:
+            raise RuntimeError("Tree locked")
+        n3 = self.N ** 3
+        resized = False
+        with torch.no_grad():
+            slots = None
+            for rep in range(repeats):
+                filled = self.n_internal
+                if slots is None:
+                    if sel is None:
+                        sel = tuple(self._all_leaves().T)
+                    slots = self._pack_index(torch.stack(
+                        [s.to(self.child.device).long() for s in sel], dim=-1))
+                nodes = torch.div(slots, n3, rounding_mode="floor")
+                ok = (self.parent_depth[nodes, 1] < self.depth_limit) & \
+                     (self.child.view(-1)[slots] == 0)
+                slots, nodes = slots[ok], nodes[ok]
+                n_new = slots.numel()
+                if n_new == 0:
+                    return False
+                grow = filled + n_new - self.capacity
+                if grow > 0:
+                    self._resize_add_cap(grow)
+                    resized = True
+                new_ids = torch.arange(filled, filled + n_new, device=slots.device)
+                self.child[filled:filled + n_new] = 0
+                self.child.view(-1)[slots] = (new_ids - nodes).to(torch.int32)
+                flat = self.data.data.view(-1, self.data_dim)
+                self.data.data[filled:filled + n_new] = flat[slots][:, None, None, None]
+                self.parent_depth[filled:filled + n_new, 0] = slots.to(torch.int32)
+                self.parent_depth[filled:filled + n_new, 1] = self.parent_depth[nodes, 1] + 1
+                if rep < repeats - 1:
+                    slots = (new_ids[:, None] * n3 +
+                             torch.arange(n3, device=slots.device)[None]).reshape(-1)
+                self._n_internal += n_new
+        if repeats > 0:
+            self._invalidate()
+        return resized
+
+    def check_integrity(self):
+        """Structural invariants (as svox/svox.py:583-618); raises AssertionError."""
+        n_int, n_free = self.n_internal, self._n_free.item()
+        assert n_int - n_free > 0, "Tree has no root"
+        assert self.data.shape[0] == self.capacity, "Data capacity mismatch"
+        assert self.child.shape[0] == self.capacity, "Child capacity mismatch"
+        assert (self.parent_depth[0] == 0).all(), "Node at index 0 must be root"
+        live = (self.parent_depth[:n_int, 0] != -1).nonzero().reshape(-1)
+        links = self.child[live]
+        assert (links >= 0).all(), "Nodes not topologically sorted"
+        target = links.long() + live[:, None, None, None]
+        assert target.max() < n_int, "Tree has an out-of-bounds child link"
+        assert (self.parent_depth[target.reshape(-1), 0] != -1).all(), \
+            "Tree has a child link to a deleted node"
+        rest = live[live != 0]
+        if rest.numel() == 0:
+            return True
+        pslot = self.parent_depth[rest, 0].long()
+        assert pslot.min() >= 0 and pslot.max() < n_int * self.N ** 3, "Parent link out-of-bounds"
+        pnode = torch.div(pslot, self.N ** 3, rounding_mode="floor")
+        assert (pnode + self.child.view(-1)[pslot] == rest).all(), \
+            "parent->child cycle consistency failed"
+        return True
+
+    # ------------------------------------------------------------------
+    # Sizes
+    @property
+    def n_leaves(self):
+        return self._all_leaves().shape[0]
+
+    @property
+    def n_internal(self):
+        return self._n_internal.item()
+
+    @property
+    def capacity(self):
+        return self.parent_depth.shape[0]
+
+    @property
+    def max_depth(self):
+        return torch.max(self.depths).item()
+
+    @property
+    def ndim(self):
+        return 2
+
+    @property
+    def shape(self):
+        return torch.Size((self.n_leaves, self.data_dim))
+
+    def size(self, dim):
+        return self.data_dim if dim == 1 else self.n_leaves
+
+    def numel(self):
+        return self.data_dim * self.n_leaves
+
+    def __len__(self):
+        return self.n_leaves
+
+    def __repr__(self):
+        return (f"svox.N3Tree(N={self.N}, data_dim={self.data_dim}, "
+                f"depth_limit={self.depth_limit}, "
+                f"capacity:{self.n_internal - self._n_free.item()}/{self.capacity}, "
+                f"data_format:{self.data_format or 'RGBA'})")
+
+    # ------------------------------------------------------------------
+    # Persistence (svox/svox.py:835-865, 899-938): same npz keys, data as fp16
+    def save(self, path, shrink=True, compress=True):
+        if shrink:
+            self.shrink_to_fit()
+        out = {
+            "data_dim": self.data_dim,
+            "child": self.child.cpu(),
+            "parent_depth": self.parent_depth.cpu(),
+            "n_internal": self._n_internal.cpu().item(),
+            "n_free": self._n_free.cpu().item(),
+            "invradius3": self.invradius.cpu(),
+            "offset": self.offset.cpu(),
+            "depth_limit": self.depth_limit,
+            "geom_resize_fact": self.geom_resize_fact,
+            "data": self.data.data.half().cpu().numpy(),
+        }
+        if self.data_format is not None:
+            out["data_format"] = repr(self.data_format)
+        if self.extra_data is not None:
+            out["extra_data"] = self.extra_data.cpu()
+        (np.savez_compressed if compress else np.savez)(path, **out)
+
+    @classmethod
+    def load(cls, path, device="cpu", dtype=torch.float32, map_location=None):
+        if map_location is not None:
+            warn("map_location has been renamed to device and may be removed")
+            device = map_location
+        assert dtype in (torch.float32, torch.float64), "Unsupported dtype"
+        z = np.load(path)
+        tree = cls(dtype=dtype, device=device)
+        tree.data_dim = int(z["data_dim"])
+        tree.child = torch.from_numpy(z["child"]).to(device)
+        tree.N = tree.child.shape[-1]
+        tree.parent_depth = torch.from_numpy(z["parent_depth"]).to(device)
+        tree._n_internal.fill_(z["n_internal"].item())
+        if "invradius3" in z.files:
+            tree.invradius = torch.from_numpy(z["invradius3"].astype(np.float32)).to(device)
+        else:
+            tree.invradius.fill_(z["invradius"].item())
+        tree.offset = torch.from_numpy(z["offset"].astype(np.float32)).to(device)
+        tree.depth_limit = int(z["depth_limit"])
+        tree.geom_resize_fact = float(z["geom_resize_fact"])
+        tree.data = nn.Parameter(torch.from_numpy(z["data"].astype(np.float32)).to(
+            device=device, dtype=dtype))
+        tree._n_free.fill_(z["n_free"].item() if "n_free" in z.files else 0)
+        tree.data_format = DataFormat(z["data_format"].item()) if "data_format" in z.files \
+            else None
+        tree.extra_data = torch.from_numpy(z["extra_data"]).to(device) \
+            if "extra_data" in z.files else None
+        tree._invalidate()
+        return tree
+
+    def shrink_to_fit(self):
+        """Drop unused capacity (no merged nodes to defragment in this package)."""
+        if self._lock_tree_structure:
+            raise RuntimeError("Tree locked")
+        if self._n_free.item() != 0:
+            raise NotImplementedError("defragmenting merged nodes is not part of this package")
+        new_cap = self.n_internal
+        if new_cap >= self.capacity:
+            return False
+        self.data = nn.Parameter(self.data.data[:new_cap].clone())
+        self.child = self.child[:new_cap].clone()
+        self.parent_depth = self.parent_depth[:new_cap].clone()
+        self._invalidate()
+        return True
+
+    # ------------------------------------------------------------------
+    # Internal utilities
+    def _pack_index(self, txyz):
+        N = self.N
+        return txyz[:, 0] * (N ** 3) + txyz[:, 1] * (N ** 2) + txyz[:, 2] * N + txyz[:, 3]
+
+    def _unpack_index(self, flat):
+        N = self.N
+        w = flat % N
+        v = torch.div(flat, N, rounding_mode="floor") % N
+        u = torch.div(flat, N * N, rounding_mode="floor") % N
+        node = torch.div(flat, N ** 3, rounding_mode="floor")
+        return torch.stack((node, u, v, w), dim=-1)
+
+    def _resize_add_cap(self, cap_needed):
+        cap_needed = max(cap_needed, int(self.capacity * (self.geom_resize_fact - 1.0)))
+
+        def grow(t):
+            pad = torch.zeros((cap_needed, *t.shape[1:]), dtype=t.dtype, device=t.device)
+            return torch.cat((t, pad), dim=0)
+
+        self.data = nn.Parameter(grow(self.data.data))
+        self.child = grow(self.child)
+        self.parent_depth = grow(self.parent_depth)
+
+    def _all_leaves(self):
+        if self._last_all_leaves is None:
+            self._last_all_leaves = (self.child[:self.n_internal] == 0).nonzero(
+                as_tuple=False).cpu()
+        return self._last_all_leaves
+
+    def _calc_corners(self, nodes):
+        """Lower corner of each ``(node, u, v, w)`` cell in tree-local coordinates."""
+        nodes = nodes.to(self.parent_depth.device).long()
+        out = torch.zeros(nodes.shape[0], 3, device=nodes.device, dtype=self.data.dtype)
+        alive = torch.arange(nodes.shape[0], device=nodes.device)
+        cur = nodes
+        while alive.numel():
+            out[alive] = (out[alive] + cur[:, 1:].to(out.dtype)) / self.N
+            up = cur[:, 0] != 0
+            alive, cur = alive[up], cur[up]
+            if alive.numel():
+                cur = self._unpack_index(self.parent_depth[cur[:, 0], 0].long())
+        return out.to(self.data.device)
+
+    def world2tree(self, indices):
+        return torch.addcmul(self.offset, indices, self.invradius)
+
+    def tree2world(self, indices):
+        return (indices - self.offset) / self.invradius
+
+    def _invalidate(self):
+        self._ver += 1
+        self._last_all_leaves = None
+        self._last_frontier = None
+
+    def _spec(self, world=True):
+        """Pack the tensors for the native library (svox/svox.py:1084-1103)."""
+        spec = _C.TreeSpec()
+        spec.data = self.data
+        spec.child = self.child
+        spec.parent_depth = self.parent_depth
+        dev, dt = self.data.device, self.data.dtype
+        spec.extra_data = self.extra_data if self.extra_data is not None else \
+            torch.empty((0, 0), dtype=dt, device=dev)
+        if world:
+            spec.offset, spec.scaling = self.offset, self.invradius
+        else:
+            spec.offset = torch.zeros(3, dtype=dt, device=dev)
+            spec.scaling = torch.ones(3, dtype=dt, device=dev)
+        spec._weight_accum = self._weight_accum if self._weight_accum is not None else \
+            torch.empty(0, dtype=dt, device=dev)
+        spec._weight_accum_max = (self._weight_accum_op == "max")
+        return spec
+
+    def _maybe_auto_data_dim(self):
+        fmt = self.data_format
+        if fmt is not None and fmt.data_dim is not None:
+            if self.data_dim is None:
+                self.data_dim = fmt.data_dim
+            else:
+                assert fmt.data_dim == self.data_dim, "data_dim invalid for given data format"
+        elif self.data_dim is None:
+            self.data_dim = 4  # legacy RGBA default
+
+    @classmethod
+    def from_grid(cls, grid, *args, **kwargs):
+        D = grid.shape[0]
+        assert grid.ndim == 4 and grid.shape[1] == D and grid.shape[2] == D, \
+            "Grid must be a 4D array with first 3 dims equal"
+        logd = int(math.log2(D))
+        assert 2 ** logd == D, "Grid size must be power of 2"
+        kwargs["init_refine"] = logd - 1
+        tree = cls(*args, **kwargs)
+        tree.set_grid(grid)
+        return tree
+
+    def set_grid(self, grid):
+        D = grid.shape[0]
+        assert grid.ndim == 4 and grid.shape[1] == D and grid.shape[2] == D and \
+            grid.shape[-1] == self.data_dim
+        arr = (torch.arange(D) + 0.5) / D
+        xyz = torch.stack(torch.meshgrid(arr, arr, arr, indexing="ij"), -1).reshape(-1, 3)
+        self[LocalIndex(xyz.to(self.data.device))] = grid.reshape(-1, self.data_dim).to(
+            self.data.device)
+
+
+def _install_view_redirects():
+    """``tree.depths`` == ``tree[:].depths`` etc. (svox/svox.py:1106-1123)."""
+    props = ["depths", "lengths", "lengths_local", "corners", "corners_local", "values",
+             "values_local"]
+    funcs = ["sample", "sample_local", "aux", "normal_", "clamp_", "uniform_", "relu_",
+             "sigmoid_", "nan_to_num_"]
+
+    def add_func(name):
+        setattr(N3Tree, name, lambda self, *a, **k: getattr(self[:], name)(*a, **k))
+
+    def add_prop(name):
+        setattr(N3Tree, name, property(lambda self: getattr(self[:], name)))
+
+    for n in funcs:
+        add_func(n)
+    for n in props:
+        add_prop(n)
+
+
+_install_view_redirects()
