@@ -30,7 +30,7 @@ class OrcOptions(C.Structure):
 
 CONTRACT_FIELDS = ["transform", "norm", "pos", "dda_root", "dda_leaf", "sh_dot",
                    "color_pad", "out_acc", "bg_acc", "cam_xy", "cam_rot",
-                   "ndc_shift", "sh_basis"]
+                   "ndc_shift", "sh_basis", "ndc_norm", "descend"]
 
 
 class OrcContract(C.Structure):
@@ -48,17 +48,18 @@ def lib():
     return _lib
 
 
-def get_contract():
+def get_contract(backward=False):
+    """Fused-multiply-add pattern of the forward (or backward) kernels."""
     c = OrcContract()
-    lib().orc_get_contract(C.byref(c))
+    lib().orc_get_contract(C.c_int(int(backward)), C.byref(c))
     return {n: getattr(c, n) for n in CONTRACT_FIELDS}
 
 
-def set_contract(**kw):
-    cur = get_contract()
+def set_contract(backward=False, **kw):
+    cur = get_contract(backward)
     cur.update(kw)
     c = OrcContract(*[cur[n] for n in CONTRACT_FIELDS])
-    lib().orc_set_contract(C.byref(c))
+    lib().orc_set_contract(C.c_int(int(backward)), C.byref(c))
     return cur
 
 
@@ -168,15 +169,31 @@ def trace_log(tree, origin, dir, vdir, opt, cap=4096):
     return slots[:n], dts[:n], ts[:n], out[:out_dim(tree, opt)]
 
 
-def volume_render_backward(tree, origins, dirs, vdirs, opt, grad_out, want_counts=False):
+def _grad_buffers(shape, want_abs):
+    """grad (and, behind it in the same allocation, the sum of |contributions|)."""
+    n = int(np.prod(shape))
+    buf = np.zeros(2 * n if want_abs else n, np.float64)
+    grad = buf[:n].reshape(shape)
+    gabs = buf[n:].reshape(shape) if want_abs else None
+    lib().orc_set_grad_abs(_ptr(grad), _ptr(gabs))
+    return grad, gabs
+
+
+def volume_render_backward(tree, origins, dirs, vdirs, opt, grad_out, want_counts=False,
+                           want_abs=False):
+    """Gradient w.r.t. data (float64).  ``want_abs`` also returns the per-element sum of
+    |contributions| (the scale of a float-atomics sum's rounding error)."""
     o, d, v, g = _f32(origins), _f32(dirs), _f32(vdirs), _f32(grad_out)
     Q = o.shape[0]
-    grad = np.zeros(tree.data.shape, np.float64)
+    grad, gabs = _grad_buffers(tree.data.shape, want_abs)
     vis = np.zeros(Q, np.int32) if want_counts else None
     con = np.zeros(Q, np.int32) if want_counts else None
     _check(lib().orc_volume_render_backward(C.byref(tree.c), _ptr(o), _ptr(d), _ptr(v),
                                             C.c_int64(Q), C.byref(opt), _ptr(g), _ptr(grad),
                                             _ptr(vis), _ptr(con)), "volume_render_backward")
+    lib().orc_set_grad_abs(None, None)
+    if want_abs:
+        return (grad, gabs, vis, con) if want_counts else (grad, gabs)
     return (grad, vis, con) if want_counts else grad
 
 
@@ -198,14 +215,16 @@ def volume_render_image(tree, c2w, fx, fy, width, height, opt, want_counts=False
     return (out, vis, con) if want_counts else out
 
 
-def volume_render_image_backward(tree, c2w, fx, fy, width, height, opt, grad_out):
+def volume_render_image_backward(tree, c2w, fx, fy, width, height, opt, grad_out,
+                                 want_abs=False):
     c = _c2w34(c2w)
     g = _f32(grad_out)
-    grad = np.zeros(tree.data.shape, np.float64)
+    grad, gabs = _grad_buffers(tree.data.shape, want_abs)
     _check(lib().orc_volume_render_image_backward(
         C.byref(tree.c), _ptr(c), C.c_float(fx), C.c_float(fy), C.c_int32(width),
         C.c_int32(height), C.byref(opt), _ptr(g), _ptr(grad)), "volume_render_image_backward")
-    return grad
+    lib().orc_set_grad_abs(None, None)
+    return (grad, gabs) if want_abs else grad
 
 
 def pixel_rays(c2w, fx, fy, width, height):

@@ -75,15 +75,25 @@ typedef struct {
     int32_t out_acc;   /* out += weight*colour           (rt_kernel.cu:289)   */
     int32_t bg_acc;    /* out += T*background            (rt_kernel.cu:318)   */
     int32_t cam_xy;    /* 0 none, 1 fma(y,y,x*x), 2 fma(x,x,y*y) (rt_kernel.cu:766) */
-    int32_t cam_rot;   /* 0 none, 1 fma(c2,z,fma(c1,y,c0*x)), 2 fma(c2,z, fma(c0,x,c1*y)) (rt_kernel.cu:768-770) */
+    int32_t cam_rot;   /* per output row r (base-3 digit r): 0 none, 1 fma(c2,z,fma(c1,y,c0*x)),
+                          2 fma(c2,z,fma(c0,x,c1*y))       (rt_kernel.cu:768-770) */
     int32_t ndc_shift; /* cen + t*dir                    (rt_kernel.cu:784)   */
     int32_t sh_basis;  /* a*b-c forms inside the SH basis (rt_kernel.cu:147-180) */
+    int32_t ndc_norm;  /* sum of squares in the NDC re-normalisation, as `norm` (rt_kernel.cu:795) */
+    int32_t descend;   /* x*N - floor(x*N) as fma(x, N, -floor) (common.cuh:68-76; exact, so moot, for N = 2) */
 } OrcContract;
 
-static OrcContract g_fc = {1, 1, 1, 0, 0, 1, 1, 1, 1, 1, 1, 1, 1};
+/* The forward and the backward kernels of the reference are separate
+ * compilations of the same source, so each has its own pattern. */
+#define ORC_DEFAULT_CONTRACT {1, 2, 1, 0, 0, 1, 1, 1, 1, 1, 1 + 3 * 2 + 9 * 2, 1, 1, 2, 0}
+static OrcContract g_fw = ORC_DEFAULT_CONTRACT;
+static OrcContract g_bw = ORC_DEFAULT_CONTRACT;
+static const OrcContract* g_cur = &g_fw;
+#define g_fc (*g_cur)
 
-void orc_set_contract(const OrcContract* c) { g_fc = *c; }
-void orc_get_contract(OrcContract* c) { *c = g_fc; }
+/* which: 0 = forward kernels and point query, 1 = backward render kernels */
+void orc_set_contract(int which, const OrcContract* c) { *(which ? &g_bw : &g_fw) = *c; }
+void orc_get_contract(int which, OrcContract* c) { *c = which ? g_bw : g_fw; }
 
 static inline float madd(int fused, float a, float b, float c) {
     return fused ? fmaf(a, b, c) : a * b + c;
@@ -119,11 +129,17 @@ static inline int64_t descend(const OrcTree* tr, float* xyz, float* cube_sz) {
     int64_t node = 0;
     *cube_sz = N;
     for (int lvl = 0; lvl < 64; ++lvl) {
+        const float x0 = xyz[0], x1 = xyz[1], x2 = xyz[2];
         xyz[0] *= N; xyz[1] *= N; xyz[2] *= N;
         int32_t u = (int32_t)floorf(xyz[0]);
         int32_t v = (int32_t)floorf(xyz[1]);
         int32_t w = (int32_t)floorf(xyz[2]);
-        xyz[0] -= (float)u; xyz[1] -= (float)v; xyz[2] -= (float)w;
+        if (g_fc.descend) {
+            xyz[0] = fmaf(x0, N, -(float)u); xyz[1] = fmaf(x1, N, -(float)v);
+            xyz[2] = fmaf(x2, N, -(float)w);
+        } else {
+            xyz[0] -= (float)u; xyz[1] -= (float)v; xyz[2] -= (float)w;
+        }
         int64_t slot = node * (int64_t)(Ni * Ni * Ni) + u * (Ni * Ni) + v * Ni + w;
         int32_t skip = tr->child[slot];
         if (skip == 0) return slot;
@@ -376,6 +392,20 @@ static int trace_ray(const OrcTree* tr, const float* origin, float* dir, const f
     return 0;
 }
 
+/* Optional second accumulator: the sum of |contribution| per element, the
+ * scale against which a float-atomics sum may legitimately differ. */
+static double* g_grad_abs = NULL;
+static int64_t g_grad_abs_delta = 0; /* element offset from grad to grad_abs */
+
+static inline void scatter(double* g, float v) {
+#pragma omp atomic
+    *g += (double)v;
+    if (g_grad_abs) {
+#pragma omp atomic
+        g[g_grad_abs_delta] += fabs((double)v);
+    }
+}
+
 /* svox/csrc/rt_kernel.cu:323-477 (trace_ray_backward).  Per-ray arithmetic
  * is float as in the reference; the scatter into grad is a double sum so
  * the result is independent of the order in which rays are processed. */
@@ -425,8 +455,7 @@ static int trace_ray_backward(const OrcTree* tr, const float* grad_output, const
                                                    (double)grad_output[c] * (double)d_rgb_pad);
                         for (int i = opt->min_comp; i <= opt->max_comp; ++i) {
                             const float toadd = basis_fn[i] * tmp2;
-#pragma omp atomic
-                            gval[off + i] += (double)toadd;
+                            scatter(&gval[off + i], toadd);
                         }
                         float col = g_fc.color_pad ? fmaf(sg, d_rgb_pad, -opt->rgb_padding)
                                                    : sg * d_rgb_pad - opt->rgb_padding;
@@ -436,8 +465,7 @@ static int trace_ray_backward(const OrcTree* tr, const float* grad_output, const
                     for (int c = 0; c < out_dim; ++c) {
                         const float sg = sigmoidf(val[c]);
                         const float toadd = weight * sg * (1.f - sg) * grad_output[c] * d_rgb_pad;
-#pragma omp atomic
-                        gval[c] += (double)toadd;
+                        scatter(&gval[c], toadd);
                         float col = g_fc.color_pad ? fmaf(sg, d_rgb_pad, -opt->rgb_padding)
                                                    : sg * d_rgb_pad - opt->rgb_padding;
                         total_color = madd(g_fc.out_acc, col, grad_output[c], total_color);
@@ -498,8 +526,7 @@ static int trace_ray_backward(const OrcTree* tr, const float* grad_output, const
                                            : total_color * light - accum;
                 float gs = delta_t * delta_scale * inner *
                            (opt->density_softplus ? sigmoidf(raw_sigma - 1) : 1);
-#pragma omp atomic
-                gval[K - 1] += (double)gs;
+                scatter(&gval[K - 1], gs);
             }
             t += delta_t;
         }
@@ -518,10 +545,13 @@ static inline void cam2world_ray(int ix, int iy, float* dir, float* origin, cons
     else s = x * x + y * y;
     float z = sqrtf((float)((double)s + 1.0));
     x /= z; y /= z; z = -1.0f / z;
+    int code = g_fc.cam_rot; /* base-3 digits: pattern of row 0, 1, 2 */
     for (int r = 0; r < 3; ++r) {
         const float* c = c2w + 4 * r;
-        if (g_fc.cam_rot == 1) dir[r] = fmaf(c[2], z, fmaf(c[1], y, c[0] * x));
-        else if (g_fc.cam_rot == 2) dir[r] = fmaf(c[2], z, fmaf(c[0], x, c[1] * y));
+        const int pat = code % 3;
+        code /= 3;
+        if (pat == 1) dir[r] = fmaf(c[2], z, fmaf(c[1], y, c[0] * x));
+        else if (pat == 2) dir[r] = fmaf(c[2], z, fmaf(c[0], x, c[1] * y));
         else dir[r] = c[0] * x + c[1] * y + c[2] * z;
         origin[r] = c[3];
     }
@@ -540,8 +570,8 @@ static inline void maybe_world2ndc(const OrcOptions* opt, float* dir, float* cen
     cen[1] = -((2 * opt->ndc_focal) / opt->ndc_height) * (cen[1] / cen[2]);
     cen[2] = 1 + 2 * near / cen[2];
     float a = dir[0] * dir[0], b = dir[1] * dir[1], s;
-    if (g_fc.norm == 1) s = fmaf(dir[2], dir[2], fmaf(dir[1], dir[1], a));
-    else if (g_fc.norm == 2) s = fmaf(dir[2], dir[2], fmaf(dir[0], dir[0], b));
+    if (g_fc.ndc_norm == 1) s = fmaf(dir[2], dir[2], fmaf(dir[1], dir[1], a));
+    else if (g_fc.ndc_norm == 2) s = fmaf(dir[2], dir[2], fmaf(dir[0], dir[0], b));
     else s = a + b + dir[2] * dir[2];
     float n = sqrtf(s);
     dir[0] /= n; dir[1] /= n; dir[2] /= n;
@@ -592,6 +622,7 @@ int orc_volume_render_backward(const OrcTree* tr, const float* origins, const fl
                                int32_t* contrib) {
     const int od = out_dim_of(tr, opt);
     int bad = 0;
+    g_cur = &g_bw;
 #pragma omp parallel for schedule(dynamic, 64) reduction(| : bad)
     for (int64_t i = 0; i < Q; ++i) {
         float o[3] = {origins[3 * i], origins[3 * i + 1], origins[3 * i + 2]};
@@ -603,6 +634,7 @@ int orc_volume_render_backward(const OrcTree* tr, const float* origins, const fl
         if (visits) visits[i] = (int32_t)st.visits;
         if (contrib) contrib[i] = (int32_t)st.contrib;
     }
+    g_cur = &g_fw;
     return bad;
 }
 
@@ -643,12 +675,14 @@ int orc_volume_render_image_backward(const OrcTree* tr, const float* c2w, float 
     const int od = out_dim_of(tr, opt);
     const int64_t Q = (int64_t)W * H;
     int bad = 0;
+    g_cur = &g_bw;
 #pragma omp parallel for schedule(dynamic, 64) reduction(| : bad)
     for (int64_t i = 0; i < Q; ++i) {
         float o[3], d[3], vd[3];
         pixel_ray(tr, c2w, fx, fy, W, H, opt, i, o, d, vd);
         bad |= trace_ray_backward(tr, grad_out + i * od, o, d, vd, opt, grad, NULL);
     }
+    g_cur = &g_fw;
     return bad;
 }
 
@@ -659,6 +693,14 @@ void orc_pixel_rays(const float* c2w, float fx, float fy, int32_t W, int32_t H, 
     const int64_t Q = (int64_t)W * H;
     for (int64_t i = 0; i < Q; ++i)
         cam2world_ray((int)(i % W), (int)(i / W), dirs + 3 * i, origins + 3 * i, c2w, fx, fy, W, H);
+}
+
+/* Direct the next backward calls to also accumulate sum(|contribution|) into
+ * grad_abs (same shape as grad; NULL switches it off).  grad_abs and grad
+ * must be the two halves of ONE allocation: grad_abs = grad + n_elements. */
+void orc_set_grad_abs(double* grad, double* grad_abs) {
+    g_grad_abs = grad_abs;
+    g_grad_abs_delta = grad_abs ? (int64_t)(grad_abs - grad) : 0;
 }
 
 int orc_num_threads(void) {

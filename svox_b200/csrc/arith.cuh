@@ -6,18 +6,22 @@
 // sample position (a different bit can put a sample in the neighbouring leaf),
 // so each such site is pinned here, 1 = fused (one rounding), 0 = separate
 // multiply and add (two roundings), to the choice that reproduces the
-// reference extension built with nvcc 12.9 for sm_100 on the seeded fixtures.
+// reference extension built with nvcc 12.9 for sm_100 on the seeded fixtures
+// (tests/golden/ref_cuda_*.npz).  The forward and the backward kernels of the
+// reference turned out to use the same pattern.
 #pragma once
 
 namespace svoxb {
 
 constexpr int FC_TRANSFORM = 1;  // offset + scaling * q            (common.cuh:48)
-constexpr int FC_NORM = 1;       // 1: fma(z,z,fma(y,y,x*x)); 2: fma(z,z,fma(x,x,y*y)); 0: none (rt_kernel.cu:92)
+constexpr int FC_NORM = 2;       // 1: fma(z,z,fma(y,y,x*x)); 2: fma(z,z,fma(x,x,y*y)); 0: none (rt_kernel.cu:92)
 constexpr int FC_POS = 1;        // origin + t * dir                (rt_kernel.cu:263)
 constexpr int FC_DDA_ROOT = 0;   // t2 = (-cen*invdir) + invdir, cube entry (rt_kernel.cu:215-216,240)
 constexpr int FC_DDA_LEAF = 0;   // same expression inside a leaf   (rt_kernel.cu:271)
 constexpr int FC_CAM_XY = 1;     // x*x + y*y: 1 fma(y,y,x*x), 2 fma(x,x,y*y), 0 none (rt_kernel.cu:766)
-constexpr int FC_CAM_ROT = 1;    // c0*x + c1*y + c2*z: 1 fma(c2,z,fma(c1,y,c0*x)), 2 fma(c2,z,fma(c0,x,c1*y)), 0 none (rt_kernel.cu:768-770)
+// c0*x + c1*y + c2*z per output row: 1 fma(c2,z,fma(c1,y,c0*x)), 2 fma(c2,z,fma(c0,x,c1*y)), 0 none
+// (rt_kernel.cu:768-770; the three rows of the compiled reference differ)
+__host__ __device__ constexpr int fc_cam_rot(int row) { return row == 0 ? 1 : 2; }
 constexpr int FC_NDC_SHIFT = 1;  // cen + t * dir                   (rt_kernel.cu:784)
 
 template <int FUSED>

@@ -184,8 +184,8 @@ struct PixelRays {  // render_image_kernel's inputs (svox/csrc/rt_kernel.cu:758-
         for (int k = 0; k < 3; ++k) {
             const float c0 = __ldg(c2w + 4 * k), c1 = __ldg(c2w + 4 * k + 1),
                         c2 = __ldg(c2w + 4 * k + 2);
-            if (FC_CAM_ROT == 1) d[k] = __fmaf_rn(c2, z, __fmaf_rn(c1, y, __fmul_rn(c0, x)));
-            else if (FC_CAM_ROT == 2) d[k] = __fmaf_rn(c2, z, __fmaf_rn(c0, x, __fmul_rn(c1, y)));
+            if (fc_cam_rot(k) == 1) d[k] = __fmaf_rn(c2, z, __fmaf_rn(c1, y, __fmul_rn(c0, x)));
+            else if (fc_cam_rot(k) == 2) d[k] = __fmaf_rn(c2, z, __fmaf_rn(c0, x, __fmul_rn(c1, y)));
             else d[k] = __fadd_rn(__fadd_rn(__fmul_rn(c0, x), __fmul_rn(c1, y)), __fmul_rn(c2, z));
             o[k] = __ldg(c2w + 4 * k + 3);
             r.vdir[k] = d[k];

@@ -1,0 +1,219 @@
+"""Seeded parity cases shared by the fixture generators and the tests.
+
+Every case is rebuilt from its seed on the CPU (trees and inputs are not
+stored); the fixtures under this directory only hold the OUTPUTS that the
+reference produced for them.  Each builder returns a dict:
+
+    tree     svox_b200.N3Tree on the CPU
+    kind     "rays" | "image" | "query"
+    rays     svox_b200.Rays            (kind == "rays")
+    grad_out upstream gradient         (rays / image; None -> no backward)
+    camera   dict(c2w, width, height, fx, fy)   (kind == "image")
+    points   (Q, 3) world points, grad_out (Q, K)  (kind == "query")
+    render   kwargs for VolumeRenderer(tree, **render)
+    attrs    attributes set on the renderer (sigma_thresh / stop_thresh overrides)
+    fast     the ``fast`` flag of the render call
+"""
+import torch
+
+from svox_b200 import N3Tree, NDCConfig, Rays
+from svox_b200 import workloads as W
+
+
+def _g(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+def _unit(v):
+    return v / v.norm(dim=-1, keepdim=True)
+
+
+def _small_shell(fmt, seed, init_refine=3, extra=3):
+    gen = _g(seed)
+    tree = W.shell_tree(init_refine, extra, fmt, gen, (5.0, 50.0),
+                        [((0.5, 0.5, 0.5), 0.30, 0.35)])
+    return tree, gen
+
+
+def _base(tree, kind, **kw):
+    d = dict(tree=tree, kind=kind, render={}, attrs={}, fast=False, grad_out=None)
+    d.update(kw)
+    return d
+
+
+def c1_rays():
+    """BASELINE config 1: 16^3-leaf SH4 tree, 4096 rays, backward of sum(rgb)."""
+    tree, rays = W.config1()
+    return _base(tree, "rays", rays=rays, grad_out=torch.ones(rays.origins.shape[0], 3))
+
+
+def shell_sh9_rays():
+    """Config-4-like scene at 1/4 resolution: shell refined to 128^3, SH9, 8192 rays."""
+    tree, gen = _small_shell("SH9", 103)
+    rays = W.sphere_rays(8192, gen, 4.0, 0.2, 0.8)
+    gout = torch.randn(8192, 3, generator=gen)
+    return _base(tree, "rays", rays=rays, grad_out=gout)
+
+
+def c4_sample_rays():
+    """BASELINE config 4 (full tree), first 16384 rays of its 2^20, forward only."""
+    tree, rays, _ = W.config4(Q=1 << 14)
+    return _base(tree, "rays", rays=rays)
+
+
+def shell_sh16_image():
+    """Config-3-like scene at 1/4 resolution: SH16, 96x96 image, stop_thresh 1e-2."""
+    tree, gen = _small_shell("SH16", 102)
+    c2w = W.look_at_cameras(1, gen, 4.0)[0]
+    gout = torch.randn(96, 96, 3, generator=gen)
+    return _base(tree, "image", camera=dict(c2w=c2w, width=96, height=96, fx=133.0, fy=133.0),
+                 attrs=dict(stop_thresh=1e-2), grad_out=gout)
+
+
+def _variant(seed=104, Q=2048, **kw):
+    tree, gen = _small_shell("SH9", seed, extra=2)
+    rays = W.sphere_rays(Q, gen, 4.0, 0.2, 0.8)
+    gout = torch.randn(Q, 3, generator=gen)
+    return _base(tree, "rays", rays=rays, grad_out=gout, **kw)
+
+
+def opt_fast():
+    """fast=True: sigma_thresh = stop_thresh = 1e-2."""
+    return _variant(fast=True)
+
+
+def opt_softplus_pad_bg():
+    """density_softplus, rgb_padding, grey background, smaller step."""
+    return _variant(render=dict(density_softplus=True, rgb_padding=0.001,
+                                background_brightness=0.5, step_size=5e-4))
+
+
+def opt_comp_range():
+    """Only SH components 1..3 are rendered."""
+    return _variant(render=dict(min_comp=1, max_comp=3))
+
+
+def rgba_rays():
+    """RGBA records (K = 4), uniform 8^3 tree."""
+    gen = _g(105)
+    tree = W.uniform_tree(2, "RGBA", gen, sigma_range=(0.0, 20.0))
+    rays = W.sphere_rays(1024, gen, 2.0, 0.3, 0.7)
+    return _base(tree, "rays", rays=rays, grad_out=torch.randn(1024, 3, generator=gen))
+
+
+def sh1_rays():
+    gen = _g(106)
+    tree = W.uniform_tree(2, "SH1", gen, sigma_range=(0.0, 20.0))
+    rays = W.sphere_rays(1024, gen, 2.0, 0.3, 0.7)
+    return _base(tree, "rays", rays=rays, grad_out=torch.randn(1024, 3, generator=gen))
+
+
+def sh25_rays():
+    gen = _g(107)
+    tree = W.uniform_tree(2, "SH25", gen, sigma_range=(0.0, 20.0), coef_std=0.5)
+    rays = W.sphere_rays(1024, gen, 2.0, 0.3, 0.7)
+    return _base(tree, "rays", rays=rays, grad_out=torch.randn(1024, 3, generator=gen))
+
+
+def _aniso_tree(gen, fmt="SH4"):
+    tree = N3Tree(N=2, data_format=fmt, init_refine=2, radius=[0.6, 0.8, 1.0],
+                  center=[0.1, -0.2, 0.3])
+    # irregular structure: refine a random third of the leaves twice
+    for _ in range(2):
+        mask = torch.rand(tree.n_leaves, generator=gen) < 0.33
+        tree[mask].refine()
+    with torch.no_grad():
+        d = tree.data.data
+        d[..., :-1] = torch.randn(d[..., :-1].shape, generator=gen)
+        d[..., -1] = torch.rand(d[..., -1].shape, generator=gen) * 12.0 - 2.0
+    return tree
+
+
+def aniso_rays():
+    """Non-cubic world box (scaling != 1, offset != 0), irregular depth, negative densities."""
+    gen = _g(108)
+    tree = _aniso_tree(gen)
+    Q = 2048
+    origins = torch.tensor([0.1, -0.2, 0.3]) + 3.0 * _unit(torch.randn(Q, 3, generator=gen))
+    targets = torch.tensor([0.1, -0.2, 0.3]) + (torch.rand(Q, 3, generator=gen) - 0.5) * \
+        torch.tensor([1.0, 1.4, 1.8])
+    dirs = _unit(targets - origins) * (0.5 + torch.rand(Q, 1, generator=gen))  # non-unit dirs
+    vdirs = _unit(dirs + 0.05 * torch.randn(Q, 3, generator=gen))
+    return _base(tree, "rays", rays=Rays(origins, dirs, vdirs),
+                 grad_out=torch.randn(Q, 3, generator=gen))
+
+
+def ndc_image():
+    """Forward-facing camera rendered through the NDC warp; world box [-1,1]^3."""
+    gen = _g(109)
+    tree = N3Tree(N=2, data_format="SH4", init_refine=3, radius=1.0, center=[0.0, 0.0, 0.0])
+    with torch.no_grad():
+        d = tree.data.data
+        d[..., :-1] = torch.randn(d[..., :-1].shape, generator=gen)
+        d[..., -1] = torch.rand(d[..., -1].shape, generator=gen) * 6.0
+    c2w = torch.tensor([[0.9950, 0.0, 0.0998, 0.10],
+                        [0.0050, 0.9987, -0.0498, -0.05],
+                        [-0.0997, 0.0500, 0.9938, 0.20]])
+    return _base(tree, "image", camera=dict(c2w=c2w, width=64, height=48, fx=60.0, fy=60.0),
+                 render=dict(ndc=NDCConfig(width=64, height=48, focal=60.0)),
+                 grad_out=torch.randn(48, 64, 3, generator=gen))
+
+
+def n3_rays():
+    """Branching factor 3 (27 children per node)."""
+    gen = _g(110)
+    tree = N3Tree(N=3, data_format="SH4", init_refine=2)
+    with torch.no_grad():
+        d = tree.data.data
+        d[..., :-1] = torch.randn(d[..., :-1].shape, generator=gen)
+        d[..., -1] = torch.rand(d[..., -1].shape, generator=gen) * 10.0
+    rays = W.sphere_rays(1024, gen, 2.0, 0.3, 0.7)
+    return _base(tree, "rays", rays=rays, grad_out=torch.randn(1024, 3, generator=gen))
+
+
+def _edge_points(gen, Q, lo, hi):
+    """Uniform points plus the corner cases: cube faces, corners, outside, cell boundaries."""
+    pts = torch.rand(Q, 3, generator=gen) * (hi - lo) + lo
+    special = torch.tensor([[0.0, 0.0, 0.0], [1.0, 1.0, 1.0], [0.5, 0.5, 0.5], [-3.0, 0.2, 7.0],
+                            [0.999999, 0.9999999, 1.0000001], [0.25, 0.75, 0.125],
+                            [0.0625, 0.5, 0.99], [1e-9, 1e-20, 0.3]])
+    special = special * (hi - lo) + lo
+    pts[:special.shape[0]] = special
+    return pts
+
+
+def query_c1():
+    """Point query on the config-1 tree incl. boundary and out-of-range points."""
+    tree, _ = W.config1()
+    gen = _g(111)
+    pts = _edge_points(gen, 16384, torch.zeros(3), torch.ones(3))
+    return _base(tree, "query", points=pts,
+                 grad_out=torch.randn(16384, tree.data_dim, generator=gen))
+
+
+def query_aniso():
+    """Point query with a world transform on an irregular tree."""
+    gen = _g(112)
+    tree = _aniso_tree(gen, "SH9")
+    lo = torch.tensor([0.1 - 0.6, -0.2 - 0.8, 0.3 - 1.0])
+    hi = torch.tensor([0.1 + 0.6, -0.2 + 0.8, 0.3 + 1.0])
+    pts = _edge_points(gen, 8192, lo, hi)
+    return _base(tree, "query", points=pts,
+                 grad_out=torch.randn(8192, tree.data_dim, generator=gen))
+
+
+def query_shell():
+    """Point query on the deep shell tree (depths 4..7 mixed)."""
+    tree, gen = _small_shell("SH16", 113)
+    pts = _edge_points(gen, 16384, torch.zeros(3), torch.ones(3))
+    return _base(tree, "query", points=pts,
+                 grad_out=torch.randn(16384, tree.data_dim, generator=gen))
+
+
+CASES = {f.__name__: f for f in [
+    c1_rays, shell_sh9_rays, c4_sample_rays, shell_sh16_image, opt_fast, opt_softplus_pad_bg,
+    opt_comp_range, rgba_rays, sh1_rays, sh25_rays, aniso_rays, ndc_image, n3_rays,
+    query_c1, query_aniso, query_shell]}
+
+# Cases whose fixtures are cheap enough to check on the CPU in the default test run.
+BIG = {"c4_sample_rays"}

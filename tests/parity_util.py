@@ -1,0 +1,212 @@
+"""Run one parity case (tests/golden/cases.py) through each implementation.
+
+* ``run_product``  -- the CUDA path of svox_b200, through its public API
+* ``run_oracle``   -- the CPU oracle (oracle/)
+* ``run_ref_cuda`` -- the unmodified reference extension built into
+  ``oracle/_ref`` (GPU only; used to generate fixtures and as an extra check)
+
+Each returns a dict with ``out`` (rendered colours or queried values),
+``ids`` (query) and ``grad`` (gradient w.r.t. tree.data, float64 numpy or
+None).
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+QUERY_ROWS_KEPT = 256  # query fixtures keep the values of this many points
+
+import svox_b200  # noqa: E402
+from svox_b200 import csrc as _C  # noqa: E402
+
+
+def _renderer(tree, case):
+    r = svox_b200.VolumeRenderer(tree, **case["render"])
+    for k, v in case["attrs"].items():
+        setattr(r, k, v)
+    return r
+
+
+def options_of(case):
+    """The RenderOptions the renderer would pack for this case."""
+    return _renderer(case["tree"], case)._get_options(case["fast"])
+
+
+# ---------------------------------------------------------------------------
+def run_product(case, device="cuda:0", backward=True, single_march=True):
+    tree = case["tree"].to(device)
+    tree.zero_grad(set_to_none=True)
+    res = {"ids": None, "grad": None}
+    if case["kind"] == "query":
+        pts = case["points"].to(device)
+        vals, ids = tree(pts, want_node_ids=True)
+        res["out"], res["ids"] = vals.detach().cpu().numpy(), ids.cpu().numpy()
+        if backward and case["grad_out"] is not None:
+            vals.backward(case["grad_out"].to(device))
+    else:
+        r = _renderer(tree, case)
+        if case["kind"] == "rays":
+            rays = svox_b200.Rays(*[t.to(device) for t in case["rays"]])
+            out = r(rays, fast=case["fast"])
+        else:
+            cam = case["camera"]
+            out = r.render_persp(cam["c2w"].to(device), width=cam["width"], height=cam["height"],
+                                 fx=cam["fx"], fy=cam["fy"], fast=case["fast"])
+        res["out"] = out.detach().cpu().numpy()
+        if backward and case["grad_out"] is not None:
+            if not single_march:
+                out.grad_fn.fwd = None  # force the reference's two-march backward
+            out.backward(case["grad_out"].to(device))
+    if tree.data.grad is not None:
+        res["grad"] = tree.data.grad.double().cpu().numpy()
+    _C.check_device_status()
+    case["tree"].to("cpu")
+    tree.zero_grad(set_to_none=True)
+    return res
+
+
+# ---------------------------------------------------------------------------
+def run_oracle(case, backward=True, want_counts=False):
+    """Also returns ``grad_abs``: per element the sum of |contributions|, the scale
+    against which a sum formed by float atomics in any order may differ."""
+    from oracle import oracle as orc
+    tree = case["tree"]
+    res = {"ids": None, "grad": None, "grad_abs": None}
+    if case["kind"] == "query":
+        ot = orc.Tree.from_n3tree(tree, world=True)
+        pts = case["points"].numpy()
+        res["out"], res["ids"] = orc.query_vertical(ot, pts)
+        if backward and case["grad_out"] is not None:
+            g = case["grad_out"].numpy()
+            res["grad"] = orc.query_vertical_backward(ot, pts, g)
+            res["grad_abs"] = orc.query_vertical_backward(ot, pts, np.abs(g))
+        return res
+    ot = orc.Tree.from_n3tree(tree, world=True)
+    po = options_of(case)
+    opt = orc.options(step_size=po.step_size, background_brightness=po.background_brightness,
+                      format=po.format, basis_dim=po.basis_dim, ndc_width=po.ndc_width,
+                      ndc_height=po.ndc_height, ndc_focal=po.ndc_focal, min_comp=po.min_comp,
+                      max_comp=po.max_comp, sigma_thresh=po.sigma_thresh,
+                      stop_thresh=po.stop_thresh, density_softplus=po.density_softplus,
+                      rgb_padding=po.rgb_padding)
+    if case["kind"] == "rays":
+        o, d, v = [t.numpy() for t in case["rays"]]
+        r = orc.volume_render(ot, o, d, v, opt, want_counts=want_counts)
+        if want_counts:
+            res["out"], res["visits"], res["contrib"] = r
+        else:
+            res["out"] = r
+        if backward and case["grad_out"] is not None:
+            res["grad"], res["grad_abs"] = orc.volume_render_backward(
+                ot, o, d, v, opt, case["grad_out"].numpy(), want_abs=True)
+    else:
+        cam = case["camera"]
+        args = (cam["c2w"].numpy(), cam["fx"], cam["fy"], cam["width"], cam["height"], opt)
+        r = orc.volume_render_image(ot, *args, want_counts=want_counts)
+        if want_counts:
+            res["out"], res["visits"], res["contrib"] = r
+        else:
+            res["out"] = r
+        if backward and case["grad_out"] is not None:
+            res["grad"], res["grad_abs"] = orc.volume_render_image_backward(
+                ot, *args, case["grad_out"].numpy(), want_abs=True)
+    return res
+
+
+# ---------------------------------------------------------------------------
+_ref_mod = None
+
+
+def ref_module():
+    global _ref_mod
+    if _ref_mod is None:
+        from oracle.build_ref import load_module
+        _ref_mod = load_module()
+    return _ref_mod
+
+
+def run_ref_cuda(case, device="cuda:0", backward=True):
+    ref = ref_module()
+    assert ref is not None, "oracle/_ref is not built"
+    tree = case["tree"].to(device)
+    spec = ref.TreeSpec()
+    spec.data, spec.child, spec.parent_depth = tree.data.data, tree.child, tree.parent_depth
+    spec.extra_data = torch.empty((0, 0), device=device)
+    spec.offset, spec.scaling = tree.offset, tree.invradius
+    spec._weight_accum = torch.empty(0, device=device)
+    spec._weight_accum_max = False
+    res = {"ids": None, "grad": None}
+    if case["kind"] == "query":
+        pts = case["points"].to(device)
+        vals, ids = ref.query_vertical(spec, pts)
+        res["out"], res["ids"] = vals.cpu().numpy(), ids.cpu().numpy()
+        if backward and case["grad_out"] is not None:
+            g = ref.query_vertical_backward(spec, pts, case["grad_out"].to(device))
+            res["grad"] = g.double().cpu().numpy()
+    else:
+        po = options_of(case)
+        opt = ref.RenderOptions()
+        for k in ("step_size", "background_brightness", "format", "basis_dim", "ndc_width",
+                  "ndc_height", "ndc_focal", "min_comp", "max_comp", "sigma_thresh",
+                  "stop_thresh", "density_softplus", "rgb_padding"):
+            setattr(opt, k, getattr(po, k))
+        if case["kind"] == "rays":
+            rs = ref.RaysSpec()
+            rs.origins, rs.dirs, rs.vdirs = [t.to(device).contiguous() for t in case["rays"]]
+            out = ref.volume_render(spec, rs, opt)
+            res["out"] = out.cpu().numpy()
+            if backward and case["grad_out"] is not None:
+                g = ref.volume_render_backward(spec, rs, opt, case["grad_out"].to(device))
+                res["grad"] = g.double().cpu().numpy()
+        else:
+            cam = case["camera"]
+            cs = ref.CameraSpec()
+            cs.c2w = cam["c2w"].to(device).contiguous()
+            cs.width, cs.height, cs.fx, cs.fy = cam["width"], cam["height"], cam["fx"], cam["fy"]
+            out = ref.volume_render_image(spec, cs, opt)
+            res["out"] = out.cpu().numpy()
+            if backward and case["grad_out"] is not None:
+                g = ref.volume_render_image_backward(spec, cs, opt, case["grad_out"].to(device))
+                res["grad"] = g.double().cpu().numpy()
+    torch.cuda.synchronize()
+    case["tree"].to("cpu")
+    return res
+
+
+# ---------------------------------------------------------------------------
+# Gradient fixtures: the full gradient is as large as the tree, so a fixture
+# keeps a seeded sample of its non-zero elements plus two global sums.
+def grad_digest(grad, n_sample=20000, seed=0):
+    flat = np.asarray(grad, dtype=np.float64).reshape(-1)
+    nz = np.flatnonzero(flat)
+    rng = np.random.default_rng(seed)
+    idx = np.sort(rng.choice(nz, size=min(n_sample, nz.size), replace=False)) if nz.size else nz
+    return dict(grad_idx=idx.astype(np.int64), grad_val=flat[idx], grad_sum=flat.sum(),
+                grad_abs_sum=np.abs(flat).sum(), grad_nnz=np.int64(nz.size),
+                grad_max=np.abs(flat).max() if flat.size else 0.0)
+
+
+def grad_excess(grad, ref_grad, grad_abs, rel_tol=1e-4):
+    """Worst |g - ref| in units of the tolerance rel_tol * sum|contributions|
+    (floored at 1e-4 of the largest gradient); <= 1 means within tolerance."""
+    g, r = np.asarray(grad, np.float64).reshape(-1), np.asarray(ref_grad, np.float64).reshape(-1)
+    scale = np.maximum(np.asarray(grad_abs, np.float64).reshape(-1), 1e-4 * np.abs(r).max())
+    return float((np.abs(g - r) / (rel_tol * scale)).max())
+
+
+def grad_error(grad, ref_grad):
+    """max |g - ref| / max |ref| and the worst element-wise relative error over
+    elements with |ref| > 1e-3 * max|ref|."""
+    g, r = np.asarray(grad, np.float64).reshape(-1), np.asarray(ref_grad, np.float64).reshape(-1)
+    scale = np.abs(r).max()
+    if scale == 0:
+        return float(np.abs(g).max()), 0.0
+    err = np.abs(g - r)
+    big = np.abs(r) > 1e-3 * scale
+    rel = float((err[big] / np.abs(r[big])).max()) if big.any() else 0.0
+    return float(err.max() / scale), rel

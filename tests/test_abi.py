@@ -1,0 +1,70 @@
+"""The C-ABI library: loads, exports every symbol the header declares, and
+rejects bad arguments with status codes before touching the GPU (no GPU)."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from svox_b200 import csrc
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "svox_b200.h")
+
+
+def _declared():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(svoxb_[a-z_0-9]+)\s*\(", text)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    if not csrc.is_built():
+        from svox_b200.csrc.build import build
+        build()
+    return csrc.library()
+
+
+def test_header_symbols_exported(lib):
+    names = _declared()
+    assert {"svoxb_query_vertical", "svoxb_query_vertical_backward", "svoxb_volume_render",
+            "svoxb_volume_render_image", "svoxb_volume_render_backward",
+            "svoxb_volume_render_image_backward", "svoxb_device_status",
+            "svoxb_strerror"} <= set(names)
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in svox_b200.h but not exported"
+
+
+def test_strerror_and_version(lib):
+    assert lib.svoxb_strerror(0) == b"ok"
+    assert b"null" in lib.svoxb_strerror(1)
+    assert lib.svoxb_strerror(12345) == b"unknown status"
+    assert re.fullmatch(rb"\d+\.\d+\.\d+", lib.svoxb_version())
+
+
+def test_argument_errors_without_gpu(lib):
+    tree = csrc._CTree(0, 0, 0, 0, 1, 2, 4)
+    assert lib.svoxb_query_vertical(C.byref(tree), None, C.c_int64(4), None, None, None) == 1
+    assert lib.svoxb_query_vertical(None, None, C.c_int64(0), None, None, None) == 1
+    ok = csrc._CTree(16, 16, 16, 16, 1, 2, 4)       # non-null dummies, never dereferenced
+    assert lib.svoxb_query_vertical(C.byref(ok), None, C.c_int64(-1), None, None, None) == 2
+    assert lib.svoxb_query_vertical(C.byref(ok), None, C.c_int64(0), None, None, None) == 0
+    bad_n = csrc._CTree(16, 16, 16, 16, 1, 1, 4)
+    assert lib.svoxb_query_vertical(C.byref(bad_n), None, C.c_int64(0), None, None, None) == 2
+    rays = csrc._CRays(0, 0, 0, 0)
+    opt = csrc.RenderOptions()
+    opt.format, opt.basis_dim, opt.max_comp = csrc.FORMAT_SG, 1, 0
+    o = opt._pack()
+    assert lib.svoxb_volume_render(C.byref(ok), C.byref(rays), C.byref(o), None, None) == 3
+    opt.format, opt.basis_dim, opt.max_comp = csrc.FORMAT_SH, 2, 1   # not a square
+    o = opt._pack()
+    assert lib.svoxb_volume_render(C.byref(ok), C.byref(rays), C.byref(o), None, None) == 3
+    opt.basis_dim, opt.max_comp, opt.step_size = 1, 0, -1.0
+    o = opt._pack()
+    assert lib.svoxb_volume_render(C.byref(ok), C.byref(rays), C.byref(o), None, None) == 4
+    opt.step_size = 1e-3
+    o = opt._pack()
+    # empty batch: nothing to do, no launch
+    assert lib.svoxb_volume_render(C.byref(ok), C.byref(rays), C.byref(o), None, None) == 0
+    assert lib.svoxb_tune(99, 0) == 4
