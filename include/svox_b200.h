@@ -132,6 +132,15 @@ int svoxb_volume_render_image_backward(const svoxb_tree* tree, const svoxb_camer
                                        const float* grad_output, const float* fwd_out,
                                        float* grad_data_out, int zero_first, void* stream);
 
+/* Per-ray march statistics for a ray batch (no counterpart in the
+ * reference; it is how the byte model of the roofline is counted): number of
+ * sampled leaves, of samples passing the forward density test
+ * (sigma > sigma_thresh, up to the early stop) and of samples with sigma > 0
+ * (what the backward pass touches).  Each output is (Q) int32 and may be null. */
+int svoxb_march_stats(const svoxb_tree* tree, const svoxb_rays* rays,
+                      const svoxb_render_options* opt, int32_t* visits, int32_t* contrib_fwd,
+                      int32_t* contrib_bwd, void* stream);
+
 /* Device-side anomaly report.  The kernels bound every loop (the
  * reference's descent and march are unbounded, svox/csrc/include/
  * common.cuh:67-88, rt_kernel.cu:261) and record SVOXB_ERR_TREE /

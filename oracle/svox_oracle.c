@@ -397,14 +397,16 @@ static int trace_ray(const OrcTree* tr, const float* origin, float* dir, const f
 static double* g_grad_abs = NULL;
 static int64_t g_grad_abs_delta = 0; /* element offset from grad to grad_abs */
 
-static inline void scatter(double* g, float v) {
+static inline void scatter_scaled(double* g, float v, double scale) {
 #pragma omp atomic
     *g += (double)v;
     if (g_grad_abs) {
 #pragma omp atomic
-        g[g_grad_abs_delta] += fabs((double)v);
+        g[g_grad_abs_delta] += scale;
     }
 }
+
+static inline void scatter(double* g, float v) { scatter_scaled(g, v, fabs((double)v)); }
 
 /* svox/csrc/rt_kernel.cu:323-477 (trace_ray_backward).  Per-ray arithmetic
  * is float as in the reference; the scatter into grad is a double sum so
@@ -421,6 +423,7 @@ static int trace_ray_backward(const OrcTree* tr, const float* grad_output, const
     float pos[3], basis_fn[25];
     if (opt->format == ORC_FORMAT_SH) sh_basis(opt->basis_dim, vdir, basis_fn);
     float accum = 0.0f;
+    double accum_abs = 0.0; /* sum of |terms| of accum: the scale of its rounding error */
     const float d_rgb_pad = 1 + 2 * opt->rgb_padding;
     /* PASS 1 (:357-419) */
     {
@@ -473,12 +476,15 @@ static int trace_ray_backward(const OrcTree* tr, const float* grad_output, const
                 }
                 light *= att;
                 accum = madd(g_fc.out_acc, weight, total_color, accum);
+                accum_abs += fabs((double)weight * total_color);
             }
             t += delta_t;
         }
         float total_grad = 0.f;
         for (int j = 0; j < out_dim; ++j) total_grad += grad_output[j];
         accum = madd(g_fc.bg_acc, light * opt->background_brightness, total_grad, accum);
+        for (int j = 0; j < out_dim; ++j)
+            accum_abs += fabs((double)light * opt->background_brightness * grad_output[j]);
     }
     /* PASS 2 (:420-475) */
     {
@@ -526,7 +532,11 @@ static int trace_ray_backward(const OrcTree* tr, const float* grad_output, const
                                            : total_color * light - accum;
                 float gs = delta_t * delta_scale * inner *
                            (opt->density_softplus ? sigmoidf(raw_sigma - 1) : 1);
-                scatter(&gval[K - 1], gs);
+                /* the density gradient is a difference of two quantities of the
+                 * size of accum's terms: that is its error scale */
+                scatter_scaled(&gval[K - 1], gs,
+                               fabs((double)delta_t * delta_scale) *
+                                   (fabs((double)total_color * light) + accum_abs));
             }
             t += delta_t;
         }

@@ -126,6 +126,34 @@ def _stream():
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+# Optional per-call device timing (used by the benchmark): when a list is
+# installed with ``set_timing``, every library call appends
+# (name, start_event, end_event), recorded on the launching stream around the
+# call's kernels only (output zero-fill excluded).
+_timing = None
+
+
+def set_timing(records):
+    global _timing
+    _timing = records
+
+
+class _timed:
+    def __init__(self, name):
+        self.name = name
+
+    def __enter__(self):
+        if _timing is not None:
+            self.a = torch.cuda.Event(enable_timing=True)
+            self.b = torch.cuda.Event(enable_timing=True)
+            self.a.record()
+
+    def __exit__(self, *exc):
+        if _timing is not None:
+            self.b.record()
+            _timing.append((self.name, self.a, self.b))
+
+
 def _check_input(x, name, dtype=torch.float32):
     # mirrors CHECK_INPUT (svox/csrc/include/data_spec.hpp:37-42) plus the dtype
     # check the reference leaves out
@@ -242,8 +270,9 @@ def volume_render(tree, rays, opt):
     with torch.cuda.device(tree.data.device):
         out = torch.empty((cr.Q, _out_dim(opt, ct.K)), dtype=torch.float32,
                           device=tree.data.device)
-        st = lib.svoxb_volume_render(C.byref(ct), C.byref(cr), C.byref(co),
-                                     C.c_void_p(out.data_ptr()), _stream())
+        with _timed("volume_render"):
+            st = lib.svoxb_volume_render(C.byref(ct), C.byref(cr), C.byref(co),
+                                         C.c_void_p(out.data_ptr()), _stream())
     if st:
         _raise(st, "volume_render")
     return out
@@ -289,10 +318,11 @@ def volume_render_backward(tree, rays, opt, grad_output, fwd_out=None):
     if tuple(grad_output.shape) != shape:
         raise RuntimeError(f"grad_output must be {shape}")
     with torch.cuda.device(tree.data.device):
-        grad = torch.empty_like(tree.data, memory_format=torch.contiguous_format)
-        st = lib.svoxb_volume_render_backward(
-            C.byref(ct), C.byref(cr), C.byref(co), C.c_void_p(grad_output.data_ptr()),
-            _fwd_ptr(fwd_out, shape), C.c_void_p(grad.data_ptr()), C.c_int(1), _stream())
+        grad = torch.zeros_like(tree.data, memory_format=torch.contiguous_format)
+        with _timed("volume_render_backward"):
+            st = lib.svoxb_volume_render_backward(
+                C.byref(ct), C.byref(cr), C.byref(co), C.c_void_p(grad_output.data_ptr()),
+                _fwd_ptr(fwd_out, shape), C.c_void_p(grad.data_ptr()), C.c_int(0), _stream())
     if st:
         _raise(st, "volume_render_backward")
     return grad
@@ -316,6 +346,22 @@ def volume_render_image_backward(tree, cam, opt, grad_output, fwd_out=None):
     if st:
         _raise(st, "volume_render_image_backward")
     return grad
+
+
+def march_stats(tree, rays, opt):
+    """Per-ray (visits, contributing samples forward, contributing samples backward),
+    three (Q,) int32 tensors (no counterpart in the reference)."""
+    lib = library()
+    ct = _pack_tree(tree)
+    cr = _pack_rays(rays, tree.data.device)
+    co = opt._pack()
+    with torch.cuda.device(tree.data.device):
+        outs = [torch.zeros(cr.Q, dtype=torch.int32, device=tree.data.device) for _ in range(3)]
+        st = lib.svoxb_march_stats(C.byref(ct), C.byref(cr), C.byref(co),
+                                   *[C.c_void_p(t.data_ptr()) for t in outs], _stream())
+    if st:
+        _raise(st, "march_stats")
+    return tuple(outs)
 
 
 def device_status(clear=True):

@@ -307,65 +307,78 @@ render_fwd_sh(TreeArgs tr, Source src, svoxb_render_options opt, TopTable topg, 
         const int64_t gran = next_granule(&s_next, lane);
         if (gran >= n_gran) break;
         const int64_t ray = gran * 32 + lane;
-        if (ray >= Q) continue;
+        const bool valid = ray < Q;
         Ray r;
-        src.load(ray, tr, opt, r);
-        ray_setup(r, tr.scaling);
+        r.hit = false;
+        if (valid) {
+            src.load(ray, tr, opt, r);
+            ray_setup(r, tr.scaling);
+        }
         float o0, o1, o2;
-        if (!r.hit) {
-            o0 = o1 = o2 = opt.background_brightness;
-        } else {
-            o0 = o1 = o2 = 0.f;
-            float basis[BD];
+        o0 = o1 = o2 = r.hit ? 0.f : opt.background_brightness;
+        float basis[BD];
+        if (r.hit) {
             sh_basis<BD>(r.vdir, basis);
 #pragma unroll
             for (int i = 0; i < BD; ++i)
                 if (i < opt.min_comp || i > opt.max_comp) basis[i] = 0.f;
-            float light = 1.f, t = r.tmin;
-            bool stopped = false;
-            int it = 0;
-            while (t < r.tmax) {
-                if (++it > kMaxSteps) { report(SVOXB_ERR_MARCH); break; }
+        }
+        float light = 1.f, t = r.tmin;
+        bool stopped = false;
+        int it = 0;
+        // Warp-uniform loop: the vote makes the warp reconverge every step.
+        bool go = r.hit && t < r.tmax;
+        while (__any_sync(0xffffffffu, go)) {
+            if (go) {
                 Step s;
-                if (!march_step(tr, top, r, t, opt.step_size, s)) break;
-                const float* __restrict__ rec = tr.data + s.leaf.slot * K;
-                float sigma = __ldg(rec + (K - 1));
-                if (opt.density_softplus) sigma = softplus_m1(sigma);
-                if (sigma > opt.sigma_thresh) {
-                    const float att = expf(-s.delta_t * r.delta_scale * sigma);
-                    const float weight = light * (1.f - att);
-                    float v[K];
-                    load_record<K, VEC>(rec, v);
-                    float c[3];
+                if (++it > kMaxSteps) {
+                    report(SVOXB_ERR_MARCH);
+                    go = false;
+                } else if (!march_step(tr, top, r, t, opt.step_size, s)) {
+                    go = false;
+                } else {
+                    const float* __restrict__ rec = tr.data + s.leaf.slot * K;
+                    float sigma = __ldg(rec + (K - 1));
+                    if (opt.density_softplus) sigma = softplus_m1(sigma);
+                    if (sigma > opt.sigma_thresh) {
+                        const float att = expf(-s.delta_t * r.delta_scale * sigma);
+                        const float weight = light * (1.f - att);
+                        float v[K];
+                        load_record<K, VEC>(rec, v);
+                        float c[3];
 #pragma unroll
-                    for (int ch = 0; ch < 3; ++ch) {
-                        float tmp = 0.0f;
+                        for (int ch = 0; ch < 3; ++ch) {
+                            float tmp = 0.0f;
 #pragma unroll
-                        for (int i = 0; i < BD; ++i) tmp += basis[i] * v[ch * BD + i];
-                        c[ch] = sigmoid_ref(tmp) * d_rgb_pad - opt.rgb_padding;
+                            for (int i = 0; i < BD; ++i) tmp += basis[i] * v[ch * BD + i];
+                            c[ch] = sigmoid_ref(tmp) * d_rgb_pad - opt.rgb_padding;
+                        }
+                        o0 += weight * c[0];
+                        o1 += weight * c[1];
+                        o2 += weight * c[2];
+                        light *= att;
+                        if (light <= opt.stop_thresh) {
+                            const float scale = 1.0 / (1.0 - light);
+                            o0 *= scale; o1 *= scale; o2 *= scale;
+                            stopped = true;
+                            go = false;
+                        }
                     }
-                    o0 += weight * c[0];
-                    o1 += weight * c[1];
-                    o2 += weight * c[2];
-                    light *= att;
-                    if (light <= opt.stop_thresh) {
-                        const float scale = 1.0 / (1.0 - light);
-                        o0 *= scale; o1 *= scale; o2 *= scale;
-                        stopped = true;
-                        break;
-                    }
+                    t = __fadd_rn(t, s.delta_t);
+                    if (!(t < r.tmax)) go = false;
                 }
-                t = __fadd_rn(t, s.delta_t);
-            }
-            if (!stopped) {
-                o0 += light * opt.background_brightness;
-                o1 += light * opt.background_brightness;
-                o2 += light * opt.background_brightness;
             }
         }
-        out[3 * ray + 0] = o0;
-        out[3 * ray + 1] = o1;
-        out[3 * ray + 2] = o2;
+        if (r.hit && !stopped) {
+            o0 += light * opt.background_brightness;
+            o1 += light * opt.background_brightness;
+            o2 += light * opt.background_brightness;
+        }
+        if (valid) {
+            out[3 * ray + 0] = o0;
+            out[3 * ray + 1] = o1;
+            out[3 * ray + 2] = o2;
+        }
     }
 }
 
@@ -391,54 +404,69 @@ render_bwd_sh(TreeArgs tr, Source src, svoxb_render_options opt, TopTable topg, 
         const int64_t gran = next_granule(&s_next, lane);
         if (gran >= n_gran) break;
         const int64_t ray = gran * 32 + lane;
-        if (ray >= Q) continue;
         Ray r;
-        src.load(ray, tr, opt, r);
-        ray_setup(r, tr.scaling);
-        if (!r.hit) continue;
+        r.hit = false;
+        if (ray < Q) {
+            src.load(ray, tr, opt, r);
+            ray_setup(r, tr.scaling);
+        }
         float basis[BD];
-        sh_basis<BD>(r.vdir, basis);
-#pragma unroll
-        for (int i = 0; i < BD; ++i)
-            if (i < opt.min_comp || i > opt.max_comp) basis[i] = 0.f;
-        const float g0 = __ldg(grad_out + 3 * ray), g1 = __ldg(grad_out + 3 * ray + 1),
-                    g2 = __ldg(grad_out + 3 * ray + 2);
-        const float gch[3] = {g0, g1, g2};
+        float gch[3] = {0.f, 0.f, 0.f};
         float accum = 0.f;
-        if (SINGLE) {
-            accum = __ldg(fwd_out + 3 * ray) * g0;
-            accum += __ldg(fwd_out + 3 * ray + 1) * g1;
-            accum += __ldg(fwd_out + 3 * ray + 2) * g2;
-        } else {
+        if (r.hit) {
+            sh_basis<BD>(r.vdir, basis);
+#pragma unroll
+            for (int i = 0; i < BD; ++i)
+                if (i < opt.min_comp || i > opt.max_comp) basis[i] = 0.f;
+            gch[0] = __ldg(grad_out + 3 * ray);
+            gch[1] = __ldg(grad_out + 3 * ray + 1);
+            gch[2] = __ldg(grad_out + 3 * ray + 2);
+            if (SINGLE) {
+                accum = __ldg(fwd_out + 3 * ray) * gch[0];
+                accum += __ldg(fwd_out + 3 * ray + 1) * gch[1];
+                accum += __ldg(fwd_out + 3 * ray + 2) * gch[2];
+            }
+        }
+        if (!SINGLE) {
             // PASS 1 of the reference (rt_kernel.cu:357-419) without the scatter
             float light = 1.f, t = r.tmin;
             int it = 0;
-            while (t < r.tmax) {
-                if (++it > kMaxSteps) { report(SVOXB_ERR_MARCH); break; }
-                Step s;
-                if (!march_step(tr, top, r, t, opt.step_size, s)) break;
-                const float* __restrict__ rec = tr.data + s.leaf.slot * K;
-                float sigma = __ldg(rec + (K - 1));
-                if (opt.density_softplus) sigma = softplus_m1(sigma);
-                if (sigma > 0.0f) {
-                    const float att = expf(-s.delta_t * sigma * r.delta_scale);
-                    const float weight = light * (1.f - att);
-                    float v[K];
-                    load_record<K, VEC>(rec, v);
-                    float total_color = 0.f;
+            bool go = r.hit && t < r.tmax;
+            while (__any_sync(0xffffffffu, go)) {
+                if (go) {
+                    Step s;
+                    if (++it > kMaxSteps) {
+                        report(SVOXB_ERR_MARCH);
+                        go = false;
+                    } else if (!march_step(tr, top, r, t, opt.step_size, s)) {
+                        go = false;
+                    } else {
+                        const float* __restrict__ rec = tr.data + s.leaf.slot * K;
+                        float sigma = __ldg(rec + (K - 1));
+                        if (opt.density_softplus) sigma = softplus_m1(sigma);
+                        if (sigma > 0.0f) {
+                            const float att = expf(-s.delta_t * sigma * r.delta_scale);
+                            const float weight = light * (1.f - att);
+                            float v[K];
+                            load_record<K, VEC>(rec, v);
+                            float total_color = 0.f;
 #pragma unroll
-                    for (int ch = 0; ch < 3; ++ch) {
-                        float tmp = 0.0f;
+                            for (int ch = 0; ch < 3; ++ch) {
+                                float tmp = 0.0f;
 #pragma unroll
-                        for (int i = 0; i < BD; ++i) tmp += basis[i] * v[ch * BD + i];
-                        total_color += (sigmoid_ref(tmp) * d_rgb_pad - opt.rgb_padding) * gch[ch];
+                                for (int i = 0; i < BD; ++i) tmp += basis[i] * v[ch * BD + i];
+                                total_color +=
+                                    (sigmoid_ref(tmp) * d_rgb_pad - opt.rgb_padding) * gch[ch];
+                            }
+                            light *= att;
+                            accum += weight * total_color;
+                        }
+                        t = __fadd_rn(t, s.delta_t);
+                        if (!(t < r.tmax)) go = false;
                     }
-                    light *= att;
-                    accum += weight * total_color;
                 }
-                t = __fadd_rn(t, s.delta_t);
             }
-            const float total_grad = g0 + g1 + g2;
+            const float total_grad = gch[0] + gch[1] + gch[2];
             accum += light * opt.background_brightness * total_grad;
         }
         // Scatter march: colour-coefficient gradients (reference PASS 1) and
@@ -446,41 +474,102 @@ render_bwd_sh(TreeArgs tr, Source src, svoxb_render_options opt, TopTable topg, 
         {
             float light = 1.f, t = r.tmin;
             int it = 0;
-            while (t < r.tmax) {
-                if (++it > kMaxSteps) { report(SVOXB_ERR_MARCH); break; }
+            bool go = r.hit && t < r.tmax;
+            while (__any_sync(0xffffffffu, go)) {
+                if (go) {
+                    Step s;
+                    if (++it > kMaxSteps) {
+                        report(SVOXB_ERR_MARCH);
+                        go = false;
+                    } else if (!march_step(tr, top, r, t, opt.step_size, s)) {
+                        go = false;
+                    } else {
+                        const int64_t off = s.leaf.slot * K;
+                        const float* __restrict__ rec = tr.data + off;
+                        float sigma = __ldg(rec + (K - 1));
+                        const float raw_sigma = sigma;
+                        if (opt.density_softplus) sigma = softplus_m1(sigma);
+                        if (sigma > 0.0f) {
+                            const float att = expf(-s.delta_t * sigma * r.delta_scale);
+                            const float weight = light * (1.f - att);
+                            float v[K];
+                            load_record<K, VEC>(rec, v);
+                            float total_color = 0.f;
+#pragma unroll
+                            for (int ch = 0; ch < 3; ++ch) {
+                                float tmp = 0.0f;
+#pragma unroll
+                                for (int i = 0; i < BD; ++i) tmp += basis[i] * v[ch * BD + i];
+                                const float sg = sigmoid_ref(tmp);
+                                const float tmp2 = weight * sg * (1.0 - sg) * gch[ch] * d_rgb_pad;
+#pragma unroll
+                                for (int i = 0; i < BD; ++i) v[ch * BD + i] = basis[i] * tmp2;
+                                total_color += (sg * d_rgb_pad - opt.rgb_padding) * gch[ch];
+                            }
+                            light *= att;
+                            accum -= weight * total_color;
+                            v[K - 1] = s.delta_t * r.delta_scale * (total_color * light - accum) *
+                                       (opt.density_softplus ? sigmoid_ref(raw_sigma - 1) : 1);
+                            scatter_record<K, VEC>(grad_data + off, v);
+                        }
+                        t = __fadd_rn(t, s.delta_t);
+                        if (!(t < r.tmax)) go = false;
+                    }
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Per-ray march statistics (no counterpart in the reference): the number of
+// leaves a ray samples, how many of them pass the forward density test
+// (sigma > sigma_thresh, until the early stop) and how many the backward one
+// (sigma > 0).  These are the V / C_f / C_b of the byte model.
+template <int BLOCK, class Source>
+__global__ void __launch_bounds__(BLOCK)
+march_stats_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable topg,
+                   bool top_in_smem, int32_t* __restrict__ visits,
+                   int32_t* __restrict__ contrib_fwd, int32_t* __restrict__ contrib_bwd,
+                   int64_t Q) {
+    extern __shared__ int32_t s_top[];
+    __shared__ unsigned s_next;
+    if (threadIdx.x == 0) s_next = 0;
+    const TopTable top = stage_top(topg, s_top, top_in_smem);
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int64_t n_gran = (Q + 31) >> 5;
+    const int K = tr.K;
+    for (;;) {
+        const int64_t gran = next_granule(&s_next, lane);
+        if (gran >= n_gran) break;
+        const int64_t ray = gran * 32 + lane;
+        if (ray >= Q) continue;
+        Ray r;
+        src.load(ray, tr, opt, r);
+        ray_setup(r, tr.scaling);
+        int nv = 0, nf = 0, nb = 0;
+        if (r.hit) {
+            float light = 1.f, t = r.tmin;
+            bool stopped = false;
+            while (t < r.tmax && nv < kMaxSteps) {
                 Step s;
                 if (!march_step(tr, top, r, t, opt.step_size, s)) break;
-                const int64_t off = s.leaf.slot * K;
-                const float* __restrict__ rec = tr.data + off;
-                float sigma = __ldg(rec + (K - 1));
-                const float raw_sigma = sigma;
+                float sigma = __ldg(tr.data + s.leaf.slot * K + (K - 1));
                 if (opt.density_softplus) sigma = softplus_m1(sigma);
-                if (sigma > 0.0f) {
-                    const float att = expf(-s.delta_t * sigma * r.delta_scale);
-                    const float weight = light * (1.f - att);
-                    float v[K];
-                    load_record<K, VEC>(rec, v);
-                    float total_color = 0.f;
-#pragma unroll
-                    for (int ch = 0; ch < 3; ++ch) {
-                        float tmp = 0.0f;
-#pragma unroll
-                        for (int i = 0; i < BD; ++i) tmp += basis[i] * v[ch * BD + i];
-                        const float sg = sigmoid_ref(tmp);
-                        const float tmp2 = weight * sg * (1.0 - sg) * gch[ch] * d_rgb_pad;
-#pragma unroll
-                        for (int i = 0; i < BD; ++i) v[ch * BD + i] = basis[i] * tmp2;
-                        total_color += (sg * d_rgb_pad - opt.rgb_padding) * gch[ch];
-                    }
-                    light *= att;
-                    accum -= weight * total_color;
-                    v[K - 1] = s.delta_t * r.delta_scale * (total_color * light - accum) *
-                               (opt.density_softplus ? sigmoid_ref(raw_sigma - 1) : 1);
-                    scatter_record<K, VEC>(grad_data + off, v);
+                ++nv;
+                if (sigma > 0.0f) ++nb;
+                if (!stopped && sigma > opt.sigma_thresh) {
+                    ++nf;
+                    light *= expf(-s.delta_t * r.delta_scale * sigma);
+                    if (light <= opt.stop_thresh) stopped = true;
                 }
                 t = __fadd_rn(t, s.delta_t);
             }
         }
+        if (visits) visits[ray] = nv;
+        if (contrib_fwd) contrib_fwd[ray] = nf;
+        if (contrib_bwd) contrib_bwd[ray] = nb;
     }
 }
 

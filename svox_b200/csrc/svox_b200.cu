@@ -253,6 +253,31 @@ int svoxb_volume_render_image_backward(const svoxb_tree* tree, const svoxb_camer
     return render_dispatch(c, PixelRays{cam->c2w, cam->fx, cam->fy, cam->width, cam->height});
 }
 
+int svoxb_march_stats(const svoxb_tree* tree, const svoxb_rays* rays,
+                      const svoxb_render_options* opt, int32_t* visits, int32_t* contrib_fwd,
+                      int32_t* contrib_bwd, void* stream) {
+    if (!tree || !rays || !opt) return SVOXB_ERR_NULL;
+    if (rays->Q > 0 && (!rays->origins || !rays->dirs || !rays->vdirs)) return SVOXB_ERR_NULL;
+    int st = validate_tree(tree);
+    if (st) return st;
+    if (!(opt->step_size >= 0.f)) return SVOXB_ERR_OPTION;
+    if (rays->Q < 0) return SVOXB_ERR_SHAPE;
+    if (rays->Q == 0) return SVOXB_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    TopScratch scratch;
+    if ((st = scratch.build(tree, 4, s))) return st;
+    const TopTable top{scratch.cells, scratch.level};
+    const bool in_smem = scratch.level > 0;
+    const size_t smem = in_smem ? ((size_t)4 << (3 * scratch.level)) : 0;
+    auto k = march_stats_kernel<256, RayBatch>;
+    unsigned grid = 1;
+    if ((st = persistent_grid(k, 256, smem, (rays->Q + 31) / 32, &grid))) return st;
+    k<<<grid, 256, smem, s>>>(tree_args(tree), RayBatch{rays->origins, rays->dirs, rays->vdirs},
+                             *opt, top, in_smem, visits, contrib_fwd, contrib_bwd, rays->Q);
+    SVOXB_CUDA(cudaGetLastError());
+    return SVOXB_OK;
+}
+
 int svoxb_device_status(int clear, void* stream) {
     int word = 0;
     SVOXB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));

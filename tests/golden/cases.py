@@ -143,6 +143,16 @@ def aniso_rays():
                  grad_out=torch.randn(Q, 3, generator=gen))
 
 
+def aniso_image():
+    """Perspective image of the non-cubic, irregular tree (image kernels' world transform)."""
+    gen = _g(114)
+    tree = _aniso_tree(gen)
+    c2w = W.look_at_cameras(1, gen, 3.0, center=0.0)[0]
+    c2w[:, 3] += torch.tensor([0.1, -0.2, 0.3])
+    return _base(tree, "image", camera=dict(c2w=c2w, width=80, height=60, fx=70.0, fy=75.0),
+                 grad_out=torch.randn(60, 80, 3, generator=gen))
+
+
 def ndc_image():
     """Forward-facing camera rendered through the NDC warp; world box [-1,1]^3."""
     gen = _g(109)
@@ -212,7 +222,7 @@ def query_shell():
 
 CASES = {f.__name__: f for f in [
     c1_rays, shell_sh9_rays, c4_sample_rays, shell_sh16_image, opt_fast, opt_softplus_pad_bg,
-    opt_comp_range, rgba_rays, sh1_rays, sh25_rays, aniso_rays, ndc_image, n3_rays,
+    opt_comp_range, rgba_rays, sh1_rays, sh25_rays, aniso_rays, aniso_image, ndc_image, n3_rays,
     query_c1, query_aniso, query_shell]}
 
 # Cases whose fixtures are cheap enough to check on the CPU in the default test run.
