@@ -159,7 +159,9 @@ const char* svoxb_last_cuda_error(void);
 
 /* Experiment hook (no counterpart in the reference): key 0 = render block
  * size (256 or 1024, 0 = automatic), key 1 = cap on the render jump-table
- * level (-1 = automatic), key 2 = cap on the query jump-table level. */
+ * level (-1 = automatic), key 2 = cap on the query jump-table level, key 3 =
+ * render algorithm (2 = item queue, the default; 0 = warp-cooperative; 1 = one
+ * thread per ray). */
 int svoxb_tune(int key, int value);
 
 /* Library version, "major.minor.patch". */

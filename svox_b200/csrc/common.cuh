@@ -129,6 +129,7 @@ int sm_count();                     // multiprocessors of the current device
     } while (0)
 
 int validate_tree(const svoxb_tree* t);
+int keep_pool_cached();  // stream-ordered pool keeps freed scratch for the next call
 
 // Scratch jump table of one call: chosen level, device buffer from the
 // stream-ordered pool (released by the destructor on the same stream).
@@ -145,6 +146,7 @@ struct Tuning {
     int render_block = 0;     // 0 = automatic
     int render_top_level = -1;  // -1 = automatic
     int query_top_level = -1;
+    int render_algo = 2;        // 2 = item queue, 0 = warp-cooperative, 1 = one thread per ray
 };
 extern Tuning g_tuning;
 

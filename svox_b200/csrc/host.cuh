@@ -62,10 +62,28 @@ static int auto_top_level(int64_t M, int max_level) {
     return L;
 }
 
+// Scratch buffers come from the device's stream-ordered pool.  By default that
+// pool hands its memory back to the driver at every synchronisation, which
+// makes the next call pay for a fresh allocation; keep it cached instead.
+int keep_pool_cached() {
+    static bool done[64] = {false};
+    int dev = 0;
+    SVOXB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || done[dev]) return SVOXB_OK;
+    cudaMemPool_t pool;
+    SVOXB_CUDA(cudaDeviceGetDefaultMemPool(&pool, dev));
+    unsigned long long keep = ~0ull;
+    SVOXB_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+    done[dev] = true;
+    return SVOXB_OK;
+}
+
 int TopScratch::build(const svoxb_tree* t, int max_level, cudaStream_t s) {
     stream = s;
     level = (t->N == 2) ? auto_top_level(t->M, max_level) : 0;
     if (level == 0) return SVOXB_OK;
+    int st = keep_pool_cached();
+    if (st) return st;
     const size_t n = (size_t)1 << (3 * level);
     SVOXB_CUDA(cudaMallocAsync((void**)&cells, n * sizeof(int32_t), s));
     build_top_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(t->child, t->M, level, cells);

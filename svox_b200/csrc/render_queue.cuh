@@ -1,0 +1,579 @@
+// Queue-based warp-cooperative volume rendering for octrees (N = 2) with SH
+// colour in three channels (record K = 3 * basis_dim + 1): forward, and
+// backward in one or two marches.
+//
+// The path is bound by memory LATENCY (dependent loads of the descent, then
+// the record fetch), not by arithmetic, so the kernel is organised to expose
+// at most one L2 round trip per loop iteration and no HBM round trip at all:
+//
+//   G step  one lane = one ray.  Every iteration consumes ONE child entry that
+//           was requested during the previous iteration (software-pipelined):
+//           an inner node moves the lane's cursor one level down; a leaf is
+//           sampled (step length, density, transmittance, weight), the ray
+//           advances, and the cursor of the next sample restarts from the
+//           lowest common ancestor kept in a per-lane path cache (or from the
+//           shared-memory jump table).  Lanes never wait for another lane's
+//           longer descent.  The descent reads an ANNOTATED copy of the child
+//           array whose leaf entries carry the density of leaves that pass
+//           the density test (annotate_sigma_kernel, built per call), so the
+//           march itself runs out of L2-resident data and empty leaves never
+//           touch HBM.  A contributing sample is pushed as an ITEM (leaf slot,
+//           weight, ...) into the warp's queue in shared memory.
+//   S step  one lane = one item.  When 32 items are queued their records are
+//           requested with cp.async (coalesced 16-byte pieces, global ->
+//           shared staging rows) and the warp goes on marching; the batch is
+//           evaluated when the next one is full, by which time the data has
+//           arrived.  Lane i evaluates item i (SH dot products, sigmoids) with
+//           the owner ray's basis; then every owner folds the results of its
+//           own items into its ray state in march order, which keeps the
+//           reference's order of accumulation (svox/csrc/rt_kernel.cu:282-295,
+//           379-411, 442-471).  In the backward pass lane i forms the gradient
+//           of record i in its staging row and groups of lanes flush the rows
+//           with red.global.add.v4.f32, 16 bytes per lane.
+//
+// Lanes whose ray has ended refill from a block-wide ticket counter.  All
+// control flow around warp-level primitives is driven by votes.
+#pragma once
+
+#include "render.cuh"
+#include "render_coop.cuh"
+
+namespace svoxb {
+
+#ifdef SVOXB_PROFILE
+__device__ unsigned long long g_prof[16];
+// Per-warp cycle accounting of the loop phases (debug builds only).
+#define PROF_T0() unsigned long long prof_acc[16] = {0}; long long prof_t = clock64()
+#define PROF_ADD(i) do { long long n_ = clock64(); prof_acc[i] += (unsigned long long)(n_ - prof_t); prof_t = n_; } while (0)
+#define PROF_CNT(i, v) do { prof_acc[i] += (unsigned long long)(v); } while (0)
+#define PROF_END() do { if (lane == 0) { for (int i_ = 0; i_ < 16; ++i_) atomicAdd(&g_prof[i_], prof_acc[i_]); } } while (0)
+#else
+#define PROF_T0()
+#define PROF_ADD(i)
+#define PROF_CNT(i, v)
+#define PROF_END()
+#endif
+
+constexpr int kCoordBits = 24;  // integer coordinates: floor(x * 2^24), exact for float x < 1
+constexpr int kPathLevels = 6;  // cached ancestors below the jump-table level
+
+// Annotated child entry: > 0 link; 0 leaf failing the density test; < 0 leaf
+// passing it, with the density's float bits in the low 31 bits when the
+// density is a non-negative float that needs no softplus, else kOccupied
+// (the reader then fetches the density from the record).
+__global__ void annotate_sigma_kernel(const int32_t* __restrict__ child,
+                                      const float* __restrict__ data, int K, int64_t n_slots,
+                                      float thresh, int softplus, int32_t* __restrict__ out) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_slots) return;
+    int32_t c = child[i];
+    if (c == 0) {
+        const float raw = __ldg(data + i * K + (K - 1));
+        const float sigma = softplus ? softplus_m1(raw) : raw;
+        if (sigma > thresh)
+            c = (!softplus && raw >= 0.f) ? (int32_t)(0x80000000u | __float_as_uint(raw))
+                                          : kOccupied;
+    }
+    out[i] = c;
+}
+
+// L2 residency hints.  The annotated child array (tens of MB, re-read hundreds
+// of times per launch) must stay in L2 while the leaf records and gradients
+// (GBs, touched a few times each) stream through it; without hints the stream
+// evicts a third of the child entries and every descent step waits on HBM.
+__device__ __forceinline__ uint64_t l2_policy_keep() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_stream() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ int32_t ld_keep(const int32_t* a, uint64_t pol) {
+    int32_t v;
+    asm volatile("ld.global.nc.L2::cache_hint.s32 %0, [%1], %2;" : "=r"(v) : "l"(a), "l"(pol));
+    return v;
+}
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, uint64_t pol) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(s),
+                 "l"(gmem), "l"(pol)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem, uint64_t pol) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global.L2::cache_hint [%0], [%1], 4, %2;" ::"r"(s),
+                 "l"(gmem), "l"(pol)
+                 : "memory");
+}
+__device__ __forceinline__ void red_add_v4_hint(float* addr, float a, float b, float c, float d,
+                                                uint64_t pol) {
+    asm volatile("red.global.add.L2::cache_hint.v4.f32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(addr),
+                 "f"(a), "f"(b), "f"(c), "f"(d), "l"(pol)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
+// Shared memory of one warp.
+template <int K, bool BWD>
+struct alignas(16) WarpQueue {
+    using Shape = CoopShape<K>;
+    static constexpr int CAP = 96;  // a batch in flight (32) + items being collected (< 64)
+    static constexpr int BD = (K - 1) / 3;
+    static constexpr int RAYW = (BD + 3) | 1;  // basis + upstream gradient; odd stride: no bank conflicts
+    uint32_t slot[CAP];
+    float w[CAP];                   // weight T * (1 - att)
+    float T[BWD ? CAP : 4];         // transmittance after the sample
+    float dd[BWD ? CAP : 4];        // delta_t * delta_scale
+    unsigned char owner[CAP];       // bits 0-4 owner lane, bit 7: item of an accumulation march
+    float res[32][4];               // per item: forward c0,c1,c2; backward tc, d(sigma)
+    float rayv[32][RAYW];           // per ray: SH basis [0, BD), upstream gradient [BD, BD+3)
+    alignas(16) float rows[32 * Shape::STRIDE + 4];  // staging rows (cp.async targets)
+};
+
+enum { kNeedRay = 0, kMarching = 1, kDraining = 2, kExhausted = 3 };
+
+template <int BD, int BLOCK, int MODE, class Source>
+__global__ void __launch_bounds__(BLOCK)
+render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable topg,
+                    int top_bytes, int64_t Q, float* __restrict__ out,
+                    const float* __restrict__ grad_out, const float* __restrict__ fwd_out,
+                    float* __restrict__ grad_data) {
+    constexpr int K = 3 * BD + 1;
+    constexpr bool BWD = MODE == kModeBackward;
+    using WQ = WarpQueue<K, BWD>;
+    using Shape = CoopShape<K>;
+    extern __shared__ __align__(16) unsigned char s_raw[];
+    __shared__ unsigned s_next;
+    if (threadIdx.x == 0) s_next = 0;
+    const TopTable top = stage_top(topg, reinterpret_cast<int32_t*>(s_raw), top_bytes > 0);
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31;
+    WQ& q = *reinterpret_cast<WQ*>(s_raw + top_bytes + (size_t)(threadIdx.x >> 5) * sizeof(WQ));
+    const float d_rgb_pad = 1 + 2 * opt.rgb_padding;
+    const bool single = BWD && fwd_out != nullptr;
+    const float bg = opt.background_brightness;
+    const int sub = lane / Shape::GROUP, wj = lane % Shape::GROUP;
+    const int32_t* __restrict__ child = tr.child;
+    const int M = (int)tr.M;
+    const int base = top.level;  // level of the jump table (0: none)
+    const float big = (float)(1 << kCoordBits);
+    const uint64_t pol_keep = l2_policy_keep(), pol_stream = l2_policy_stream();
+
+    // ---- per-lane ray state -------------------------------------------------
+    Ray r;
+    r.hit = false;
+    int64_t ray = 0;
+    int state = kNeedRay;
+    float t = 0.f, light = 1.f;
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f;  // forward: colour sums
+    float accum = 0.f;                    // backward
+    bool stopped = false;
+    int phase = 1;  // backward: 0 = accumulation march (reference PASS 1), 1 = scatter march
+    int it = 0;
+    // cursor of the descent in progress
+    int node = 0, lvl = 0, ix = 0, iy = 0, iz = 0;
+    float px = 0.f, py = 0.f, pz = 0.f;
+    int32_t e_pre = 0;        // child entry at the cursor, requested one iteration ahead
+    int path[kPathLevels];    // path[j]: node at level base + 1 + j on the way to the last leaf
+#pragma unroll
+    for (int j = 0; j < kPathLevels; ++j) path[j] = 0;
+    unsigned mine_lo = 0u;            // my items among queue positions [0, 32)
+    unsigned long long mine_hi = 0ull;  // ... among [32, 96)
+    int qn = 0;                       // queued items (warp-uniform)
+    bool inflight = false;            // records of items [0, 32) have been requested
+
+    // Places the cursor for the sample at parameter t, reusing the deepest cached
+    // ancestor shared with the previous sample (valid down to level `deepest`),
+    // and requests the child entry there.
+    auto place_cursor = [&](int deepest) {
+        px = clamp01(mad_site<FC_POS>(t, r.dx, r.ox));
+        py = clamp01(mad_site<FC_POS>(t, r.dy, r.oy));
+        pz = clamp01(mad_site<FC_POS>(t, r.dz, r.oz));
+        const int nx = (int)(px * big), ny = (int)(py * big), nz = (int)(pz * big);
+        const int diff = (nx ^ ix) | (ny ^ iy) | (nz ^ iz);
+        int common = __clz(diff) - (32 - kCoordBits);  // leading coordinate bits in common
+        if (common > deepest) common = deepest;
+        if (common > base + kPathLevels) common = base + kPathLevels;
+        ix = nx; iy = ny; iz = nz;
+        if (base > 0 && common > base) {
+            const int j = common - base - 1;
+            int n = path[0];
+#pragma unroll
+            for (int jj = 1; jj < kPathLevels; ++jj) n = (j == jj) ? path[jj] : n;
+            node = n;
+            lvl = common;
+        } else {
+            node = 0;
+            lvl = 0;
+            if (base > 0) {
+                const int sh = kCoordBits - base;
+                const int32_t e = top.cells[((((ix >> sh) << base) + (iy >> sh)) << base) + (iz >> sh)];
+                if (e >= 0) { node = e; lvl = base; }
+            }
+        }
+        const int b = kCoordBits - 1 - lvl;
+        const int cell = (((ix >> b) & 1) << 2) | (((iy >> b) & 1) << 1) | ((iz >> b) & 1);
+        e_pre = ld_keep(child + ((uint32_t)node * 8u + (uint32_t)cell), pol_keep);
+    };
+
+    // Evaluates the first nb queued items, whose records are in the staging rows.
+    auto evaluate = [&](int nb) {
+        float sg[3] = {0.f, 0.f, 0.f};
+        float raw_sigma = 0.f;
+        int own = lane;
+        bool acc_item = false;
+        if (lane < nb) {
+            own = q.owner[lane] & 31;
+            acc_item = (q.owner[lane] & 0x80) != 0;
+            const float* row = q.rows + lane * Shape::STRIDE;
+            float bs[BD];
+#pragma unroll
+            for (int i = 0; i < BD; ++i) bs[i] = q.rayv[own][i];
+            float v[K];
+            if (Shape::VEC) {
+#pragma unroll
+                for (int w = 0; w < K / 4; ++w) {
+                    const float4 x = reinterpret_cast<const float4*>(row)[w];
+                    v[4 * w] = x.x; v[4 * w + 1] = x.y; v[4 * w + 2] = x.z; v[4 * w + 3] = x.w;
+                }
+            } else {
+#pragma unroll
+                for (int w = 0; w < K; ++w) v[w] = row[w];
+            }
+            raw_sigma = v[K - 1];
+            float col[3];
+#pragma unroll
+            for (int ch = 0; ch < 3; ++ch) {
+                float tmp = 0.0f;
+#pragma unroll
+                for (int i = 0; i < BD; ++i) tmp += bs[i] * v[ch * BD + i];
+                sg[ch] = sigmoid_ref(tmp);
+                col[ch] = sg[ch] * d_rgb_pad - opt.rgb_padding;
+            }
+            if (!BWD) {
+                q.res[lane][0] = col[0]; q.res[lane][1] = col[1]; q.res[lane][2] = col[2];
+            } else {
+                float total_color = 0.f;
+#pragma unroll
+                for (int ch = 0; ch < 3; ++ch) total_color += col[ch] * q.rayv[own][BD + ch];
+                q.res[lane][0] = total_color;
+            }
+        }
+        __syncwarp();
+        // every owner folds in its items, in march order
+        {
+            unsigned m = mine_lo;
+            while (m != 0u) {
+                const int k = __ffs(m) - 1;
+                m &= m - 1u;
+                const float wk = q.w[k];
+                if (!BWD) {
+                    a0 += wk * q.res[k][0];
+                    a1 += wk * q.res[k][1];
+                    a2 += wk * q.res[k][2];
+                } else {
+                    const float tc = q.res[k][0];
+                    if (q.owner[k] & 0x80) {
+                        accum += wk * tc;
+                    } else {
+                        accum -= wk * tc;
+                        q.res[k][1] = q.dd[k] * (tc * q.T[k] - accum);
+                    }
+                }
+            }
+        }
+        if (BWD) {
+            __syncwarp();
+            // lane i forms the gradient of record i in its staging row
+            if (lane < nb && !acc_item) {
+                float* row = q.rows + lane * Shape::STRIDE;
+                const float wk = q.w[lane];
+                float v[K];
+#pragma unroll
+                for (int ch = 0; ch < 3; ++ch) {
+                    const float tmp2 = wk * sg[ch] * (1.0 - sg[ch]) * q.rayv[own][BD + ch] * d_rgb_pad;
+#pragma unroll
+                    for (int i = 0; i < BD; ++i) v[ch * BD + i] = q.rayv[own][i] * tmp2;
+                }
+                v[K - 1] = q.res[lane][1] * (opt.density_softplus ? sigmoid_ref(raw_sigma - 1) : 1);
+                if (Shape::VEC) {
+#pragma unroll
+                    for (int w = 0; w < K / 4; ++w)
+                        reinterpret_cast<float4*>(row)[w] =
+                            make_float4(v[4 * w], v[4 * w + 1], v[4 * w + 2], v[4 * w + 3]);
+                } else {
+#pragma unroll
+                    for (int w = 0; w < K; ++w) row[w] = v[w];
+                }
+            }
+            __syncwarp();
+            // groups of lanes flush the gradient rows
+#pragma unroll
+            for (int p = 0; p < 32 / Shape::IPP; ++p) {
+                const int k = p * Shape::IPP + sub;
+                if (k < nb && !(q.owner[k] & 0x80)) {
+                    float* __restrict__ g = grad_data + (size_t)q.slot[k] * K;
+                    const float* row = q.rows + k * Shape::STRIDE;
+#pragma unroll
+                    for (int w = 0; w < Shape::WPL; ++w) {
+                        const int word = wj + w * Shape::GROUP;
+                        if (word < Shape::WORDS) {
+                            if (Shape::VEC) {
+                                const float4 x = reinterpret_cast<const float4*>(row)[word];
+                                red_add_v4_hint(g + 4 * word, x.x, x.y, x.z, x.w, pol_stream);
+                            } else {
+                                atomicAdd(g + word, row[word]);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        // drop the first 32 positions: entries 32.. move to the front
+        const int rem = qn > 32 ? qn - 32 : 0;
+        for (int b0 = 0; b0 < rem; b0 += 32) {
+            const int i = b0 + lane;
+            uint32_t s_ = 0; float w_ = 0.f, T_ = 0.f, d_ = 0.f; unsigned char o_ = 0;
+            if (i < rem) {
+                s_ = q.slot[32 + i]; w_ = q.w[32 + i]; o_ = q.owner[32 + i];
+                if (BWD) { T_ = q.T[32 + i]; d_ = q.dd[32 + i]; }
+            }
+            __syncwarp();
+            if (i < rem) {
+                q.slot[i] = s_; q.w[i] = w_; q.owner[i] = o_;
+                if (BWD) { q.T[i] = T_; q.dd[i] = d_; }
+            }
+            __syncwarp();
+        }
+        qn = rem;
+        mine_lo = (unsigned)(mine_hi & 0xffffffffull);
+        mine_hi >>= 32;
+    };
+
+    // Requests the records of the first nb queued items into the staging rows.
+    auto request = [&](int nb) {
+#pragma unroll
+        for (int p = 0; p < 32 / Shape::IPP; ++p) {
+            const int k = p * Shape::IPP + sub;
+            if (k < nb) {
+                const float* __restrict__ rec = tr.data + (size_t)q.slot[k] * K;
+                float* row = q.rows + k * Shape::STRIDE;
+#pragma unroll
+                for (int w = 0; w < Shape::WPL; ++w) {
+                    const int word = wj + w * Shape::GROUP;
+                    if (word < Shape::WORDS) {
+                        if (Shape::VEC) cp_async16(row + 4 * word, rec + 4 * word, pol_stream);
+                        else cp_async4(row + word, rec + word, pol_stream);
+                    }
+                }
+            }
+        }
+    };
+
+    PROF_T0();
+    for (;;) {
+        // ---- finish rays whose items are all folded in, then refill ------------------
+        if (state == kDraining && mine_lo == 0u && mine_hi == 0ull) {
+            if (!BWD) {
+                if (stopped) {
+                    const float scale = 1.0 / (1.0 - light);
+                    out[3 * ray + 0] = a0 * scale;
+                    out[3 * ray + 1] = a1 * scale;
+                    out[3 * ray + 2] = a2 * scale;
+                } else {
+                    out[3 * ray + 0] = a0 + light * bg;
+                    out[3 * ray + 1] = a1 + light * bg;
+                    out[3 * ray + 2] = a2 + light * bg;
+                }
+                state = kNeedRay;
+            } else if (phase == 0) {
+                // tail of the reference's PASS 1 (rt_kernel.cu:415-418), then march again
+                const float total_grad = q.rayv[lane][BD] + q.rayv[lane][BD + 1] + q.rayv[lane][BD + 2];
+                accum += light * bg * total_grad;
+                phase = 1;
+                t = r.tmin; light = 1.f; it = 0;
+                state = kMarching;
+                place_cursor(0);
+            } else {
+                state = kNeedRay;
+            }
+        }
+        if (__any_sync(0xffffffffu, state == kNeedRay)) {
+            if (state == kNeedRay) {
+                const unsigned ticket = atomicAdd(&s_next, 1u);
+                const int64_t gran = (int64_t)blockIdx.x + (int64_t)gridDim.x * (ticket >> 5);
+                ray = gran * 32 + (ticket & 31);
+                if (ray >= Q) {
+                    if (gran * 32 >= Q) state = kExhausted;
+                } else {
+                    src.load(ray, tr, opt, r);
+                    ray_setup(r, tr.scaling);
+                    if (!r.hit || !(r.tmin < r.tmax)) {
+                        if (!BWD) { out[3 * ray + 0] = bg; out[3 * ray + 1] = bg; out[3 * ray + 2] = bg; }
+                    } else {
+                        state = kMarching;
+                        t = r.tmin; light = 1.f; it = 0; stopped = false;
+                        float basis[BD];
+                        sh_basis<BD>(r.vdir, basis);
+#pragma unroll
+                        for (int i = 0; i < BD; ++i)
+                            q.rayv[lane][i] = (i < opt.min_comp || i > opt.max_comp) ? 0.f : basis[i];
+                        if (!BWD) {
+                            a0 = a1 = a2 = 0.f;
+                        } else {
+                            const float g0 = __ldg(grad_out + 3 * ray), g1 = __ldg(grad_out + 3 * ray + 1),
+                                        g2 = __ldg(grad_out + 3 * ray + 2);
+                            q.rayv[lane][BD] = g0; q.rayv[lane][BD + 1] = g1; q.rayv[lane][BD + 2] = g2;
+                            if (single) {
+                                accum = __ldg(fwd_out + 3 * ray) * g0;
+                                accum += __ldg(fwd_out + 3 * ray + 1) * g1;
+                                accum += __ldg(fwd_out + 3 * ray + 2) * g2;
+                                phase = 1;
+                            } else {
+                                accum = 0.f;
+                                phase = 0;
+                            }
+                        }
+                        place_cursor(0);
+                    }
+                }
+            }
+            __syncwarp();
+        }
+        const bool draining = __any_sync(0xffffffffu, state == kDraining);
+        if (!__any_sync(0xffffffffu, state == kMarching) && !draining) {
+            if (__all_sync(0xffffffffu, state == kExhausted)) break;
+            continue;
+        }
+        PROF_ADD(0);
+        PROF_CNT(8, 1);
+
+        // ---- G step: consume one child entry per lane ------------------------------------
+        bool item = false;
+        uint32_t slot = 0;
+        float weight = 0.f, dd = 0.f;
+        if (state == kMarching) {
+            const int32_t e = e_pre;
+            const int b = kCoordBits - 1 - lvl;
+            const int cell = (((ix >> b) & 1) << 2) | (((iy >> b) & 1) << 1) | ((iz >> b) & 1);
+            if (e > 0) {
+                // inner node: one level down
+                node += e;
+                ++lvl;
+                if (node >= M || lvl >= kCoordBits) {
+                    report(SVOXB_ERR_TREE);
+                    state = kDraining;
+                } else {
+                    const int j = lvl - base - 1;
+                    if (base > 0) {
+#pragma unroll
+                        for (int jj = 0; jj < kPathLevels; ++jj)
+                            if (j == jj) path[jj] = node;
+                    }
+                    const int b2 = b - 1;
+                    const int c2 = (((ix >> b2) & 1) << 2) | (((iy >> b2) & 1) << 1) | ((iz >> b2) & 1);
+                    e_pre = ld_keep(child + ((uint32_t)node * 8u + (uint32_t)c2), pol_keep);
+                }
+            } else {
+                // leaf of depth lvl + 1: sample it
+                bool done = false;
+                const int depth = lvl + 1;
+                slot = (uint32_t)node * 8u + (uint32_t)cell;
+                const float cube = __int_as_float((127 + depth) << 23);      // 2^depth
+                const float inv_cube = __int_as_float((127 - depth) << 23);  // 2^-depth
+                const int sh = kCoordBits - depth;
+                const float fx = __fmaf_rn(px, cube, -(float)(ix >> sh));  // exact
+                const float fy = __fmaf_rn(py, cube, -(float)(iy >> sh));
+                const float fz = __fmaf_rn(pz, cube, -(float)(iz >> sh));
+                float smin, smax;
+                dda_unit<FC_DDA_LEAF>(fx, fy, fz, r.ix, r.iy, r.iz, smin, smax);
+                // dividing by 2^depth == multiplying by 2^-depth, exactly
+                const float delta_t =
+                    __fadd_rn(__fmul_rn(__fsub_rn(smax, smin), inv_cube), opt.step_size);
+                if (e < 0) {
+                    float sigma = (e == kOccupied) ? __ldg(tr.data + (size_t)slot * K + (K - 1))
+                                                   : __uint_as_float((uint32_t)e & 0x7fffffffu);
+                    if (opt.density_softplus) sigma = softplus_m1(sigma);
+                    const float att = BWD ? expf(-delta_t * sigma * r.delta_scale)
+                                          : expf(-delta_t * r.delta_scale * sigma);
+                    weight = light * (1.f - att);
+                    light *= att;
+                    dd = delta_t * r.delta_scale;
+                    item = true;
+                    if (!BWD && light <= opt.stop_thresh) {
+                        stopped = true;
+                        done = true;
+                    }
+                }
+                t = __fadd_rn(t, delta_t);
+                if (!(t < r.tmax)) done = true;
+                if (++it > kMaxSteps) {
+                    report(SVOXB_ERR_MARCH);
+                    done = true;
+                }
+                if (done) state = kDraining;
+                else place_cursor(lvl);
+            }
+        }
+        PROF_ADD(1);
+
+        // ---- push items --------------------------------------------------------------
+        const unsigned pushed = __ballot_sync(0xffffffffu, item);
+        if (item) {
+            const int pos = qn + __popc(pushed & ((1u << lane) - 1u));
+            q.slot[pos] = slot;
+            q.w[pos] = weight;
+            if (BWD) { q.T[pos] = light; q.dd[pos] = dd; }
+            q.owner[pos] = (unsigned char)(lane | ((BWD && phase == 0) ? 0x80 : 0));
+            if (pos < 32) mine_lo |= 1u << pos;
+            else mine_hi |= 1ull << (pos - 32);
+        }
+        qn += __popc(pushed);
+        const bool force = qn > 0 && __any_sync(0xffffffffu, state == kDraining);
+        const int collected = qn - (inflight ? 32 : 0);
+        PROF_ADD(2);
+        if (collected < 32 && !force) continue;
+        __syncwarp();
+
+        // ---- S step -------------------------------------------------------------------
+        if (inflight) {
+            cp_async_wait_all();
+            __syncwarp();
+            PROF_ADD(3);
+            PROF_CNT(10, 1);
+            PROF_CNT(11, 32);
+            evaluate(32);
+            inflight = false;
+            PROF_ADD(4);
+        }
+        if (force) {
+            // a finished ray waits for its items: flush everything now
+            while (qn > 0) {
+                const int nb = qn < 32 ? qn : 32;
+                request(nb);
+                cp_async_wait_all();
+                __syncwarp();
+                PROF_ADD(5);
+                PROF_CNT(12, 1);
+                PROF_CNT(13, nb);
+                evaluate(nb);
+                PROF_ADD(6);
+            }
+        } else if (qn >= 32) {
+            request(32);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            inflight = true;
+            PROF_ADD(7);
+        }
+    }
+    PROF_END();
+}
+
+}  // namespace svoxb

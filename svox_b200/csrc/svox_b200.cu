@@ -5,6 +5,8 @@
 #include "host.cuh"
 #include "query.cuh"
 #include "render.cuh"
+#include "render_coop.cuh"
+#include "render_queue.cuh"
 
 namespace svoxb {
 
@@ -87,6 +89,128 @@ static int launch_sh(const RenderCall& c, const Source& src, const TopTable& top
     return SVOXB_OK;
 }
 
+// Scratch copy of the child array with the density test folded into the leaf
+// entries (render_coop.cuh); lives until the stream reaches the free.
+struct AnnotScratch {
+    int32_t* child = nullptr;
+    cudaStream_t stream = nullptr;
+    int build(const svoxb_tree* t, float thresh, int softplus, cudaStream_t s) {
+        stream = s;
+        const int64_t n = t->M * 8;
+        int st = keep_pool_cached();
+        if (st) return st;
+        SVOXB_CUDA(cudaMallocAsync((void**)&child, (size_t)n * sizeof(int32_t), s));
+        annotate_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(t->child, t->data, t->K, n,
+                                                                   thresh, softplus, child);
+        SVOXB_CUDA(cudaGetLastError());
+        return SVOXB_OK;
+    }
+    ~AnnotScratch() { if (child) cudaFreeAsync(child, stream); }
+};
+
+template <int BD, int BLOCK, class Source>
+static int launch_coop(const RenderCall& c, const Source& src, const TopTable& top, bool in_smem,
+                       size_t top_bytes) {
+    constexpr int K = 3 * BD + 1;
+    using Shape = CoopShape<K>;
+    AnnotScratch annot;
+    int st = annot.build(c.tree, c.backward ? 0.f : c.opt.sigma_thresh, c.opt.density_softplus,
+                         c.stream);
+    if (st) return st;
+    TreeArgs tr = tree_args(c.tree);
+    tr.child = annot.child;
+    const size_t smem = top_bytes + (size_t)(BLOCK / 32) * (Shape::STAGE_FLOATS * 4 + 32);
+    const int64_t n_gran = (c.Q + 31) / 32;
+    unsigned grid = 1;
+    if (!c.backward) {
+        auto k = render_coop_kernel<BD, BLOCK, kModeForward, Source>;
+        if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
+        k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, in_smem, (int)top_bytes, c.Q,
+                                          c.out, nullptr, nullptr, nullptr);
+    } else {
+        const bool single = c.fwd_out != nullptr && c.opt.sigma_thresh == 0.f &&
+                            c.opt.stop_thresh == 0.f;
+        auto k = render_coop_kernel<BD, BLOCK, kModeBackward, Source>;
+        if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
+        k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, in_smem, (int)top_bytes, c.Q,
+                                          nullptr, c.grad_out, single ? c.fwd_out : nullptr,
+                                          c.grad_data);
+    }
+    SVOXB_CUDA(cudaGetLastError());
+    return SVOXB_OK;
+}
+
+// Queue kernels (render_queue.cuh).  The block size is the largest whose
+// per-warp queues fit in shared memory next to the jump table.
+constexpr size_t kMaxSmem = 227 * 1024;
+
+template <int BD, int BLOCK, class Source>
+static int launch_queue_block(const RenderCall& c, const Source& src, const TreeArgs& tr,
+                              const TopTable& top, size_t top_bytes) {
+    constexpr int K = 3 * BD + 1;
+    const int64_t n_gran = (c.Q + 31) / 32;
+    unsigned grid = 1;
+    int st;
+    if (!c.backward) {
+        const size_t smem = top_bytes + (size_t)(BLOCK / 32) * sizeof(WarpQueue<K, false>);
+        auto k = render_queue_kernel<BD, BLOCK, kModeForward, Source>;
+        if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
+        k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, (int)top_bytes, c.Q, c.out,
+                                          nullptr, nullptr, nullptr);
+    } else {
+        const size_t smem = top_bytes + (size_t)(BLOCK / 32) * sizeof(WarpQueue<K, true>);
+        const bool single = c.fwd_out != nullptr && c.opt.sigma_thresh == 0.f &&
+                            c.opt.stop_thresh == 0.f;
+        auto k = render_queue_kernel<BD, BLOCK, kModeBackward, Source>;
+        if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
+        k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, (int)top_bytes, c.Q, nullptr,
+                                          c.grad_out, single ? c.fwd_out : nullptr, c.grad_data);
+    }
+    SVOXB_CUDA(cudaGetLastError());
+    return SVOXB_OK;
+}
+
+struct AnnotSigmaScratch {
+    int32_t* child = nullptr;
+    cudaStream_t stream = nullptr;
+    int build(const svoxb_tree* t, float thresh, int softplus, cudaStream_t s) {
+        stream = s;
+        const int64_t n = t->M * 8;
+        int st = keep_pool_cached();
+        if (st) return st;
+        SVOXB_CUDA(cudaMallocAsync((void**)&child, (size_t)n * sizeof(int32_t), s));
+        annotate_sigma_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(
+            t->child, t->data, t->K, n, thresh, softplus, child);
+        SVOXB_CUDA(cudaGetLastError());
+        return SVOXB_OK;
+    }
+    ~AnnotSigmaScratch() { if (child) cudaFreeAsync(child, stream); }
+};
+
+template <int BD, class Source>
+static int launch_queue(const RenderCall& c, const Source& src, const TopTable& top) {
+    constexpr int K = 3 * BD + 1;
+    AnnotSigmaScratch annot;
+    int st = annot.build(c.tree, c.backward ? 0.f : c.opt.sigma_thresh, c.opt.density_softplus,
+                         c.stream);
+    if (st) return st;
+    TreeArgs tr = tree_args(c.tree);
+    tr.child = annot.child;
+    // the jump table is staged in shared memory up to level 4 (16 KB)
+    const size_t top_bytes = (top.level > 0 && top.level <= 4) ? ((size_t)4 << (3 * top.level)) : 0;
+    const size_t per_warp = c.backward ? sizeof(WarpQueue<K, true>) : sizeof(WarpQueue<K, false>);
+    int want = g_tuning.render_block > 0 ? g_tuning.render_block : 768;
+    while (want > 256 && top_bytes + (size_t)(want / 32) * per_warp + 64 > kMaxSmem) want -= 128;
+    if constexpr (BD <= 9) {
+        if (want >= 1024) return launch_queue_block<BD, 1024>(c, src, tr, top, top_bytes);
+        if (want >= 768) return launch_queue_block<BD, 768>(c, src, tr, top, top_bytes);
+    }
+    if constexpr (BD <= 16) {
+        if (want >= 512) return launch_queue_block<BD, 512>(c, src, tr, top, top_bytes);
+    }
+    return launch_queue_block<BD, 256>(c, src, tr, top, top_bytes);
+}
+
 template <int BLOCK, class Source>
 static int launch_generic(const RenderCall& c, const Source& src, const TopTable& top,
                           bool in_smem, size_t smem) {
@@ -119,6 +243,28 @@ static int dispatch_layout(const RenderCall& c, const Source& src, const TopTabl
     const bool aligned = ((uintptr_t)t->data % 16 == 0) &&
                          (!c.backward || (uintptr_t)c.grad_data % 16 == 0);
     const bool vec = aligned && (t->K % 4 == 0);
+    // Warp-cooperative kernels: octrees whose records allow the chosen word
+    // size (any K with 32-bit words; 16-byte aligned buffers for K % 4 == 0).
+    if (g_tuning.render_algo == 2 && t->N == 2 && (aligned || t->K % 4 != 0) &&
+        t->M < (1LL << 28)) {
+        switch (c.opt.basis_dim) {
+            case 1: return launch_queue<1>(c, src, top);
+            case 4: return launch_queue<4>(c, src, top);
+            case 9: return launch_queue<9>(c, src, top);
+            case 16: return launch_queue<16>(c, src, top);
+            case 25: return launch_queue<25>(c, src, top);
+        }
+    }
+    if (g_tuning.render_algo == 0 && t->N == 2 && (aligned || t->K % 4 != 0) &&
+        t->M * 8 < 0xffffffffLL) {
+        switch (c.opt.basis_dim) {
+            case 1: return launch_coop<1, BLOCK>(c, src, top, in_smem, smem);
+            case 4: return launch_coop<4, BLOCK>(c, src, top, in_smem, smem);
+            case 9: return launch_coop<9, BLOCK>(c, src, top, in_smem, smem);
+            case 16: return launch_coop<16, BLOCK>(c, src, top, in_smem, smem);
+            case 25: return launch_coop<25, BLOCK>(c, src, top, in_smem, smem);
+        }
+    }
     switch (c.opt.basis_dim) {
         case 1:
             return vec ? launch_sh<1, true, BLOCK>(c, src, top, in_smem, smem)
@@ -157,6 +303,7 @@ static int render_dispatch(const RenderCall& c, const Source& src) {
     int block = g_tuning.render_block;
     if (block == 0) block = (smem > 64 * 1024) ? 1024 : 256;
     if (block >= 1024) return dispatch_layout<1024>(c, src, top, in_smem, smem);
+    if (block >= 512) return dispatch_layout<512>(c, src, top, in_smem, smem);
     return dispatch_layout<256>(c, src, top, in_smem, smem);
 }
 
@@ -308,13 +455,27 @@ const char* svoxb_last_cuda_error(void) { return t_cuda_error; }
 
 const char* svoxb_version(void) { return "0.1.0"; }
 
+#ifdef SVOXB_PROFILE
+int svoxb_prof_read(unsigned long long* out16, int clear) {
+    SVOXB_CUDA(cudaDeviceSynchronize());
+    SVOXB_CUDA(cudaMemcpyFromSymbol(out16, g_prof, 16 * sizeof(unsigned long long)));
+    if (clear) {
+        unsigned long long z[16] = {0};
+        SVOXB_CUDA(cudaMemcpyToSymbol(g_prof, z, sizeof z));
+    }
+    return 0;
+}
+#endif
+
 // Tuning hook for experiments: key 0 = render block size (256 | 1024, 0 auto),
-// 1 = render jump-table level cap (-1 auto), 2 = query jump-table level cap.
+// 1 = render jump-table level cap (-1 auto), 2 = query jump-table level cap,
+// 3 = render algorithm (2 item queue, 0 warp-cooperative, 1 one thread per ray).
 int svoxb_tune(int key, int value) {
     switch (key) {
         case 0: g_tuning.render_block = value; return SVOXB_OK;
         case 1: g_tuning.render_top_level = value; return SVOXB_OK;
         case 2: g_tuning.query_top_level = value; return SVOXB_OK;
+        case 3: g_tuning.render_algo = value; return SVOXB_OK;
     }
     return SVOXB_ERR_OPTION;
 }
