@@ -168,7 +168,7 @@ def run_reference(a):
 def run_b200(a):
     import torch.distributed as dist
     import svox_b200
-    from svox_b200 import csrc, workloads as W
+    from svox_b200 import csrc, distributed as D, workloads as W
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -183,7 +183,7 @@ def run_b200(a):
     tree_cpu, rays_cpu, targets_cpu = W.config4(Q=a.rays, init_refine=a.init_refine,
                                                 extra_levels=a.extra_levels)
     Q = a.rays
-    lo, hi = rank * Q // world, (rank + 1) * Q // world
+    lo, hi = D.shard_bounds(Q, rank, world)
     tree = tree_cpu.to(dev)
     rays_h = [t[lo:hi].contiguous().pin_memory() for t in rays_cpu]
     tg_h = targets_cpu[lo:hi].contiguous().pin_memory()
@@ -197,8 +197,7 @@ def run_b200(a):
         out = renderer(r)
         loss = ((out - tg) ** 2).sum() / denom      # this rank's share of the global MSE
         loss.backward()
-        if world > 1:
-            dist.all_reduce(tree.data.grad)
+        D.allreduce_grad(tree)
         return loss
 
     def e2e_step():
@@ -284,8 +283,8 @@ def run_b200(a):
                           "achieved": (fwd_bytes + bwd_bytes) / ms_step / 1e6,
                           "frac": (fwd_bytes + bwd_bytes) / ms_step / 1e6 / peak},
         "e2e": e2e,
-        # per step: jump-table build + render kernel, forward and backward
-        "gpu_launches": 4 * a.steps,
+        # per step, forward and backward each: jump-table build, annotation pass, render kernel
+        "gpu_launches": 6 * a.steps,
         "clocks": clocks,
     }
     if rank == 0 and world == 1 and not a.no_cpu_baseline:

@@ -1,0 +1,73 @@
+"""Multi-GPU use of the render path: rays are sharded, the tree is replicated.
+
+Rays are independent given a read-only tree, so each rank renders a
+contiguous slice of the batch with no communication; the only exchange is one
+sum all-reduce of the dense ``tree.data.grad`` after the backward pass.  One
+process per GPU (``torchrun``); works with any ``torch.distributed`` backend
+(NCCL on GPUs, gloo in the CPU tests).
+"""
+import torch
+import torch.distributed as dist
+
+from .render import Rays
+
+__all__ = ["shard_bounds", "shard_rays", "shard_rows", "allreduce_grad", "broadcast_tree",
+           "gather_rows"]
+
+
+def _rank_world(rank, world):
+    if rank is None or world is None:
+        if dist.is_available() and dist.is_initialized():
+            return dist.get_rank(), dist.get_world_size()
+        return 0, 1
+    return rank, world
+
+
+def shard_bounds(n, rank=None, world=None):
+    """[lo, hi) of this rank's contiguous slice of ``n`` items (sizes differ by at most 1)."""
+    rank, world = _rank_world(rank, world)
+    return rank * n // world, (rank + 1) * n // world
+
+
+def shard_rows(t, rank=None, world=None):
+    lo, hi = shard_bounds(t.shape[0], rank, world)
+    return t[lo:hi].contiguous()
+
+
+def shard_rays(rays, rank=None, world=None):
+    """This rank's slice of a ``Rays`` batch."""
+    return Rays(*[shard_rows(t, rank, world) for t in rays])
+
+
+def allreduce_grad(tree, group=None, async_op=False):
+    """Sum ``tree.data.grad`` over all ranks (the one collective of a training step).
+
+    A rank whose rays all missed the tree has no gradient yet: it contributes zeros.
+    """
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return None
+    if tree.data.grad is None:
+        tree.data.grad = torch.zeros_like(tree.data)
+    return dist.all_reduce(tree.data.grad, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
+
+
+def broadcast_tree(tree, src=0, group=None):
+    """Replicate rank ``src``'s tree tensors (same shapes everywhere) to all ranks."""
+    for t in (tree.data.data, tree.child, tree.parent_depth, tree.invradius, tree.offset,
+              tree._n_internal, tree._n_free):
+        dist.broadcast(t, src=src, group=group)
+    tree._invalidate()
+
+
+def gather_rows(local, n_total, group=None):
+    """Reassemble per-rank row slices (as cut by ``shard_rows``) into the full tensor."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return local
+    world = dist.get_world_size(group)
+    parts = []
+    for r in range(world):
+        lo, hi = shard_bounds(n_total, r, world)
+        parts.append(torch.empty((hi - lo, *local.shape[1:]), dtype=local.dtype,
+                                 device=local.device))
+    dist.all_gather(parts, local.contiguous(), group=group)
+    return torch.cat(parts, dim=0)
