@@ -132,6 +132,29 @@ int svoxb_volume_render_image_backward(const svoxb_tree* tree, const svoxb_camer
                                        const float* grad_output, const float* fwd_out,
                                        float* grad_data_out, int zero_first, void* stream);
 
+/* Forward ray render that allocates nothing (no counterpart in the
+ * reference).  Same inputs, outputs and results as svoxb_volume_render, for
+ * hosts that may not touch a device allocator while rendering: an application
+ * that hands the whole device heap to its own manager, a plug-in inside a
+ * real-time loop that forbids allocation, a process with a memory budget fixed
+ * at start-up.  The per-call scratch lives in a static device array instead:
+ * 16 MiB + 16 KiB that every GPU which loads the library holds until exit.
+ *
+ * Limits: octrees (N = 2) with SH colour in three channels (K = 3 * basis_dim
+ * + 1) and at most SVOXB_NOALLOC_MAX_NODES nodes; a larger tree is refused
+ * with SVOXB_ERR_TOO_LARGE, another layout with SVOXB_ERR_FORMAT, before
+ * anything is launched.
+ *
+ * The first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress); make that first call outside any stream capture.
+ * All calls share the one array.  Each call overwrites the parts it reads, so
+ * nothing has to be cleared between calls, but two calls whose kernels
+ * overlap on the GPU (different streams, no ordering between them) race on
+ * it: keep calls to this entry point ordered on a device. */
+#define SVOXB_NOALLOC_MAX_NODES (1 << 19)
+int svoxb_volume_render_noalloc(const svoxb_tree* tree, const svoxb_rays* rays,
+                                const svoxb_render_options* opt, float* out, void* stream);
+
 /* Per-ray march statistics for a ray batch (no counterpart in the
  * reference; it is how the byte model of the roofline is counted): number of
  * sampled leaves, of samples passing the forward density test

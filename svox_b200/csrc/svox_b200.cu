@@ -481,3 +481,5 @@ int svoxb_tune(int key, int value) {
 }
 
 }  // extern "C"
+
+#include "noalloc.cuh"
