@@ -122,6 +122,9 @@ def oracle_step_fn(tree, rays, targets):
 
 def cpu_reference(a, tree, rays, targets, budget_s):
     """Times the oracle on a bounded ray sample; returns (Mrays/s, ms/step, info)."""
+    from oracle import oracle as orc
+    # torchrun sets OMP_NUM_THREADS=1; the CPU arm uses every core this process may run on
+    orc.set_num_threads(len(os.sched_getaffinity(0)))
     step, threads = oracle_step_fn(tree, rays, targets)
     o, d, v = [t.numpy() for t in rays]
     tg = targets.numpy()
