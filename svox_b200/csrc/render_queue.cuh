@@ -124,15 +124,19 @@ struct alignas(16) WarpQueue {
     using Shape = CoopShape<K>;
     static constexpr int CAP = 96;  // a batch in flight (32) + items being collected (< 64)
     static constexpr int BD = (K - 1) / 3;
-    static constexpr int RAYW = (BD + 3) | 1;  // basis + upstream gradient; odd stride: no bank conflicts
+    static constexpr int RAYW = (BD + (BWD ? 3 : 0)) | 1;  // odd stride: no bank conflicts
     uint32_t slot[CAP];
     float w[CAP];                   // weight T * (1 - att)
     float T[BWD ? CAP : 4];         // transmittance after the sample
     float dd[BWD ? CAP : 4];        // delta_t * delta_scale
-    unsigned char owner[CAP];       // bits 0-4 owner lane, bit 7: item of an accumulation march
-    float res[32][4];               // per item: forward c0,c1,c2; backward tc, d(sigma)
-    float rayv[32][RAYW];           // per ray: SH basis [0, BD), upstream gradient [BD, BD+3)
-    alignas(16) float rows[32 * Shape::STRIDE + 4];  // staging rows (cp.async targets)
+    unsigned char owner[CAP];       // bits 0-4 owner lane, bit 5 ray parity, bit 7 accumulation march
+    float rayv[2][32][RAYW];        // per lane and ray parity: SH basis [0,BD), upstream gradient
+    float oldv[BWD ? 1 : 32][4];    // forward: colour sums and transmittance of the previous ray
+    long long oldray[BWD ? 1 : 32];
+    unsigned char oldstop[BWD ? 4 : 32];
+    // Staging rows (cp.async targets).  After lane i has read row i it reuses the
+    // row's first words for the item's results.
+    alignas(16) float rows[32 * Shape::STRIDE + 4];
 };
 
 enum { kNeedRay = 0, kMarching = 1, kDraining = 2, kExhausted = 3 };
@@ -147,6 +151,7 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
     constexpr bool BWD = MODE == kModeBackward;
     using WQ = WarpQueue<K, BWD>;
     using Shape = CoopShape<K>;
+    static_assert(Shape::STRIDE >= 3, "result words live in the staging row");
     extern __shared__ __align__(16) unsigned char s_raw[];
     __shared__ unsigned s_next;
     if (threadIdx.x == 0) s_next = 0;
@@ -165,15 +170,21 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
     const float big = (float)(1 << kCoordBits);
     const uint64_t pol_keep = l2_policy_keep(), pol_stream = l2_policy_stream();
 
-    // ---- per-lane ray state -------------------------------------------------
+    // ---- per-lane state -------------------------------------------------------
+    // A lane marches one ray (the CURRENT one) and may still have items queued for
+    // the ray it marched before (the OLD one): a finished ray hands its partial
+    // result over and the lane refills at once instead of waiting for the queue.
     Ray r;
     r.hit = false;
     int64_t ray = 0;
     int state = kNeedRay;
     float t = 0.f, light = 1.f;
-    float a0 = 0.f, a1 = 0.f, a2 = 0.f;  // forward: colour sums
-    float accum = 0.f;                    // backward
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f;  // forward: colour sums of the current ray
+    float accum = 0.f, accum_old = 0.f;   // backward
     bool stopped = false;
+    int par = 0;                 // parity tag of the current ray's items
+    int cnt_cur = 0, cnt_old = 0;  // queued items of the current / old ray
+    bool old_valid = false;
     int phase = 1;  // backward: 0 = accumulation march (reference PASS 1), 1 = scatter march
     int it = 0;
     // cursor of the descent in progress
@@ -183,14 +194,13 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
     int path[kPathLevels];    // path[j]: node at level base + 1 + j on the way to the last leaf
 #pragma unroll
     for (int j = 0; j < kPathLevels; ++j) path[j] = 0;
-    unsigned mine_lo = 0u;            // my items among queue positions [0, 32)
+    unsigned mine_lo = 0u;              // my items among queue positions [0, 32)
     unsigned long long mine_hi = 0ull;  // ... among [32, 96)
-    int qn = 0;                       // queued items (warp-uniform)
-    bool inflight = false;            // records of items [0, 32) have been requested
+    int qn = 0;                         // queued items (warp-uniform)
+    bool inflight = false;              // records of items [0, 32) have been requested
 
     // Places the cursor for the sample at parameter t, reusing the deepest cached
-    // ancestor shared with the previous sample (valid down to level `deepest`),
-    // and requests the child entry there.
+    // ancestor shared with the previous sample (valid down to level `deepest`).
     auto place_cursor = [&](int deepest) {
         px = clamp01(mad_site<FC_POS>(t, r.dx, r.ox));
         py = clamp01(mad_site<FC_POS>(t, r.dy, r.oy));
@@ -217,24 +227,33 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                 if (e >= 0) { node = e; lvl = base; }
             }
         }
-        const int b = kCoordBits - 1 - lvl;
-        const int cell = (((ix >> b) & 1) << 2) | (((iy >> b) & 1) << 1) | ((iz >> b) & 1);
-        e_pre = ld_keep(child + ((uint32_t)node * 8u + (uint32_t)cell), pol_keep);
+    };
+
+    // Writes the result of a finished forward ray.
+    auto write_out = [&](int64_t ry, float c0, float c1, float c2, float lt, bool stp) {
+        if (stp) {
+            const float scale = 1.0 / (1.0 - lt);
+            out[3 * ry + 0] = c0 * scale; out[3 * ry + 1] = c1 * scale; out[3 * ry + 2] = c2 * scale;
+        } else {
+            out[3 * ry + 0] = c0 + lt * bg; out[3 * ry + 1] = c1 + lt * bg; out[3 * ry + 2] = c2 + lt * bg;
+        }
     };
 
     // Evaluates the first nb queued items, whose records are in the staging rows.
     auto evaluate = [&](int nb) {
         float sg[3] = {0.f, 0.f, 0.f};
         float raw_sigma = 0.f;
-        int own = lane;
+        int own = lane, opar = 0;
         bool acc_item = false;
         if (lane < nb) {
-            own = q.owner[lane] & 31;
-            acc_item = (q.owner[lane] & 0x80) != 0;
-            const float* row = q.rows + lane * Shape::STRIDE;
+            const int ob = q.owner[lane];
+            own = ob & 31;
+            opar = (ob >> 5) & 1;
+            acc_item = (ob & 0x80) != 0;
+            float* row = q.rows + lane * Shape::STRIDE;
             float bs[BD];
 #pragma unroll
-            for (int i = 0; i < BD; ++i) bs[i] = q.rayv[own][i];
+            for (int i = 0; i < BD; ++i) bs[i] = q.rayv[opar][own][i];
             float v[K];
             if (Shape::VEC) {
 #pragma unroll
@@ -257,12 +276,12 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                 col[ch] = sg[ch] * d_rgb_pad - opt.rgb_padding;
             }
             if (!BWD) {
-                q.res[lane][0] = col[0]; q.res[lane][1] = col[1]; q.res[lane][2] = col[2];
+                row[0] = col[0]; row[1] = col[1]; row[2] = col[2];
             } else {
                 float total_color = 0.f;
 #pragma unroll
-                for (int ch = 0; ch < 3; ++ch) total_color += col[ch] * q.rayv[own][BD + ch];
-                q.res[lane][0] = total_color;
+                for (int ch = 0; ch < 3; ++ch) total_color += col[ch] * q.rayv[opar][own][BD + ch];
+                row[0] = total_color;
             }
         }
         __syncwarp();
@@ -273,19 +292,40 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                 const int k = __ffs(m) - 1;
                 m &= m - 1u;
                 const float wk = q.w[k];
+                const int ob = q.owner[k];
+                const bool is_cur = ((ob >> 5) & 1) == par;
+                float* res = q.rows + k * Shape::STRIDE;
                 if (!BWD) {
-                    a0 += wk * q.res[k][0];
-                    a1 += wk * q.res[k][1];
-                    a2 += wk * q.res[k][2];
-                } else {
-                    const float tc = q.res[k][0];
-                    if (q.owner[k] & 0x80) {
-                        accum += wk * tc;
+                    if (is_cur) {
+                        a0 += wk * res[0]; a1 += wk * res[1]; a2 += wk * res[2];
+                        --cnt_cur;
                     } else {
+                        float o0 = q.oldv[lane][0], o1 = q.oldv[lane][1], o2 = q.oldv[lane][2];
+                        o0 += wk * res[0]; o1 += wk * res[1]; o2 += wk * res[2];
+                        q.oldv[lane][0] = o0; q.oldv[lane][1] = o1; q.oldv[lane][2] = o2;
+                        --cnt_old;
+                    }
+                } else {
+                    const float tc = res[0];
+                    if (ob & 0x80) {
+                        accum += wk * tc;
+                        --cnt_cur;
+                    } else if (is_cur) {
                         accum -= wk * tc;
-                        q.res[k][1] = q.dd[k] * (tc * q.T[k] - accum);
+                        res[1] = q.dd[k] * (tc * q.T[k] - accum);
+                        --cnt_cur;
+                    } else {
+                        accum_old -= wk * tc;
+                        res[1] = q.dd[k] * (tc * q.T[k] - accum_old);
+                        --cnt_old;
                     }
                 }
+            }
+            if (old_valid && cnt_old == 0) {
+                if (!BWD)
+                    write_out(q.oldray[lane], q.oldv[lane][0], q.oldv[lane][1], q.oldv[lane][2],
+                              q.oldv[lane][3], q.oldstop[lane] != 0);
+                old_valid = false;
             }
         }
         if (BWD) {
@@ -294,14 +334,16 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
             if (lane < nb && !acc_item) {
                 float* row = q.rows + lane * Shape::STRIDE;
                 const float wk = q.w[lane];
+                const float gs = row[1];
                 float v[K];
 #pragma unroll
                 for (int ch = 0; ch < 3; ++ch) {
-                    const float tmp2 = wk * sg[ch] * (1.0 - sg[ch]) * q.rayv[own][BD + ch] * d_rgb_pad;
+                    const float tmp2 =
+                        wk * sg[ch] * (1.0 - sg[ch]) * q.rayv[opar][own][BD + ch] * d_rgb_pad;
 #pragma unroll
-                    for (int i = 0; i < BD; ++i) v[ch * BD + i] = q.rayv[own][i] * tmp2;
+                    for (int i = 0; i < BD; ++i) v[ch * BD + i] = q.rayv[opar][own][i] * tmp2;
                 }
-                v[K - 1] = q.res[lane][1] * (opt.density_softplus ? sigmoid_ref(raw_sigma - 1) : 1);
+                v[K - 1] = gs * (opt.density_softplus ? sigmoid_ref(raw_sigma - 1) : 1);
                 if (Shape::VEC) {
 #pragma unroll
                     for (int w = 0; w < K / 4; ++w)
@@ -379,33 +421,27 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
 
     PROF_T0();
     for (;;) {
-        // ---- finish rays whose items are all folded in, then refill ------------------
-        if (state == kDraining && mine_lo == 0u && mine_hi == 0ull) {
-            if (!BWD) {
-                if (stopped) {
-                    const float scale = 1.0 / (1.0 - light);
-                    out[3 * ray + 0] = a0 * scale;
-                    out[3 * ray + 1] = a1 * scale;
-                    out[3 * ray + 2] = a2 * scale;
+        bool force = false;
+        // ---- lanes that are not marching: finish, refill, termination ---------------------
+        if (__ballot_sync(0xffffffffu, state != kMarching) != 0u) {
+            if (state == kDraining && cnt_cur == 0) {
+                if (BWD && phase == 0) {
+                    // tail of the reference's PASS 1 (rt_kernel.cu:415-418), then march again
+                    const float* g = &q.rayv[par][lane][BD];
+                    const float total_grad = g[0] + g[1] + g[2];
+                    accum += light * bg * total_grad;
+                    phase = 1;
+                    t = r.tmin; light = 1.f; it = 0;
+                    state = kMarching;
+                    place_cursor(0);
+                    const int b = kCoordBits - 1 - lvl;
+                    const int cell = (((ix >> b) & 1) << 2) | (((iy >> b) & 1) << 1) | ((iz >> b) & 1);
+                    e_pre = ld_keep(child + ((uint32_t)node * 8u + (uint32_t)cell), pol_keep);
                 } else {
-                    out[3 * ray + 0] = a0 + light * bg;
-                    out[3 * ray + 1] = a1 + light * bg;
-                    out[3 * ray + 2] = a2 + light * bg;
+                    if (!BWD) write_out(ray, a0, a1, a2, light, stopped);
+                    state = kNeedRay;
                 }
-                state = kNeedRay;
-            } else if (phase == 0) {
-                // tail of the reference's PASS 1 (rt_kernel.cu:415-418), then march again
-                const float total_grad = q.rayv[lane][BD] + q.rayv[lane][BD + 1] + q.rayv[lane][BD + 2];
-                accum += light * bg * total_grad;
-                phase = 1;
-                t = r.tmin; light = 1.f; it = 0;
-                state = kMarching;
-                place_cursor(0);
-            } else {
-                state = kNeedRay;
             }
-        }
-        if (__any_sync(0xffffffffu, state == kNeedRay)) {
             if (state == kNeedRay) {
                 const unsigned ticket = atomicAdd(&s_next, 1u);
                 const int64_t gran = (int64_t)blockIdx.x + (int64_t)gridDim.x * (ticket >> 5);
@@ -424,13 +460,15 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                         sh_basis<BD>(r.vdir, basis);
 #pragma unroll
                         for (int i = 0; i < BD; ++i)
-                            q.rayv[lane][i] = (i < opt.min_comp || i > opt.max_comp) ? 0.f : basis[i];
+                            q.rayv[par][lane][i] =
+                                (i < opt.min_comp || i > opt.max_comp) ? 0.f : basis[i];
                         if (!BWD) {
                             a0 = a1 = a2 = 0.f;
                         } else {
                             const float g0 = __ldg(grad_out + 3 * ray), g1 = __ldg(grad_out + 3 * ray + 1),
                                         g2 = __ldg(grad_out + 3 * ray + 2);
-                            q.rayv[lane][BD] = g0; q.rayv[lane][BD + 1] = g1; q.rayv[lane][BD + 2] = g2;
+                            float* g = &q.rayv[par][lane][BD];
+                            g[0] = g0; g[1] = g1; g[2] = g2;
                             if (single) {
                                 accum = __ldg(fwd_out + 3 * ray) * g0;
                                 accum += __ldg(fwd_out + 3 * ray + 1) * g1;
@@ -442,15 +480,23 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                             }
                         }
                         place_cursor(0);
+                        const int b = kCoordBits - 1 - lvl;
+                        const int cell = (((ix >> b) & 1) << 2) | (((iy >> b) & 1) << 1) | ((iz >> b) & 1);
+                        e_pre = ld_keep(child + ((uint32_t)node * 8u + (uint32_t)cell), pol_keep);
                     }
                 }
             }
             __syncwarp();
-        }
-        const bool draining = __any_sync(0xffffffffu, state == kDraining);
-        if (!__any_sync(0xffffffffu, state == kMarching) && !draining) {
-            if (__all_sync(0xffffffffu, state == kExhausted)) break;
-            continue;
+            if (__ballot_sync(0xffffffffu, state == kMarching) == 0u) {
+                // nobody marches: flush what is queued, then stop when every lane is done
+                if (qn == 0) {
+                    if (__all_sync(0xffffffffu, state == kExhausted)) break;
+                    continue;
+                }
+                force = true;
+            } else if (__any_sync(0xffffffffu, state == kDraining)) {
+                force = true;
+            }
         }
         PROF_ADD(0);
         PROF_CNT(8, 1);
@@ -461,8 +507,7 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
         float weight = 0.f, dd = 0.f;
         if (state == kMarching) {
             const int32_t e = e_pre;
-            const int b = kCoordBits - 1 - lvl;
-            const int cell = (((ix >> b) & 1) << 2) | (((iy >> b) & 1) << 1) | ((iz >> b) & 1);
+            bool go = true;
             if (e > 0) {
                 // inner node: one level down
                 node += e;
@@ -470,28 +515,25 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                 if (node >= M || lvl >= kCoordBits) {
                     report(SVOXB_ERR_TREE);
                     state = kDraining;
-                } else {
+                    go = false;
+                } else if (base > 0) {
                     const int j = lvl - base - 1;
-                    if (base > 0) {
 #pragma unroll
-                        for (int jj = 0; jj < kPathLevels; ++jj)
-                            if (j == jj) path[jj] = node;
-                    }
-                    const int b2 = b - 1;
-                    const int c2 = (((ix >> b2) & 1) << 2) | (((iy >> b2) & 1) << 1) | ((iz >> b2) & 1);
-                    e_pre = ld_keep(child + ((uint32_t)node * 8u + (uint32_t)c2), pol_keep);
+                    for (int jj = 0; jj < kPathLevels; ++jj)
+                        if (j == jj) path[jj] = node;
                 }
             } else {
                 // leaf of depth lvl + 1: sample it
                 bool done = false;
                 const int depth = lvl + 1;
-                slot = (uint32_t)node * 8u + (uint32_t)cell;
+                const int b = kCoordBits - depth;
+                slot = (uint32_t)node * 8u +
+                       (uint32_t)((((ix >> b) & 1) << 2) | (((iy >> b) & 1) << 1) | ((iz >> b) & 1));
                 const float cube = __int_as_float((127 + depth) << 23);      // 2^depth
                 const float inv_cube = __int_as_float((127 - depth) << 23);  // 2^-depth
-                const int sh = kCoordBits - depth;
-                const float fx = __fmaf_rn(px, cube, -(float)(ix >> sh));  // exact
-                const float fy = __fmaf_rn(py, cube, -(float)(iy >> sh));
-                const float fz = __fmaf_rn(pz, cube, -(float)(iz >> sh));
+                const float fx = __fmaf_rn(px, cube, -(float)(ix >> b));  // exact
+                const float fy = __fmaf_rn(py, cube, -(float)(iy >> b));
+                const float fz = __fmaf_rn(pz, cube, -(float)(iz >> b));
                 float smin, smax;
                 dda_unit<FC_DDA_LEAF>(fx, fy, fz, r.ix, r.iy, r.iz, smin, smax);
                 // dividing by 2^depth == multiplying by 2^-depth, exactly
@@ -518,8 +560,40 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                     report(SVOXB_ERR_MARCH);
                     done = true;
                 }
-                if (done) state = kDraining;
-                else place_cursor(lvl);
+                if (!done) {
+                    place_cursor(lvl);
+                } else {
+                    go = false;
+                    const int pending = cnt_cur + (item ? 1 : 0);
+                    if (BWD && phase == 0) {
+                        state = kDraining;     // accum must be complete before the second march
+                    } else if (pending == 0) {
+                        if (!BWD) write_out(ray, a0, a1, a2, light, stopped);
+                        state = kNeedRay;
+                    } else if (!old_valid) {
+                        // hand the ray over to the "old" context and refill at once
+                        if (!BWD) {
+                            q.oldv[lane][0] = a0; q.oldv[lane][1] = a1; q.oldv[lane][2] = a2;
+                            q.oldv[lane][3] = light;
+                            q.oldray[lane] = ray;
+                            q.oldstop[lane] = stopped ? 1 : 0;
+                        } else {
+                            accum_old = accum;
+                        }
+                        cnt_old = pending;
+                        cnt_cur = item ? -1 : 0;  // the push below counts the last item ...
+                        if (!item) par ^= 1;      // ... and then switches the parity tag
+                        old_valid = true;
+                        state = kNeedRay;
+                    } else {
+                        state = kDraining;     // both contexts busy: wait for the queue
+                    }
+                }
+            }
+            if (go) {
+                const int b = kCoordBits - 1 - lvl;
+                const int cell = (((ix >> b) & 1) << 2) | (((iy >> b) & 1) << 1) | ((iz >> b) & 1);
+                e_pre = ld_keep(child + ((uint32_t)node * 8u + (uint32_t)cell), pol_keep);
             }
         }
         PROF_ADD(1);
@@ -531,15 +605,18 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
             q.slot[pos] = slot;
             q.w[pos] = weight;
             if (BWD) { q.T[pos] = light; q.dd[pos] = dd; }
-            q.owner[pos] = (unsigned char)(lane | ((BWD && phase == 0) ? 0x80 : 0));
+            q.owner[pos] = (unsigned char)(lane | (par << 5) | ((BWD && phase == 0) ? 0x80 : 0));
             if (pos < 32) mine_lo |= 1u << pos;
             else mine_hi |= 1ull << (pos - 32);
+            ++cnt_cur;
+            // a ray that ended with this item has just been handed over: its items carry
+            // the parity they were pushed with, the next ray uses the other one
+            if (cnt_cur == 0) par ^= 1;
         }
         qn += __popc(pushed);
-        const bool force = qn > 0 && __any_sync(0xffffffffu, state == kDraining);
         const int collected = qn - (inflight ? 32 : 0);
         PROF_ADD(2);
-        if (collected < 32 && !force) continue;
+        if (collected < 32 && !(force && qn > 0)) continue;
         __syncwarp();
 
         // ---- S step -------------------------------------------------------------------
@@ -554,7 +631,7 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
             PROF_ADD(4);
         }
         if (force) {
-            // a finished ray waits for its items: flush everything now
+            // a lane waits for its items (or nobody marches any more): flush everything now
             while (qn > 0) {
                 const int nb = qn < 32 ? qn : 32;
                 request(nb);
