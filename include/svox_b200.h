@@ -138,7 +138,7 @@ int svoxb_volume_render_image_backward(const svoxb_tree* tree, const svoxb_camer
  * that hands the whole device heap to its own manager, a plug-in inside a
  * real-time loop that forbids allocation, a process with a memory budget fixed
  * at start-up.  The per-call scratch lives in a static device array instead:
- * 16 MiB + 16 KiB that every GPU which loads the library holds until exit.
+ * 17 MiB that every GPU which loads the library holds until exit.
  *
  * Limits: octrees (N = 2) with SH colour in three channels (K = 3 * basis_dim
  * + 1) and at most SVOXB_NOALLOC_MAX_NODES nodes; a larger tree is refused

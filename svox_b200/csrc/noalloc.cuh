@@ -17,10 +17,10 @@
 namespace svoxb {
 
 constexpr int64_t kNoAllocMaxNodes = 1 << 19;  // 524288 nodes -> 16 MiB of annotated entries
-constexpr int kNoAllocTopLevel = 4;            // jump table: 16^3 entries (16 KiB)
+constexpr int kNoAllocTopLevel = 6;            // leaf table: 64^3 entries (1 MiB)
 constexpr int64_t kNoAllocTopCells = 1 << (3 * kNoAllocTopLevel);
 
-// [0, 8 * kNoAllocMaxNodes): annotated child entries; then the jump table.
+// [0, 8 * kNoAllocMaxNodes): annotated child entries; then the leaf table.
 static __device__ __align__(256) int32_t g_noalloc_scratch[kNoAllocMaxNodes * 8 + kNoAllocTopCells];
 
 // Device address of the array, per device.  In host code the symbol's name is
@@ -54,11 +54,12 @@ static int launch_noalloc(const RenderCall& c, const RayBatch& src, int32_t* scr
     const int level = auto_top_level(t->M, kNoAllocTopLevel);
     if (level > 0) {
         const int cells = 1 << (3 * level);
-        build_top_kernel<<<(cells + 255) / 256, 256, 0, c.stream>>>(t->child, t->M, level, table);
+        build_leaf_table_kernel<<<(cells + 255) / 256, 256, 0, c.stream>>>(annotated, t->M, level,
+                                                                          table);
         SVOXB_CUDA(cudaGetLastError());
     }
     const TopTable top{table, level};
-    const size_t top_bytes = level > 0 ? ((size_t)4 << (3 * level)) : 0;
+    const size_t top_bytes = 0;
     TreeArgs tr = tree_args(t);
     tr.child = annotated;
     if constexpr (BD <= 9) return launch_queue_block<BD, 768>(c, src, tr, top, top_bytes);

@@ -55,7 +55,7 @@ __device__ unsigned long long g_prof[16];
 #endif
 
 constexpr int kCoordBits = 24;  // integer coordinates: floor(x * 2^24), exact for float x < 1
-constexpr int kPathLevels = 6;  // cached ancestors below the jump-table level
+constexpr int kPathLevels = 6;  // cached ancestors from the table level down
 
 // Annotated child entry: > 0 link; 0 leaf failing the density test; < 0 leaf
 // passing it, with the density's float bits in the low 31 bits when the
@@ -114,6 +114,38 @@ __device__ __forceinline__ void red_add_v4_hint(float* addr, float a, float b, f
                  "f"(a), "f"(b), "f"(c), "f"(d), "l"(pol)
                  : "memory");
 }
+// Leaf table over the top `level` levels of the annotated tree, one int32 per
+// cell of the 2^level cube, in global memory (1 MB at level 6, kept in L2):
+//   > 0          id of the node at that level (its children are the next level's cells)
+//   -d (d >= 1)  the cell lies in a leaf of depth d that fails the density test:
+//                a sample there needs no further look-up at all
+//   kTabDescend  anything else (a shallow leaf that passes the test): walk from the root
+// Most samples of a sparse scene fall into empty space; with this table each of
+// them costs exactly one dependent load.
+constexpr int32_t kTabDescend = INT32_MIN;
+
+__global__ void build_leaf_table_kernel(const int32_t* __restrict__ annotated, int64_t M, int L,
+                                        int32_t* __restrict__ cells) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (1 << (3 * L))) return;
+    const int S = (1 << L) - 1;
+    const int iz = idx & S, iy = (idx >> L) & S, ix = idx >> (2 * L);
+    int64_t node = 0;
+    int32_t entry = 0;
+    for (int l = L - 1; l >= 0; --l) {
+        const int u = (ix >> l) & 1, v = (iy >> l) & 1, w = (iz >> l) & 1;
+        const int32_t e = annotated[node * 8 + (u * 4 + v * 2 + w)];
+        if (e <= 0) {
+            entry = (e == 0) ? -(L - l) : kTabDescend;
+            node = -1;
+            break;
+        }
+        node += e;
+        if (node >= M) { entry = kTabDescend; node = -1; break; }
+    }
+    cells[idx] = node >= 0 ? (int32_t)node : entry;
+}
+
 __device__ __forceinline__ void cp_async_wait_all() {
     asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
 }
@@ -155,7 +187,7 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
     extern __shared__ __align__(16) unsigned char s_raw[];
     __shared__ unsigned s_next;
     if (threadIdx.x == 0) s_next = 0;
-    const TopTable top = stage_top(topg, reinterpret_cast<int32_t*>(s_raw), top_bytes > 0);
+    const TopTable top = topg;  // leaf table in global memory (top_bytes is 0)
     __syncthreads();
 
     const int lane = threadIdx.x & 31;
@@ -190,8 +222,11 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
     // cursor of the descent in progress
     int node = 0, lvl = 0, ix = 0, iy = 0, iz = 0;
     float px = 0.f, py = 0.f, pz = 0.f;
-    int32_t e_pre = 0;        // child entry at the cursor, requested one iteration ahead
-    int path[kPathLevels];    // path[j]: node at level base + 1 + j on the way to the last leaf
+    int32_t e_pre = 0;        // entry at the cursor, requested one iteration ahead ...
+    bool from_tab = false;    // ... from the leaf table (else from the annotated child array)
+    int tab_idx = 0;
+
+    int path[kPathLevels];    // path[j]: node at level base + j on the way to the last leaf
 #pragma unroll
     for (int j = 0; j < kPathLevels; ++j) path[j] = 0;
     unsigned mine_lo = 0u;              // my items among queue positions [0, 32)
@@ -209,10 +244,10 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
         const int diff = (nx ^ ix) | (ny ^ iy) | (nz ^ iz);
         int common = __clz(diff) - (32 - kCoordBits);  // leading coordinate bits in common
         if (common > deepest) common = deepest;
-        if (common > base + kPathLevels) common = base + kPathLevels;
+        if (common > base + kPathLevels - 1) common = base + kPathLevels - 1;
         ix = nx; iy = ny; iz = nz;
-        if (base > 0 && common > base) {
-            const int j = common - base - 1;
+        if (base > 0 && common >= base) {
+            const int j = common - base;
             int n = path[0];
 #pragma unroll
             for (int jj = 1; jj < kPathLevels; ++jj) n = (j == jj) ? path[jj] : n;
@@ -223,9 +258,20 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
             lvl = 0;
             if (base > 0) {
                 const int sh = kCoordBits - base;
-                const int32_t e = top.cells[((((ix >> sh) << base) + (iy >> sh)) << base) + (iz >> sh)];
-                if (e >= 0) { node = e; lvl = base; }
+                tab_idx = ((((ix >> sh) << base) + (iy >> sh)) << base) + (iz >> sh);
+                from_tab = true;
             }
+        }
+    };
+
+    // Requests the entry at the cursor (table cell or child slot).
+    auto request_entry = [&]() {
+        if (from_tab) {
+            e_pre = ld_keep(top.cells + tab_idx, pol_keep);
+        } else {
+            const int b = kCoordBits - 1 - lvl;
+            const int cell = (((ix >> b) & 1) << 2) | (((iy >> b) & 1) << 1) | ((iz >> b) & 1);
+            e_pre = ld_keep(child + ((uint32_t)node * 8u + (uint32_t)cell), pol_keep);
         }
     };
 
@@ -434,9 +480,7 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                     t = r.tmin; light = 1.f; it = 0;
                     state = kMarching;
                     place_cursor(0);
-                    const int b = kCoordBits - 1 - lvl;
-                    const int cell = (((ix >> b) & 1) << 2) | (((iy >> b) & 1) << 1) | ((iz >> b) & 1);
-                    e_pre = ld_keep(child + ((uint32_t)node * 8u + (uint32_t)cell), pol_keep);
+                    request_entry();
                 } else {
                     if (!BWD) write_out(ray, a0, a1, a2, light, stopped);
                     state = kNeedRay;
@@ -480,9 +524,7 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                             }
                         }
                         place_cursor(0);
-                        const int b = kCoordBits - 1 - lvl;
-                        const int cell = (((ix >> b) & 1) << 2) | (((iy >> b) & 1) << 1) | ((iz >> b) & 1);
-                        e_pre = ld_keep(child + ((uint32_t)node * 8u + (uint32_t)cell), pol_keep);
+                        request_entry();
                     }
                 }
             }
@@ -501,34 +543,51 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
         PROF_ADD(0);
         PROF_CNT(8, 1);
 
-        // ---- G step: consume one child entry per lane ------------------------------------
+        // ---- G step: every lane consumes the entry it requested one iteration ago -----------
+        // An inner node moves the cursor one level down; a leaf is sampled and the cursor
+        // moves to the next sample.  Either way the next entry is requested at the end,
+        // so its latency overlaps the queue work below and the loop overhead.
         bool item = false;
         uint32_t slot = 0;
         float weight = 0.f, dd = 0.f;
         if (state == kMarching) {
-            const int32_t e = e_pre;
-            bool go = true;
-            if (e > 0) {
-                // inner node: one level down
-                node += e;
+            int32_t e = e_pre;
+            bool go = true, is_leaf = false;
+            int depth = 0;
+            if (from_tab) {
+                from_tab = false;
+                if (e > 0) {                    // node at the table level
+                    node = e;
+                    lvl = base;
+                    path[0] = e;
+                } else if (e == kTabDescend) {  // resolve from the root
+                    node = 0;
+                    lvl = 0;
+                } else {                        // empty leaf of depth -e: nothing else to read
+                    is_leaf = true;
+                    depth = -e;
+                    e = 0;
+                }
+            } else if (e > 0) {
+                node += e;                      // inner node: one level down
                 ++lvl;
                 if (node >= M || lvl >= kCoordBits) {
                     report(SVOXB_ERR_TREE);
                     state = kDraining;
                     go = false;
                 } else if (base > 0) {
-                    const int j = lvl - base - 1;
+                    const int j = lvl - base;
 #pragma unroll
-                    for (int jj = 0; jj < kPathLevels; ++jj)
+                    for (int jj = 1; jj < kPathLevels; ++jj)
                         if (j == jj) path[jj] = node;
                 }
             } else {
-                // leaf of depth lvl + 1: sample it
+                is_leaf = true;
+                depth = lvl + 1;
+            }
+            if (is_leaf) {
                 bool done = false;
-                const int depth = lvl + 1;
                 const int b = kCoordBits - depth;
-                slot = (uint32_t)node * 8u +
-                       (uint32_t)((((ix >> b) & 1) << 2) | (((iy >> b) & 1) << 1) | ((iz >> b) & 1));
                 const float cube = __int_as_float((127 + depth) << 23);      // 2^depth
                 const float inv_cube = __int_as_float((127 - depth) << 23);  // 2^-depth
                 const float fx = __fmaf_rn(px, cube, -(float)(ix >> b));  // exact
@@ -540,6 +599,8 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                 const float delta_t =
                     __fadd_rn(__fmul_rn(__fsub_rn(smax, smin), inv_cube), opt.step_size);
                 if (e < 0) {
+                    slot = (uint32_t)node * 8u + (uint32_t)((((ix >> b) & 1) << 2) |
+                                                            (((iy >> b) & 1) << 1) | ((iz >> b) & 1));
                     float sigma = (e == kOccupied) ? __ldg(tr.data + (size_t)slot * K + (K - 1))
                                                    : __uint_as_float((uint32_t)e & 0x7fffffffu);
                     if (opt.density_softplus) sigma = softplus_m1(sigma);
@@ -561,7 +622,7 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                     done = true;
                 }
                 if (!done) {
-                    place_cursor(lvl);
+                    place_cursor(depth - 1);
                 } else {
                     go = false;
                     const int pending = cnt_cur + (item ? 1 : 0);
@@ -590,11 +651,7 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                     }
                 }
             }
-            if (go) {
-                const int b = kCoordBits - 1 - lvl;
-                const int cell = (((ix >> b) & 1) << 2) | (((iy >> b) & 1) << 1) | ((iz >> b) & 1);
-                e_pre = ld_keep(child + ((uint32_t)node * 8u + (uint32_t)cell), pol_keep);
-            }
+            if (go) request_entry();
         }
         PROF_ADD(1);
 

@@ -170,34 +170,47 @@ static int launch_queue_block(const RenderCall& c, const Source& src, const Tree
     return SVOXB_OK;
 }
 
-struct AnnotSigmaScratch {
-    int32_t* child = nullptr;
+// Per-call scratch of the queue kernels: the annotated child array followed by
+// the leaf table (render_queue.cuh); one pool allocation, freed on the stream.
+struct QueueScratch {
+    int32_t* annotated = nullptr;
+    int32_t* table = nullptr;
+    int level = 0;
     cudaStream_t stream = nullptr;
-    int build(const svoxb_tree* t, float thresh, int softplus, cudaStream_t s) {
+    int build(const svoxb_tree* t, float thresh, int softplus, int max_level, cudaStream_t s) {
         stream = s;
         const int64_t n = t->M * 8;
+        level = auto_top_level(t->M, max_level);
+        const int64_t cells = level > 0 ? ((int64_t)1 << (3 * level)) : 0;
         int st = keep_pool_cached();
         if (st) return st;
-        SVOXB_CUDA(cudaMallocAsync((void**)&child, (size_t)n * sizeof(int32_t), s));
+        SVOXB_CUDA(cudaMallocAsync((void**)&annotated, (size_t)(n + cells) * sizeof(int32_t), s));
+        table = annotated + n;
         annotate_sigma_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(
-            t->child, t->data, t->K, n, thresh, softplus, child);
+            t->child, t->data, t->K, n, thresh, softplus, annotated);
         SVOXB_CUDA(cudaGetLastError());
+        if (level > 0) {
+            build_leaf_table_kernel<<<(unsigned)((cells + 255) / 256), 256, 0, s>>>(
+                annotated, t->M, level, table);
+            SVOXB_CUDA(cudaGetLastError());
+        }
         return SVOXB_OK;
     }
-    ~AnnotSigmaScratch() { if (child) cudaFreeAsync(child, stream); }
+    ~QueueScratch() { if (annotated) cudaFreeAsync(annotated, stream); }
 };
 
 template <int BD, class Source>
-static int launch_queue(const RenderCall& c, const Source& src, const TopTable& top) {
+static int launch_queue(const RenderCall& c, const Source& src) {
     constexpr int K = 3 * BD + 1;
-    AnnotSigmaScratch annot;
-    int st = annot.build(c.tree, c.backward ? 0.f : c.opt.sigma_thresh, c.opt.density_softplus,
-                         c.stream);
+    QueueScratch scratch;
+    const int max_level = g_tuning.render_top_level >= 0 ? g_tuning.render_top_level : 6;
+    int st = scratch.build(c.tree, c.backward ? 0.f : c.opt.sigma_thresh, c.opt.density_softplus,
+                           max_level > 7 ? 7 : max_level, c.stream);
     if (st) return st;
     TreeArgs tr = tree_args(c.tree);
-    tr.child = annot.child;
-    // the jump table is staged in shared memory up to level 4 (16 KB)
-    const size_t top_bytes = (top.level > 0 && top.level <= 4) ? ((size_t)4 << (3 * top.level)) : 0;
+    tr.child = scratch.annotated;
+    const TopTable top{scratch.table, scratch.level};
+    const size_t top_bytes = 0;  // the leaf table stays in global memory
     const size_t per_warp = c.backward ? sizeof(WarpQueue<K, true>) : sizeof(WarpQueue<K, false>);
     int want = g_tuning.render_block > 0 ? g_tuning.render_block : 768;
     while (want > 256 && top_bytes + (size_t)(want / 32) * per_warp + 64 > kMaxSmem) want -= 128;
@@ -245,16 +258,6 @@ static int dispatch_layout(const RenderCall& c, const Source& src, const TopTabl
     const bool vec = aligned && (t->K % 4 == 0);
     // Warp-cooperative kernels: octrees whose records allow the chosen word
     // size (any K with 32-bit words; 16-byte aligned buffers for K % 4 == 0).
-    if (g_tuning.render_algo == 2 && t->N == 2 && (aligned || t->K % 4 != 0) &&
-        t->M < (1LL << 28)) {
-        switch (c.opt.basis_dim) {
-            case 1: return launch_queue<1>(c, src, top);
-            case 4: return launch_queue<4>(c, src, top);
-            case 9: return launch_queue<9>(c, src, top);
-            case 16: return launch_queue<16>(c, src, top);
-            case 25: return launch_queue<25>(c, src, top);
-        }
-    }
     if (g_tuning.render_algo == 0 && t->N == 2 && (aligned || t->K % 4 != 0) &&
         t->M * 8 < 0xffffffffLL) {
         switch (c.opt.basis_dim) {
@@ -292,6 +295,25 @@ static int render_dispatch(const RenderCall& c, const Source& src) {
     }
     if (c.Q == 0) return SVOXB_OK;
     if (c.backward ? !c.grad_out : !c.out) return SVOXB_ERR_NULL;
+
+    // Default path: the queue kernels, for octrees with SH colour in three
+    // channels whose buffers allow the record's word size.
+    {
+        const svoxb_tree* t = c.tree;
+        const bool sh3 = c.opt.format == SVOXB_FORMAT_SH && t->K == 3 * c.opt.basis_dim + 1;
+        const bool aligned = ((uintptr_t)t->data % 16 == 0) &&
+                             (!c.backward || (uintptr_t)c.grad_data % 16 == 0);
+        if (g_tuning.render_algo == 2 && sh3 && t->N == 2 && (aligned || t->K % 4 != 0) &&
+            t->M < (1LL << 28)) {
+            switch (c.opt.basis_dim) {
+                case 1: return launch_queue<1>(c, src);
+                case 4: return launch_queue<4>(c, src);
+                case 9: return launch_queue<9>(c, src);
+                case 16: return launch_queue<16>(c, src);
+                case 25: return launch_queue<25>(c, src);
+            }
+        }
+    }
 
     TopScratch scratch;
     const int max_level = g_tuning.render_top_level >= 0 ? g_tuning.render_top_level : 5;
