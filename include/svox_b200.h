@@ -132,6 +132,40 @@ int svoxb_volume_render_image_backward(const svoxb_tree* tree, const svoxb_camer
                                        const float* grad_output, const float* fwd_out,
                                        float* grad_data_out, int zero_first, void* stream);
 
+/* Logged forward + replay backward (no counterpart in the reference; the
+ * pair computes what volume_render followed by volume_render_backward
+ * computes, svox/csrc/rt_kernel.cu:1019-1083).  The logged forward also
+ * writes every contributing sample (leaf slot, weight, transmittance, step,
+ * colour sigmoids, ray) into `log`, a caller-allocated int32 device buffer of
+ * svoxb_item_log_words(capacity_chunks) words (one chunk = 32 samples).  The
+ * replay backward streams that log instead of marching the rays and reading
+ * the leaf records again.  Only for octrees with SH colour in three channels,
+ * sigma_thresh = stop_thresh = 0 and no density_softplus (else
+ * SVOXB_ERR_FORMAT / SVOXB_ERR_OPTION).  If the log was too small
+ * (svoxb_item_log_used reports more chunks than capacity_chunks) the log must
+ * not be replayed: call svoxb_volume_render_backward instead.  `data` must
+ * not change between the two calls. */
+int64_t svoxb_item_log_words(int64_t capacity_chunks);
+int svoxb_volume_render_logged(const svoxb_tree* tree, const svoxb_rays* rays,
+                               const svoxb_render_options* opt, float* out, int32_t* log,
+                               int64_t capacity_chunks, void* stream);
+int svoxb_volume_render_image_logged(const svoxb_tree* tree, const svoxb_camera* cam,
+                                     const svoxb_render_options* opt, float* out, int32_t* log,
+                                     int64_t capacity_chunks, void* stream);
+int svoxb_volume_render_backward_replay(const svoxb_tree* tree, const svoxb_rays* rays,
+                                        const svoxb_render_options* opt,
+                                        const float* grad_output, const float* fwd_out,
+                                        int32_t* log, int64_t capacity_chunks,
+                                        float* grad_data_out, int zero_first, void* stream);
+int svoxb_volume_render_image_backward_replay(const svoxb_tree* tree, const svoxb_camera* cam,
+                                              const svoxb_render_options* opt,
+                                              const float* grad_output, const float* fwd_out,
+                                              int32_t* log, int64_t capacity_chunks,
+                                              float* grad_data_out, int zero_first,
+                                              void* stream);
+/* Chunks the logged forward needed (synchronises `stream`). */
+int svoxb_item_log_used(const int32_t* log, int64_t* chunks_used, void* stream);
+
 /* Forward ray render that allocates nothing (no counterpart in the
  * reference).  Same inputs, outputs and results as svoxb_volume_render, for
  * hosts that may not touch a device allocator while rendering: an application

@@ -294,6 +294,103 @@ def volume_render_image(tree, cam, opt):
     return out
 
 
+# ---------------------------------------------------------------------------
+# Logged forward / replay backward (training step without a second march)
+
+_items_per_ray = 48.0   # running estimate used to size the item log
+_LOG_LIST_SLACK = 2 * 16384
+
+
+def log_eligible(tree, opt):
+    """Whether the logged forward / replay backward pair applies to this call."""
+    return (opt.format == FORMAT_SH and tree.data.shape[1] == 2
+            and tree.data.shape[4] == 3 * opt.basis_dim + 1
+            and opt.sigma_thresh == 0.0 and opt.stop_thresh == 0.0
+            and not opt.density_softplus and tree.data.dtype == torch.float32)
+
+
+def _log_alloc(n_rays, device):
+    lib = library()
+    lib.svoxb_item_log_words.restype = C.c_int64
+    cap = int(n_rays * _items_per_ray / 32) + _LOG_LIST_SLACK
+    words = lib.svoxb_item_log_words(C.c_int64(cap))
+    return torch.empty(words, dtype=torch.int32, device=device), cap
+
+
+def volume_render_logged(tree, rays_or_cam, opt, image=False):
+    """Forward render that also records its contributing samples.
+
+    -> (out, (log, capacity_chunks)); pass the pair to ``volume_render_backward_replay``.
+    """
+    lib = library()
+    ct = _pack_tree(tree)
+    co = opt._pack()
+    dev = tree.data.device
+    with torch.cuda.device(dev):
+        if image:
+            cs = _pack_camera(rays_or_cam, dev)
+            shape, n = (cs.height, cs.width, 3), cs.height * cs.width
+            fn = lib.svoxb_volume_render_image_logged
+        else:
+            cs = _pack_rays(rays_or_cam, dev)
+            shape, n = (cs.Q, 3), cs.Q
+            fn = lib.svoxb_volume_render_logged
+        out = torch.empty(shape, dtype=torch.float32, device=dev)
+        log, cap = _log_alloc(n, dev)
+        with _timed("volume_render"):
+            st = fn(C.byref(ct), C.byref(cs), C.byref(co), C.c_void_p(out.data_ptr()),
+                    C.c_void_p(log.data_ptr()), C.c_int64(cap), _stream())
+    if st:
+        _raise(st, "volume_render_logged")
+    return out, (log, cap)
+
+
+def log_chunks_used(log):
+    """Chunks the logged forward needed (synchronises the current stream)."""
+    used = C.c_int64(0)
+    st = library().svoxb_item_log_used(C.c_void_p(log.data_ptr()), C.byref(used), _stream())
+    if st:
+        _raise(st, "item_log_used")
+    return used.value
+
+
+def volume_render_backward_replay(tree, rays_or_cam, opt, grad_output, fwd_out, logpair,
+                                  image=False):
+    """Gradient w.r.t. data from the item log of ``volume_render_logged``; returns None if
+    the log overflowed (the caller then uses ``volume_render[_image]_backward``)."""
+    global _items_per_ray
+    lib = library()
+    log, cap = logpair
+    dev = tree.data.device
+    with torch.cuda.device(dev):
+        used = log_chunks_used(log)
+        n = fwd_out.numel() // 3
+        if n:
+            # chunks are 32 items, partly filled ones included: keep 25 % head room
+            need = max(8.0, 1.25 * 32.0 * used / n)
+            _items_per_ray = need if used > cap else max(need, 0.9 * _items_per_ray)
+        if used > cap:
+            return None
+        ct = _pack_tree(tree)
+        co = opt._pack()
+        _check_input(grad_output, "grad_output")
+        _check_input(fwd_out, "fwd_out")
+        grad = torch.zeros_like(tree.data, memory_format=torch.contiguous_format)
+        if image:
+            cs = _pack_camera(rays_or_cam, dev)
+            fn = lib.svoxb_volume_render_image_backward_replay
+        else:
+            cs = _pack_rays(rays_or_cam, dev)
+            fn = lib.svoxb_volume_render_backward_replay
+        with _timed("volume_render_backward"):
+            st = fn(C.byref(ct), C.byref(cs), C.byref(co), C.c_void_p(grad_output.data_ptr()),
+                    C.c_void_p(fwd_out.data_ptr()), C.c_void_p(log.data_ptr()), C.c_int64(cap),
+                    C.c_void_p(grad.data_ptr()), C.c_int(0), _stream())
+    if st:
+        _raise(st, "volume_render_backward_replay")
+    return grad
+
+
 def _fwd_ptr(fwd_out, shape):
     if fwd_out is None:
         return C.c_void_p(0)

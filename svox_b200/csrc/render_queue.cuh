@@ -54,6 +54,24 @@ __device__ unsigned long long g_prof[16];
 #define PROF_END()
 #endif
 
+constexpr int kModeForwardLogged = 2;  // forward that also records its items for the backward
+
+// Item log: what a logged forward leaves behind so that the backward pass can
+// replay the contributing samples without marching again and without reading
+// the leaf records a second time.  int32 words:
+//   [0] chunks allocated   [1] replay work counter   [2] number of chunk lists
+//   [kLogHeads + i]        first chunk of list i (one list per forward warp)
+//   chunk c at kLogChunks + c * kLogChunkWords: 10 rows of 32 words,
+//     row 0: word 0 = items in the chunk (0 ends the list), word 1 = next chunk
+//     rows 1-9, one word per item: slot, weight, T after, delta_t*delta_scale,
+//     sigmoid of the three channels, ray index, owner lane | parity << 5
+// A ray's items appear in march order within its list, which is all the
+// backward's sequential per-ray bookkeeping needs.
+constexpr int kLogHeads = 32;
+constexpr int kLogMaxLists = 16384;
+constexpr int kLogChunks = kLogHeads + kLogMaxLists;
+constexpr int kLogChunkWords = 320;
+
 constexpr int kCoordBits = 24;  // integer coordinates: floor(x * 2^24), exact for float x < 1
 constexpr int kPathLevels = 6;  // cached ancestors from the table level down
 
@@ -151,16 +169,19 @@ __device__ __forceinline__ void cp_async_wait_all() {
 }
 
 // Shared memory of one warp.
-template <int K, bool BWD>
+template <int K, int MODE>
 struct alignas(16) WarpQueue {
+    static constexpr bool BWD = MODE == kModeBackward;
+    static constexpr bool LOG = MODE == kModeForwardLogged;
     using Shape = CoopShape<K>;
     static constexpr int CAP = 96;  // a batch in flight (32) + items being collected (< 64)
     static constexpr int BD = (K - 1) / 3;
     static constexpr int RAYW = (BD + (BWD ? 3 : 0)) | 1;  // odd stride: no bank conflicts
     uint32_t slot[CAP];
     float w[CAP];                   // weight T * (1 - att)
-    float T[BWD ? CAP : 4];         // transmittance after the sample
-    float dd[BWD ? CAP : 4];        // delta_t * delta_scale
+    float T[(BWD || LOG) ? CAP : 4];   // transmittance after the sample
+    float dd[(BWD || LOG) ? CAP : 4];  // delta_t * delta_scale
+    int rayid[LOG ? CAP : 4];          // ray of the item (logged forward)
     unsigned char owner[CAP];       // bits 0-4 owner lane, bit 5 ray parity, bit 7 accumulation march
     float rayv[2][32][RAYW];        // per lane and ray parity: SH basis [0,BD), upstream gradient
     float oldv[BWD ? 1 : 32][4];    // forward: colour sums and transmittance of the previous ray
@@ -178,10 +199,12 @@ __global__ void __launch_bounds__(BLOCK)
 render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable topg,
                     int top_bytes, int64_t Q, float* __restrict__ out,
                     const float* __restrict__ grad_out, const float* __restrict__ fwd_out,
-                    float* __restrict__ grad_data) {
+                    float* __restrict__ grad_data, int32_t* __restrict__ log,
+                    int64_t log_capacity) {
     constexpr int K = 3 * BD + 1;
     constexpr bool BWD = MODE == kModeBackward;
-    using WQ = WarpQueue<K, BWD>;
+    constexpr bool LOG = MODE == kModeForwardLogged;
+    using WQ = WarpQueue<K, MODE>;
     using Shape = CoopShape<K>;
     static_assert(Shape::STRIDE >= 3, "result words live in the staging row");
     extern __shared__ __align__(16) unsigned char s_raw[];
@@ -233,6 +256,19 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
     unsigned long long mine_hi = 0ull;  // ... among [32, 96)
     int qn = 0;                         // queued items (warp-uniform)
     bool inflight = false;              // records of items [0, 32) have been requested
+    // logged forward: the chunk the next batch goes to (allocated one ahead, so that a
+    // chunk can name its successor when it is written)
+    int64_t log_chunk = 0;
+    if (LOG) {
+        int c = 0;
+        if (lane == 0) {
+            c = atomicAdd(log, 1);
+            const int list = blockIdx.x * (BLOCK / 32) + (threadIdx.x >> 5);
+            log[kLogHeads + list] = c;
+            if (list == 0) log[2] = gridDim.x * (BLOCK / 32);
+        }
+        log_chunk = __shfl_sync(0xffffffffu, c, 0);
+    }
 
     // Places the cursor for the sample at parameter t, reusing the deepest cached
     // ancestor shared with the previous sample (valid down to level `deepest`).
@@ -331,6 +367,27 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
             }
         }
         __syncwarp();
+        if (LOG) {
+            int nxt = 0;
+            if (lane == 0) nxt = atomicAdd(log, 1);
+            nxt = __shfl_sync(0xffffffffu, nxt, 0);
+            if (log_chunk < log_capacity) {
+                int32_t* ch = log + kLogChunks + log_chunk * kLogChunkWords;
+                if (lane == 0) { ch[0] = nb; ch[1] = nxt; }
+                if (lane < nb) {
+                    ch[32 * 1 + lane] = (int32_t)q.slot[lane];
+                    ch[32 * 2 + lane] = __float_as_int(q.w[lane]);
+                    ch[32 * 3 + lane] = __float_as_int(q.T[lane]);
+                    ch[32 * 4 + lane] = __float_as_int(q.dd[lane]);
+                    ch[32 * 5 + lane] = __float_as_int(sg[0]);
+                    ch[32 * 6 + lane] = __float_as_int(sg[1]);
+                    ch[32 * 7 + lane] = __float_as_int(sg[2]);
+                    ch[32 * 8 + lane] = q.rayid[lane];
+                    ch[32 * 9 + lane] = q.owner[lane];
+                }
+            }
+            log_chunk = nxt;
+        }
         // every owner folds in its items, in march order
         {
             unsigned m = mine_lo;
@@ -428,15 +485,17 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
         const int rem = qn > 32 ? qn - 32 : 0;
         for (int b0 = 0; b0 < rem; b0 += 32) {
             const int i = b0 + lane;
-            uint32_t s_ = 0; float w_ = 0.f, T_ = 0.f, d_ = 0.f; unsigned char o_ = 0;
+            uint32_t s_ = 0; float w_ = 0.f, T_ = 0.f, d_ = 0.f; unsigned char o_ = 0; int r_ = 0;
             if (i < rem) {
                 s_ = q.slot[32 + i]; w_ = q.w[32 + i]; o_ = q.owner[32 + i];
-                if (BWD) { T_ = q.T[32 + i]; d_ = q.dd[32 + i]; }
+                if (BWD || LOG) { T_ = q.T[32 + i]; d_ = q.dd[32 + i]; }
+                if (LOG) r_ = q.rayid[32 + i];
             }
             __syncwarp();
             if (i < rem) {
                 q.slot[i] = s_; q.w[i] = w_; q.owner[i] = o_;
-                if (BWD) { q.T[i] = T_; q.dd[i] = d_; }
+                if (BWD || LOG) { q.T[i] = T_; q.dd[i] = d_; }
+                if (LOG) q.rayid[i] = r_;
             }
             __syncwarp();
         }
@@ -661,7 +720,8 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
             const int pos = qn + __popc(pushed & ((1u << lane) - 1u));
             q.slot[pos] = slot;
             q.w[pos] = weight;
-            if (BWD) { q.T[pos] = light; q.dd[pos] = dd; }
+            if (BWD || LOG) { q.T[pos] = light; q.dd[pos] = dd; }
+            if (LOG) q.rayid[pos] = (int)ray;
             q.owner[pos] = (unsigned char)(lane | (par << 5) | ((BWD && phase == 0) ? 0x80 : 0));
             if (pos < 32) mine_lo |= 1u << pos;
             else mine_hi |= 1ull << (pos - 32);
@@ -706,6 +766,11 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
             inflight = true;
             PROF_ADD(7);
         }
+    }
+    if (LOG && lane == 0 && log_chunk < log_capacity) {
+        int32_t* ch = log + kLogChunks + log_chunk * kLogChunkWords;
+        ch[0] = 0;    // end of this warp's list
+        ch[1] = -1;
     }
     PROF_END();
 }

@@ -7,6 +7,7 @@
 #include "render.cuh"
 #include "render_coop.cuh"
 #include "render_queue.cuh"
+#include "render_replay.cuh"
 
 namespace svoxb {
 
@@ -22,6 +23,9 @@ struct RenderCall {
     const float* fwd_out = nullptr;
     float* grad_data = nullptr;
     cudaStream_t stream = nullptr;
+    // item log (logged forward / replay backward)
+    int32_t* log = nullptr;
+    int64_t log_capacity = 0;
 };
 
 static int out_dim_of(const svoxb_tree* t, const svoxb_render_options& o) {
@@ -151,21 +155,45 @@ static int launch_queue_block(const RenderCall& c, const Source& src, const Tree
     const int64_t n_gran = (c.Q + 31) / 32;
     unsigned grid = 1;
     int st;
-    if (!c.backward) {
-        const size_t smem = top_bytes + (size_t)(BLOCK / 32) * sizeof(WarpQueue<K, false>);
+    if (!c.backward && c.log != nullptr) {
+        const size_t smem = top_bytes + (size_t)(BLOCK / 32) * sizeof(WarpQueue<K, kModeForwardLogged>);
+        auto k = render_queue_kernel<BD, BLOCK, kModeForwardLogged, Source>;
+        if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
+        if ((int64_t)grid * (BLOCK / 32) > kLogMaxLists) return SVOXB_ERR_TOO_LARGE;
+        k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, (int)top_bytes, c.Q, c.out,
+                                          nullptr, nullptr, nullptr, c.log, c.log_capacity);
+    } else if (!c.backward) {
+        const size_t smem = top_bytes + (size_t)(BLOCK / 32) * sizeof(WarpQueue<K, kModeForward>);
         auto k = render_queue_kernel<BD, BLOCK, kModeForward, Source>;
         if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
         k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, (int)top_bytes, c.Q, c.out,
-                                          nullptr, nullptr, nullptr);
+                                          nullptr, nullptr, nullptr, nullptr, 0);
     } else {
-        const size_t smem = top_bytes + (size_t)(BLOCK / 32) * sizeof(WarpQueue<K, true>);
+        const size_t smem = top_bytes + (size_t)(BLOCK / 32) * sizeof(WarpQueue<K, kModeBackward>);
         const bool single = c.fwd_out != nullptr && c.opt.sigma_thresh == 0.f &&
                             c.opt.stop_thresh == 0.f;
         auto k = render_queue_kernel<BD, BLOCK, kModeBackward, Source>;
         if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
         k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, (int)top_bytes, c.Q, nullptr,
-                                          c.grad_out, single ? c.fwd_out : nullptr, c.grad_data);
+                                          c.grad_out, single ? c.fwd_out : nullptr, c.grad_data,
+                                          nullptr, 0);
     }
+    SVOXB_CUDA(cudaGetLastError());
+    return SVOXB_OK;
+}
+
+template <int BD, class Source>
+static int launch_replay(const RenderCall& c, const Source& src) {
+    constexpr int K = 3 * BD + 1;
+    constexpr int BLOCK = 512;
+    const size_t smem = (size_t)(BLOCK / 32) * sizeof(ReplaySmem<K>);
+    auto k = render_replay_kernel<BD, BLOCK, Source>;
+    unsigned grid = 1;
+    int st;
+    if ((st = persistent_grid(k, BLOCK, smem, (int64_t)kLogMaxLists * 32, &grid))) return st;
+    SVOXB_CUDA(cudaMemsetAsync(c.log + 1, 0, sizeof(int32_t), c.stream));  // replay work counter
+    k<<<grid, BLOCK, smem, c.stream>>>(tree_args(c.tree), src, c.opt, c.log, c.grad_out, c.fwd_out,
+                                      c.grad_data, c.log_capacity);
     SVOXB_CUDA(cudaGetLastError());
     return SVOXB_OK;
 }
@@ -211,7 +239,9 @@ static int launch_queue(const RenderCall& c, const Source& src) {
     tr.child = scratch.annotated;
     const TopTable top{scratch.table, scratch.level};
     const size_t top_bytes = 0;  // the leaf table stays in global memory
-    const size_t per_warp = c.backward ? sizeof(WarpQueue<K, true>) : sizeof(WarpQueue<K, false>);
+    const size_t per_warp = c.backward ? sizeof(WarpQueue<K, kModeBackward>)
+                            : c.log    ? sizeof(WarpQueue<K, kModeForwardLogged>)
+                                       : sizeof(WarpQueue<K, kModeForward>);
     int want = g_tuning.render_block > 0 ? g_tuning.render_block : 768;
     while (want > 256 && top_bytes + (size_t)(want / 32) * per_warp + 64 > kMaxSmem) want -= 128;
     if constexpr (BD <= 9) {
@@ -420,6 +450,139 @@ int svoxb_volume_render_image_backward(const svoxb_tree* tree, const svoxb_camer
     c.grad_data = grad_data_out;
     c.stream = (cudaStream_t)stream;
     return render_dispatch(c, PixelRays{cam->c2w, cam->fx, cam->fy, cam->width, cam->height});
+}
+
+}  // extern "C"
+
+// Whether a call can take the logged forward / replay backward pair.
+static int log_eligible(const svoxb_tree* t, const svoxb_render_options* o, const float* grad) {
+    if (o->format != SVOXB_FORMAT_SH || t->K != 3 * o->basis_dim + 1 || t->N != 2)
+        return SVOXB_ERR_FORMAT;
+    if (o->sigma_thresh != 0.f || o->stop_thresh != 0.f || o->density_softplus)
+        return SVOXB_ERR_OPTION;
+    if (t->M >= (1LL << 28)) return SVOXB_ERR_TOO_LARGE;
+    if (t->K % 4 == 0 && ((uintptr_t)t->data % 16 != 0 || (uintptr_t)grad % 16 != 0))
+        return SVOXB_ERR_FORMAT;
+    return SVOXB_OK;
+}
+
+template <class Source>
+static int logged_forward(const svoxb_tree* tree, const Source& src, int64_t Q,
+                          const svoxb_render_options* opt, float* out, int32_t* log,
+                          int64_t capacity_chunks, void* stream) {
+    int st = validate_tree(tree);
+    if (st) return st;
+    if ((st = validate_options(tree, *opt))) return st;
+    if ((st = log_eligible(tree, opt, nullptr))) return st;
+    if (!log || capacity_chunks < 1 || Q < 0) return SVOXB_ERR_SHAPE;
+    if (Q > 0 && !out) return SVOXB_ERR_NULL;
+    SVOXB_CUDA(cudaMemsetAsync(log, 0, kLogHeads * sizeof(int32_t), (cudaStream_t)stream));
+    if (Q == 0) return SVOXB_OK;
+    RenderCall c{tree, *opt, Q};
+    c.out = out;
+    c.stream = (cudaStream_t)stream;
+    c.log = log;
+    c.log_capacity = capacity_chunks;
+    switch (opt->basis_dim) {
+        case 1: return launch_queue<1>(c, src);
+        case 4: return launch_queue<4>(c, src);
+        case 9: return launch_queue<9>(c, src);
+        case 16: return launch_queue<16>(c, src);
+        case 25: return launch_queue<25>(c, src);
+    }
+    return SVOXB_ERR_FORMAT;
+}
+
+template <class Source>
+static int replay_backward(const svoxb_tree* tree, const Source& src, int64_t Q,
+                           const svoxb_render_options* opt, const float* grad_output,
+                           const float* fwd_out, int32_t* log, int64_t capacity_chunks,
+                           float* grad_data_out, int zero_first, void* stream) {
+    int st = validate_tree(tree);
+    if (st) return st;
+    if ((st = validate_options(tree, *opt))) return st;
+    if (!grad_data_out || !log) return SVOXB_ERR_NULL;
+    if ((st = log_eligible(tree, opt, grad_data_out))) return st;
+    if (zero_first && (st = zero_grad(tree, grad_data_out, tree->K, (cudaStream_t)stream)))
+        return st;
+    if (Q == 0) return SVOXB_OK;
+    if (!grad_output || !fwd_out) return SVOXB_ERR_NULL;
+    RenderCall c{tree, *opt, Q};
+    c.backward = true;
+    c.grad_out = grad_output;
+    c.fwd_out = fwd_out;
+    c.grad_data = grad_data_out;
+    c.stream = (cudaStream_t)stream;
+    c.log = log;
+    c.log_capacity = capacity_chunks;
+    switch (opt->basis_dim) {
+        case 1: return launch_replay<1>(c, src);
+        case 4: return launch_replay<4>(c, src);
+        case 9: return launch_replay<9>(c, src);
+        case 16: return launch_replay<16>(c, src);
+        case 25: return launch_replay<25>(c, src);
+    }
+    return SVOXB_ERR_FORMAT;
+}
+
+extern "C" {
+
+int64_t svoxb_item_log_words(int64_t capacity_chunks) {
+    return (int64_t)kLogChunks + capacity_chunks * kLogChunkWords;
+}
+
+int svoxb_volume_render_logged(const svoxb_tree* tree, const svoxb_rays* rays,
+                               const svoxb_render_options* opt, float* out, int32_t* log,
+                               int64_t capacity_chunks, void* stream) {
+    if (!tree || !rays || !opt) return SVOXB_ERR_NULL;
+    if (rays->Q > 0 && (!rays->origins || !rays->dirs || !rays->vdirs)) return SVOXB_ERR_NULL;
+    return logged_forward(tree, RayBatch{rays->origins, rays->dirs, rays->vdirs}, rays->Q, opt,
+                          out, log, capacity_chunks, stream);
+}
+
+int svoxb_volume_render_image_logged(const svoxb_tree* tree, const svoxb_camera* cam,
+                                     const svoxb_render_options* opt, float* out, int32_t* log,
+                                     int64_t capacity_chunks, void* stream) {
+    if (!tree || !cam || !opt || !cam->c2w) return SVOXB_ERR_NULL;
+    if (cam->width < 0 || cam->height < 0) return SVOXB_ERR_SHAPE;
+    return logged_forward(tree, PixelRays{cam->c2w, cam->fx, cam->fy, cam->width, cam->height},
+                          (int64_t)cam->width * cam->height, opt, out, log, capacity_chunks,
+                          stream);
+}
+
+int svoxb_volume_render_backward_replay(const svoxb_tree* tree, const svoxb_rays* rays,
+                                        const svoxb_render_options* opt,
+                                        const float* grad_output, const float* fwd_out,
+                                        int32_t* log, int64_t capacity_chunks,
+                                        float* grad_data_out, int zero_first, void* stream) {
+    if (!tree || !rays || !opt) return SVOXB_ERR_NULL;
+    if (rays->Q > 0 && (!rays->origins || !rays->dirs || !rays->vdirs)) return SVOXB_ERR_NULL;
+    return replay_backward(tree, RayBatch{rays->origins, rays->dirs, rays->vdirs}, rays->Q, opt,
+                           grad_output, fwd_out, log, capacity_chunks, grad_data_out, zero_first,
+                           stream);
+}
+
+int svoxb_volume_render_image_backward_replay(const svoxb_tree* tree, const svoxb_camera* cam,
+                                              const svoxb_render_options* opt,
+                                              const float* grad_output, const float* fwd_out,
+                                              int32_t* log, int64_t capacity_chunks,
+                                              float* grad_data_out, int zero_first,
+                                              void* stream) {
+    if (!tree || !cam || !opt || !cam->c2w) return SVOXB_ERR_NULL;
+    if (cam->width < 0 || cam->height < 0) return SVOXB_ERR_SHAPE;
+    return replay_backward(tree, PixelRays{cam->c2w, cam->fx, cam->fy, cam->width, cam->height},
+                           (int64_t)cam->width * cam->height, opt, grad_output, fwd_out, log,
+                           capacity_chunks, grad_data_out, zero_first, stream);
+}
+
+int svoxb_item_log_used(const int32_t* log, int64_t* chunks_used, void* stream) {
+    if (!log || !chunks_used) return SVOXB_ERR_NULL;
+    int32_t used = 0;
+    SVOXB_CUDA(cudaMemcpyAsync(&used, log, sizeof(int32_t), cudaMemcpyDeviceToHost,
+                               (cudaStream_t)stream));
+    SVOXB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    *chunks_used = used;
+    return SVOXB_OK;
 }
 
 int svoxb_march_stats(const svoxb_tree* tree, const svoxb_rays* rays,

@@ -18,6 +18,11 @@ from .formats import DataFormat
 __all__ = ["VolumeRenderer", "NDCConfig", "Rays", "_VolumeRenderFunction",
            "_VolumeRenderImageFunction"]
 
+# When the tree's data requires grad, the forward records its contributing
+# samples so that the backward replays them instead of marching again (costs
+# memory: about 40 bytes per contributing sample until the backward has run).
+USE_ITEM_LOG = True
+
 NDCConfig = namedtuple("NDCConfig", ["width", "height", "focal"])
 Rays = namedtuple("Rays", ["origins", "dirs", "viewdirs"])
 
@@ -53,8 +58,13 @@ class _VolumeRenderFunction(autograd.Function):
 
     @staticmethod
     def forward(ctx, data, tree, rays, opt):
-        out = _C.volume_render(tree, rays, opt)
         ctx.tree, ctx.rays, ctx.opt = tree, rays, opt
+        ctx.log = None
+        if data.requires_grad and USE_ITEM_LOG and _C.log_eligible(tree, opt):
+            # training step: record the contributing samples for the backward pass
+            out, ctx.log = _C.volume_render_logged(tree, rays, opt)
+        else:
+            out = _C.volume_render(tree, rays, opt)
         ctx.fwd = (out, data._version) if _single_march_ok(opt) else None
         return out
 
@@ -65,7 +75,14 @@ class _VolumeRenderFunction(autograd.Function):
         fwd = None
         if ctx.fwd is not None and ctx.fwd[1] == ctx.tree.data._version:
             fwd = ctx.fwd[0]
-        return _C.volume_render_backward(ctx.tree, ctx.rays, ctx.opt, grad_out.contiguous(),
+        grad_out = grad_out.contiguous()
+        if fwd is not None and ctx.log is not None:
+            grad = _C.volume_render_backward_replay(ctx.tree, ctx.rays, ctx.opt, grad_out, fwd,
+                                                    ctx.log)
+            ctx.log = None
+            if grad is not None:
+                return grad, None, None, None
+        return _C.volume_render_backward(ctx.tree, ctx.rays, ctx.opt, grad_out,
                                          fwd), None, None, None
 
 
@@ -74,8 +91,12 @@ class _VolumeRenderImageFunction(autograd.Function):
 
     @staticmethod
     def forward(ctx, data, tree, cam, opt):
-        out = _C.volume_render_image(tree, cam, opt)
         ctx.tree, ctx.cam, ctx.opt = tree, cam, opt
+        ctx.log = None
+        if data.requires_grad and USE_ITEM_LOG and _C.log_eligible(tree, opt):
+            out, ctx.log = _C.volume_render_logged(tree, cam, opt, image=True)
+        else:
+            out = _C.volume_render_image(tree, cam, opt)
         ctx.fwd = (out, data._version) if _single_march_ok(opt) else None
         return out
 
@@ -86,8 +107,15 @@ class _VolumeRenderImageFunction(autograd.Function):
         fwd = None
         if ctx.fwd is not None and ctx.fwd[1] == ctx.tree.data._version:
             fwd = ctx.fwd[0]
-        return _C.volume_render_image_backward(ctx.tree, ctx.cam, ctx.opt,
-                                               grad_out.contiguous(), fwd), None, None, None
+        grad_out = grad_out.contiguous()
+        if fwd is not None and ctx.log is not None:
+            grad = _C.volume_render_backward_replay(ctx.tree, ctx.cam, ctx.opt, grad_out, fwd,
+                                                    ctx.log, image=True)
+            ctx.log = None
+            if grad is not None:
+                return grad, None, None, None
+        return _C.volume_render_image_backward(ctx.tree, ctx.cam, ctx.opt, grad_out,
+                                               fwd), None, None, None
 
 
 class VolumeRenderer(nn.Module):

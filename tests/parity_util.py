@@ -38,7 +38,18 @@ def options_of(case):
 
 
 # ---------------------------------------------------------------------------
-def run_product(case, device="cuda:0", backward=True, single_march=True):
+def run_product(case, device="cuda:0", backward=True, single_march=True, item_log=True):
+    """``item_log=False`` makes the backward march the rays (one march if
+    ``single_march``) instead of replaying the forward's item log."""
+    from svox_b200 import render as _render
+    _render.USE_ITEM_LOG = bool(item_log)
+    try:
+        return _run_product(case, device, backward, single_march)
+    finally:
+        _render.USE_ITEM_LOG = True
+
+
+def _run_product(case, device, backward, single_march):
     tree = case["tree"].to(device)
     tree.zero_grad(set_to_none=True)
     res = {"ids": None, "grad": None}

@@ -72,6 +72,39 @@ def test_two_march_backward_matches_single_march(name, cuda_device):
     assert P.grad_excess(a, b, orc["grad_abs"], GRAD_TOL_REF) <= 2.5
 
 
+@pytest.mark.parametrize("name", ["c1_rays", "shell_sh9_rays", "shell_sh16_image", "aniso_rays",
+                                  "aniso_image", "sh1_rays", "sh25_rays", "opt_comp_range"])
+def test_replay_backward_matches_marching_backward(name, cuda_device):
+    # With gradients enabled the forward logs its contributing samples and the
+    # backward replays the log; the marching backward must give the same gradient.
+    case = CASES[name]()
+    a = P.run_product(case, cuda_device, item_log=True)
+    b = P.run_product(case, cuda_device, item_log=False)
+    assert np.array_equal(a["out"], b["out"])          # logging does not change the render
+    orc = P.run_oracle(case)
+    assert P.grad_excess(a["grad"], orc["grad"], orc["grad_abs"], GRAD_TOL_ORACLE) <= 1.0
+    assert P.grad_excess(a["grad"], b["grad"], orc["grad_abs"], GRAD_TOL_REF) <= 2.5
+
+
+def test_item_log_overflow_falls_back(cuda_device):
+    # A log that is too small must not be replayed: the backward marches instead.
+    case = CASES["shell_sh9_rays"]()
+    old = csrc._items_per_ray
+    try:
+        csrc._items_per_ray = 0.0
+        slack = csrc._LOG_LIST_SLACK
+        csrc._LOG_LIST_SLACK = 64                       # far fewer chunks than needed
+        a = P.run_product(case, cuda_device)
+        csrc._LOG_LIST_SLACK = slack
+        assert csrc._items_per_ray > 1.0                # the estimate was raised for next time
+        b = P.run_product(case, cuda_device, item_log=False)
+        orc = P.run_oracle(case)
+        assert P.grad_excess(a["grad"], b["grad"], orc["grad_abs"], GRAD_TOL_REF) <= 2.5
+    finally:
+        csrc._items_per_ray = old
+        csrc._LOG_LIST_SLACK = slack
+
+
 def test_toy_example_known_answer(cuda_device):
     # docs/source/ex_opt_toy.py of the reference, first printed line
     t = svox.N3Tree(device=cuda_device, data_format="SH1")
