@@ -135,11 +135,16 @@ int svoxb_volume_render_image_backward(const svoxb_tree* tree, const svoxb_camer
 /* Logged forward + replay backward (no counterpart in the reference; the
  * pair computes what volume_render followed by volume_render_backward
  * computes, svox/csrc/rt_kernel.cu:1019-1083).  The logged forward also
- * writes every contributing sample (leaf slot, weight, transmittance, step,
- * colour sigmoids, ray) into `log`, a caller-allocated int32 device buffer of
- * svoxb_item_log_words(capacity_chunks) words (one chunk = 32 samples).  The
- * replay backward streams that log instead of marching the rays and reading
- * the leaf records again.  Only for octrees with SH colour in three channels,
+ * writes every contributing sample (leaf slot, ray, weight, transmittance,
+ * step, colour sigmoids, the ray's colour sums so far) into `log`, a
+ * caller-allocated int32 device buffer of svoxb_item_log_words(capacity_chunks)
+ * words (one chunk = 32 samples).  The replay backward streams that log instead
+ * of marching the rays and reading the leaf records again: it sorts the
+ * samples by leaf range (scratch from the stream's memory pool, 32 bytes per
+ * sample of `chunks_used` chunks; pass what svoxb_item_log_used reported, or 0
+ * for capacity_chunks) and reduces the gradient range by range so that it
+ * stays in L2.  If that scratch cannot be had it marches like
+ * svoxb_volume_render_backward.  Only for octrees with SH colour in three channels,
  * sigma_thresh = stop_thresh = 0 and no density_softplus (else
  * SVOXB_ERR_FORMAT / SVOXB_ERR_OPTION).  If the log was too small
  * (svoxb_item_log_used reports more chunks than capacity_chunks) the log must
@@ -156,13 +161,14 @@ int svoxb_volume_render_backward_replay(const svoxb_tree* tree, const svoxb_rays
                                         const svoxb_render_options* opt,
                                         const float* grad_output, const float* fwd_out,
                                         int32_t* log, int64_t capacity_chunks,
-                                        float* grad_data_out, int zero_first, void* stream);
+                                        int64_t chunks_used, float* grad_data_out,
+                                        int zero_first, void* stream);
 int svoxb_volume_render_image_backward_replay(const svoxb_tree* tree, const svoxb_camera* cam,
                                               const svoxb_render_options* opt,
                                               const float* grad_output, const float* fwd_out,
                                               int32_t* log, int64_t capacity_chunks,
-                                              float* grad_data_out, int zero_first,
-                                              void* stream);
+                                              int64_t chunks_used, float* grad_data_out,
+                                              int zero_first, void* stream);
 /* Chunks the logged forward needed (synchronises `stream`). */
 int svoxb_item_log_used(const int32_t* log, int64_t* chunks_used, void* stream);
 
@@ -218,7 +224,9 @@ const char* svoxb_last_cuda_error(void);
  * size (256 or 1024, 0 = automatic), key 1 = cap on the render jump-table
  * level (-1 = automatic), key 2 = cap on the query jump-table level, key 3 =
  * render algorithm (2 = item queue, the default; 0 = warp-cooperative; 1 = one
- * thread per ray). */
+ * thread per ray), key 5 = MB of gradient one bin of the replay backward spans
+ * (default 16), key 6 = L2 hint bits of the replay scatter (1 = packets
+ * evict-first, 2 = gradient evict-last; default 3). */
 int svoxb_tune(int key, int value);
 
 /* Library version, "major.minor.patch". */

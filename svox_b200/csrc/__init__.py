@@ -385,7 +385,7 @@ def volume_render_backward_replay(tree, rays_or_cam, opt, grad_output, fwd_out, 
         with _timed("volume_render_backward"):
             st = fn(C.byref(ct), C.byref(cs), C.byref(co), C.c_void_p(grad_output.data_ptr()),
                     C.c_void_p(fwd_out.data_ptr()), C.c_void_p(log.data_ptr()), C.c_int64(cap),
-                    C.c_void_p(grad.data_ptr()), C.c_int(0), _stream())
+                    C.c_int64(used), C.c_void_p(grad.data_ptr()), C.c_int(0), _stream())
     if st:
         _raise(st, "volume_render_backward_replay")
     return grad

@@ -147,6 +147,8 @@ struct Tuning {
     int render_top_level = -1;  // -1 = automatic
     int query_top_level = -1;
     int render_algo = 2;        // 2 = item queue, 0 = warp-cooperative, 1 = one thread per ray
+    int replay_bin_mb = 16;     // gradient bytes one replay bin spans
+    int replay_flags = 3;       // replay scatter: 1 = packets evict-first, 2 = gradient evict-last
 };
 extern Tuning g_tuning;
 

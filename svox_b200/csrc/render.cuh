@@ -160,6 +160,13 @@ struct RayBatch {  // render_ray_kernel's inputs (svox/csrc/rt_kernel.cu:717-733
         r.vdir[1] = __ldg(vdirs + 3 * i + 1);
         r.vdir[2] = __ldg(vdirs + 3 * i + 2);
     }
+    // The view direction alone (colour basis of the backward's gradient records).
+    __device__ __forceinline__ void load_vdir(int64_t i, const TreeArgs&,
+                                              const svoxb_render_options&, float v[3]) const {
+        v[0] = __ldg(vdirs + 3 * i + 0);
+        v[1] = __ldg(vdirs + 3 * i + 1);
+        v[2] = __ldg(vdirs + 3 * i + 2);
+    }
 };
 
 struct PixelRays {  // render_image_kernel's inputs (svox/csrc/rt_kernel.cu:758-819)
@@ -212,6 +219,12 @@ struct PixelRays {  // render_image_kernel's inputs (svox/csrc/rt_kernel.cu:758-
         r.oy = to_tree(o[1], __ldg(tr.offset + 1), __ldg(tr.scaling + 1));
         r.oz = to_tree(o[2], __ldg(tr.offset + 2), __ldg(tr.scaling + 2));
         r.dx = d[0]; r.dy = d[1]; r.dz = d[2];
+    }
+    __device__ __forceinline__ void load_vdir(int64_t i, const TreeArgs& tr,
+                                              const svoxb_render_options& opt, float v[3]) const {
+        Ray r;
+        load(i, tr, opt, r);
+        v[0] = r.vdir[0]; v[1] = r.vdir[1]; v[2] = r.vdir[2];
     }
 };
 

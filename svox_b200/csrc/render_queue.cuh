@@ -59,18 +59,23 @@ constexpr int kModeForwardLogged = 2;  // forward that also records its items fo
 // Item log: what a logged forward leaves behind so that the backward pass can
 // replay the contributing samples without marching again and without reading
 // the leaf records a second time.  int32 words:
-//   [0] chunks allocated   [1] replay work counter   [2] number of chunk lists
-//   [kLogHeads + i]        first chunk of list i (one list per forward warp)
-//   chunk c at kLogChunks + c * kLogChunkWords: 10 rows of 32 words,
-//     row 0: word 0 = items in the chunk (0 ends the list), word 1 = next chunk
-//     rows 1-9, one word per item: slot, weight, T after, delta_t*delta_scale,
-//     sigmoid of the three channels, ray index, owner lane | parity << 5
-// A ray's items appear in march order within its list, which is all the
-// backward's sequential per-ray bookkeeping needs.
+//   [0] chunks allocated   [2] bin shift   [3] number of bins
+//   [kLogHeads + b]        items whose leaf slot falls into bin b (= slot >> shift)
+//   chunk c at kLogChunks + c * kLogChunkWords: 12 rows of 32 words,
+//     row 0: word 0 = items in the chunk
+//     rows 1-11, one word per item: slot, ray, weight, T after, delta_t*delta_scale,
+//     sigmoid of the three channels, colour sums of the ray up to and including
+//     the item (three channels)
+// With the partial colour sums every item is self-contained: the reference's
+// running `accum` after item k (svox/csrc/rt_kernel.cu:462-471) equals
+// <grad_out, out> - <grad_out, partial sums>, so the backward can take the
+// items in any order.
 constexpr int kLogHeads = 32;
-constexpr int kLogMaxLists = 16384;
-constexpr int kLogChunks = kLogHeads + kLogMaxLists;
-constexpr int kLogChunkWords = 320;
+constexpr int kMaxBins = 1024;
+constexpr int kLogChunks = kLogHeads + kMaxBins;
+constexpr int kLogRows = 12;
+constexpr int kLogChunkWords = kLogRows * 32;
+constexpr int kLogGrab = 8;  // chunks a warp takes per bump of the allocation counter
 
 constexpr int kCoordBits = 24;  // integer coordinates: floor(x * 2^24), exact for float x < 1
 constexpr int kPathLevels = 6;  // cached ancestors from the table level down
@@ -200,7 +205,7 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                     int top_bytes, int64_t Q, float* __restrict__ out,
                     const float* __restrict__ grad_out, const float* __restrict__ fwd_out,
                     float* __restrict__ grad_data, int32_t* __restrict__ log,
-                    int64_t log_capacity) {
+                    int64_t log_capacity, int log_shift) {
     constexpr int K = 3 * BD + 1;
     constexpr bool BWD = MODE == kModeBackward;
     constexpr bool LOG = MODE == kModeForwardLogged;
@@ -209,7 +214,15 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
     static_assert(Shape::STRIDE >= 3, "result words live in the staging row");
     extern __shared__ __align__(16) unsigned char s_raw[];
     __shared__ unsigned s_next;
+    __shared__ int s_hist[LOG ? kMaxBins : 1];  // logged forward: items per bin
     if (threadIdx.x == 0) s_next = 0;
+    if (LOG) {
+        for (int i = threadIdx.x; i < kMaxBins; i += BLOCK) s_hist[i] = 0;
+        if (blockIdx.x == 0 && threadIdx.x == 0) {
+            log[2] = log_shift;
+            log[3] = (int)(((tr.M * 8 - 1) >> log_shift) + 1);
+        }
+    }
     const TopTable top = topg;  // leaf table in global memory (top_bytes is 0)
     __syncthreads();
 
@@ -256,19 +269,9 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
     unsigned long long mine_hi = 0ull;  // ... among [32, 96)
     int qn = 0;                         // queued items (warp-uniform)
     bool inflight = false;              // records of items [0, 32) have been requested
-    // logged forward: the chunk the next batch goes to (allocated one ahead, so that a
-    // chunk can name its successor when it is written)
+    // logged forward: the warp takes kLogGrab chunks at a time from the log
     int64_t log_chunk = 0;
-    if (LOG) {
-        int c = 0;
-        if (lane == 0) {
-            c = atomicAdd(log, 1);
-            const int list = blockIdx.x * (BLOCK / 32) + (threadIdx.x >> 5);
-            log[kLogHeads + list] = c;
-            if (list == 0) log[2] = gridDim.x * (BLOCK / 32);
-        }
-        log_chunk = __shfl_sync(0xffffffffu, c, 0);
-    }
+    int log_left = 0;
 
     // Places the cursor for the sample at parameter t, reusing the deepest cached
     // ancestor shared with the previous sample (valid down to level `deepest`).
@@ -367,27 +370,6 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
             }
         }
         __syncwarp();
-        if (LOG) {
-            int nxt = 0;
-            if (lane == 0) nxt = atomicAdd(log, 1);
-            nxt = __shfl_sync(0xffffffffu, nxt, 0);
-            if (log_chunk < log_capacity) {
-                int32_t* ch = log + kLogChunks + log_chunk * kLogChunkWords;
-                if (lane == 0) { ch[0] = nb; ch[1] = nxt; }
-                if (lane < nb) {
-                    ch[32 * 1 + lane] = (int32_t)q.slot[lane];
-                    ch[32 * 2 + lane] = __float_as_int(q.w[lane]);
-                    ch[32 * 3 + lane] = __float_as_int(q.T[lane]);
-                    ch[32 * 4 + lane] = __float_as_int(q.dd[lane]);
-                    ch[32 * 5 + lane] = __float_as_int(sg[0]);
-                    ch[32 * 6 + lane] = __float_as_int(sg[1]);
-                    ch[32 * 7 + lane] = __float_as_int(sg[2]);
-                    ch[32 * 8 + lane] = q.rayid[lane];
-                    ch[32 * 9 + lane] = q.owner[lane];
-                }
-            }
-            log_chunk = nxt;
-        }
         // every owner folds in its items, in march order
         {
             unsigned m = mine_lo;
@@ -401,11 +383,13 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                 if (!BWD) {
                     if (is_cur) {
                         a0 += wk * res[0]; a1 += wk * res[1]; a2 += wk * res[2];
+                        if (LOG) { res[0] = a0; res[1] = a1; res[2] = a2; }
                         --cnt_cur;
                     } else {
                         float o0 = q.oldv[lane][0], o1 = q.oldv[lane][1], o2 = q.oldv[lane][2];
                         o0 += wk * res[0]; o1 += wk * res[1]; o2 += wk * res[2];
                         q.oldv[lane][0] = o0; q.oldv[lane][1] = o1; q.oldv[lane][2] = o2;
+                        if (LOG) { res[0] = o0; res[1] = o1; res[2] = o2; }
                         --cnt_old;
                     }
                 } else {
@@ -430,6 +414,39 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                               q.oldv[lane][3], q.oldstop[lane] != 0);
                 old_valid = false;
             }
+        }
+        if (LOG) {
+            __syncwarp();
+            // lane i writes item i, now with its ray's colour sums, into the log
+            if (log_left == 0) {
+                int c = 0;
+                if (lane == 0) c = atomicAdd(log, kLogGrab);
+                log_chunk = __shfl_sync(0xffffffffu, c, 0);
+                log_left = kLogGrab;
+            }
+            if (log_chunk < log_capacity) {
+                int32_t* ch = log + kLogChunks + log_chunk * kLogChunkWords;
+                if (lane == 0) ch[0] = nb;
+                if (lane < nb) {
+                    const float* res = q.rows + lane * Shape::STRIDE;
+                    const uint32_t sl = q.slot[lane];
+                    ch[32 * 1 + lane] = (int32_t)sl;
+                    ch[32 * 2 + lane] = q.rayid[lane];
+                    ch[32 * 3 + lane] = __float_as_int(q.w[lane]);
+                    ch[32 * 4 + lane] = __float_as_int(q.T[lane]);
+                    ch[32 * 5 + lane] = __float_as_int(q.dd[lane]);
+                    ch[32 * 6 + lane] = __float_as_int(sg[0]);
+                    ch[32 * 7 + lane] = __float_as_int(sg[1]);
+                    ch[32 * 8 + lane] = __float_as_int(sg[2]);
+                    ch[32 * 9 + lane] = __float_as_int(res[0]);
+                    ch[32 * 10 + lane] = __float_as_int(res[1]);
+                    ch[32 * 11 + lane] = __float_as_int(res[2]);
+                    const uint32_t bin = sl >> log_shift;
+                    atomicAdd(&s_hist[bin < (uint32_t)kMaxBins ? bin : kMaxBins - 1], 1);
+                }
+            }
+            ++log_chunk;
+            --log_left;
         }
         if (BWD) {
             __syncwarp();
@@ -767,10 +784,13 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
             PROF_ADD(7);
         }
     }
-    if (LOG && lane == 0 && log_chunk < log_capacity) {
-        int32_t* ch = log + kLogChunks + log_chunk * kLogChunkWords;
-        ch[0] = 0;    // end of this warp's list
-        ch[1] = -1;
+    if (LOG) {
+        // chunks taken but not used hold no items
+        if (lane < log_left && log_chunk + lane < log_capacity)
+            log[kLogChunks + (log_chunk + lane) * kLogChunkWords] = 0;
+        __syncthreads();
+        for (int i = threadIdx.x; i < kMaxBins; i += BLOCK)
+            if (s_hist[i] != 0) atomicAdd(log + kLogHeads + i, s_hist[i]);
     }
     PROF_END();
 }

@@ -1,170 +1,299 @@
 // Backward pass by replay of the forward's item log (see render_queue.cuh for
 // the log layout).
 //
-// The logged forward has already found every contributing sample and
-// evaluated its colour sigmoids.  The backward therefore neither marches nor
-// reads a leaf record: it streams the log (coalesced 128-byte rows), redoes
-// the reference's per-ray bookkeeping in log order
-// (svox/csrc/rt_kernel.cu:386-411, 462-471 with `accum` started from
-// <grad_out, fwd_out>), and scatters one gradient record per item with
-// red.global.add.v4.f32.  What remains is the HBM traffic of the gradient
-// itself.
+// The logged forward has already found every contributing sample, evaluated
+// its colour sigmoids and recorded the ray's colour sums up to the sample, so
+// the backward neither marches nor reads a leaf record, and every item can be
+// handled on its own: with g = grad_out[ray],
+//   total_color = <g, colour of the sample>
+//   accum       = <g, out[ray]> - <g, colour sums up to and including the sample>
+//   d/d sigma   = delta * (total_color * T - accum)          (rt_kernel.cu:462-471)
+//   d/d coef    = basis[i] * weight * sg (1 - sg) * g[ch] * (1 + 2 pad)   (:386-392)
+// What is left is adding one K-float record per item into `grad_data`.  Done in
+// ray order that is the whole cost: every leaf is touched ~8 times per launch
+// by rays far apart in time, each touch misses L2 and becomes a 32-byte
+// read-modify-write in HBM (20 GB for the benchmark scene).  So the replay
+// sorts first:
 //
-// One warp replays one chunk list (= the items one forward warp produced, in
-// order).  Lane i handles item i of a chunk; the lane recorded as the item's
-// owner keeps the running `accum` of that item's ray (two rays per owner can
-// interleave, told apart by the parity bit).
+//   prefix   turns the forward's histogram of items per BIN (a bin = a range of
+//            leaf slots whose gradient spans a few MB) into bin offsets;
+//   bin      streams the log; lane i turns item i into a 32-byte packet (slot,
+//            the three colour factors, the density gradient, the ray's view
+//            direction) and appends it to its bin.  A block reserves room for the packets of 16 chunks at a
+//            time, so the bin cursors see one atomic per bin and block step;
+//   scatter  walks the packets bin after bin: all SMs work on the same few bins
+//            at a time, so the gradient lines they reduce into stay in L2 and
+//            reach HBM once.  Lane i expands packet i to its K-float record in a
+//            shared-memory row; groups of lanes flush the rows with
+//            red.global.add.v4.f32.
 #pragma once
 
 #include "render_queue.cuh"
 
 namespace svoxb {
 
+constexpr int kCursorStride = 32;
+constexpr int kScatterUnit = 2048;  // packets a block of the scatter kernel takes at a time
+
+struct ReplayBins {
+    int32_t* cursor;      // [kMaxBins * kCursorStride] append cursors (one per 128-byte line)
+    int32_t* offset;      // [kMaxBins + 1] exclusive prefix of the histogram
+    // packets: 32 bytes each {slot, f0, f1, f2 | gs, view direction}; a packet nobody wrote
+    // is told by its position (see the scatter kernel)
+    int64_t capacity;
+    int4* packet;   // [capacity * 2]
+    int64_t* work;  // scatter work counter, zero at start
+    const float4* rays;  // [3 per ray] {g0,g1,g2,out0} {out1,out2,v0,v1} {v2,-,-,-}
+};
+
+// One block: exclusive prefix of the forward's histogram.
+__global__ void replay_prefix_kernel(const int32_t* __restrict__ log, ReplayBins b) {
+    __shared__ int s[kMaxBins];
+    int n_bins = log[3];
+    if (n_bins < 0) n_bins = 0;
+    if (n_bins > kMaxBins) n_bins = kMaxBins;
+    for (int i = threadIdx.x; i < kMaxBins; i += blockDim.x) {
+        s[i] = i < n_bins ? log[kLogHeads + i] : 0;
+        b.cursor[i * kCursorStride] = 0;
+    }
+    if (threadIdx.x == 0) *b.work = 0;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int64_t run = 0;
+        for (int i = 0; i < kMaxBins; ++i) {
+            b.offset[i] = (int)(run < b.capacity ? run : b.capacity);
+            run += s[i] > 0 ? s[i] : 0;
+        }
+        b.offset[kMaxBins] = (int)(run < b.capacity ? run : b.capacity);
+    }
+}
+
+// Per-ray inputs of the bin pass, packed so that one item needs three 16-byte
+// loads instead of nine 4-byte ones.
+template <class Source>
+__global__ void replay_pack_rays_kernel(TreeArgs tr, Source src, svoxb_render_options opt,
+                                        const float* __restrict__ grad_out,
+                                        const float* __restrict__ fwd_out, int64_t n_rays,
+                                        float4* __restrict__ rays) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_rays) return;
+    float v[3];
+    src.load_vdir(i, tr, opt, v);
+    rays[3 * i] = make_float4(grad_out[3 * i], grad_out[3 * i + 1], grad_out[3 * i + 2],
+                              fwd_out[3 * i]);
+    rays[3 * i + 1] = make_float4(fwd_out[3 * i + 1], fwd_out[3 * i + 2], v[0], v[1]);
+    rays[3 * i + 2] = make_float4(v[2], 0.f, 0.f, 0.f);
+}
+
+template <int BLOCK, int CPW, int MINB>   // CPW: chunks per warp and block step
+__global__ void __launch_bounds__(BLOCK, MINB)
+replay_bin_kernel(svoxb_render_options opt, const int32_t* __restrict__ log, int64_t n_chunks,
+                  int64_t n_rays, ReplayBins b) {
+    constexpr int WARPS = BLOCK / 32;
+    __shared__ int s_cnt[kMaxBins];   // packets of this block step per bin, then their base
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float d_rgb_pad = 1 + 2 * opt.rgb_padding;
+    const int shift = log[2];
+    int n_bins = log[3];
+    if (n_bins > kMaxBins) n_bins = kMaxBins;
+    const int64_t n_steps = (n_chunks + WARPS * CPW - 1) / (WARPS * CPW);
+
+    for (int64_t step = blockIdx.x; step < n_steps; step += gridDim.x) {
+        for (int i = threadIdx.x; i < n_bins; i += BLOCK) s_cnt[i] = 0;
+        __syncthreads();
+        int bin[CPW], rank[CPW];
+        int32_t slot[CPW], ray[CPW];
+        float f[CPW][3], gs[CPW], vd[CPW][3];
+#pragma unroll
+        for (int j = 0; j < CPW; ++j) {
+            bin[j] = -1;
+            const int64_t c = (step * WARPS + warp) * CPW + j;
+            int n = 0;
+            const int32_t* __restrict__ ch = log + kLogChunks + c * kLogChunkWords;
+            if (c < n_chunks) n = ch[0];
+            if (lane < n && n <= 32) {
+                slot[j] = ch[32 * 1 + lane];
+                ray[j] = ch[32 * 2 + lane];
+                const uint32_t bb = (uint32_t)slot[j] >> shift;
+                if (bb < (uint32_t)n_bins && ray[j] >= 0 && ray[j] < n_rays) bin[j] = (int)bb;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < CPW; ++j) {
+            if (bin[j] >= 0) {
+                const int64_t c = (step * WARPS + warp) * CPW + j;
+                const int32_t* __restrict__ ch = log + kLogChunks + c * kLogChunkWords;
+                const float wk = __int_as_float(ch[32 * 3 + lane]);
+                const float T = __int_as_float(ch[32 * 4 + lane]);
+                const float dd = __int_as_float(ch[32 * 5 + lane]);
+                const float4 ra = __ldg(b.rays + 3 * (int64_t)ray[j]),
+                             rb = __ldg(b.rays + 3 * (int64_t)ray[j] + 1),
+                             rc = __ldg(b.rays + 3 * (int64_t)ray[j] + 2);
+                const float gg[3] = {ra.x, ra.y, ra.z}, oo[3] = {ra.w, rb.x, rb.y};
+                vd[j][0] = rb.z; vd[j][1] = rb.w; vd[j][2] = rc.x;
+                float total_color = 0.f, accum = 0.f;
+#pragma unroll
+                for (int chn = 0; chn < 3; ++chn) {
+                    const float sg = __int_as_float(ch[32 * (6 + chn) + lane]);
+                    const float part = __int_as_float(ch[32 * (9 + chn) + lane]);
+                    const float g = gg[chn];
+                    total_color += (sg * d_rgb_pad - opt.rgb_padding) * g;
+                    accum += (oo[chn] - part) * g;
+                    // colour-coefficient factor (rt_kernel.cu:390)
+                    f[j][chn] = wk * sg * (1.0 - sg) * g * d_rgb_pad;
+                }
+                gs[j] = dd * (total_color * T - accum);
+                rank[j] = atomicAdd(&s_cnt[bin[j]], 1);
+            }
+        }
+        __syncthreads();
+        // one reservation per bin for the whole block step
+        for (int i = threadIdx.x; i < n_bins; i += BLOCK) {
+            const int cnt = s_cnt[i];
+            if (cnt > 0) s_cnt[i] = atomicAdd(&b.cursor[i * kCursorStride], cnt);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < CPW; ++j) {
+            if (bin[j] >= 0) {
+                const int64_t pos = (int64_t)b.offset[bin[j]] + s_cnt[bin[j]] + rank[j];
+                if (pos < b.offset[bin[j] + 1]) {
+                    b.packet[2 * pos] = make_int4(slot[j], __float_as_int(f[j][0]),
+                                                  __float_as_int(f[j][1]), __float_as_int(f[j][2]));
+                    b.packet[2 * pos + 1] =
+                        make_int4(__float_as_int(gs[j]), __float_as_int(vd[j][0]),
+                                  __float_as_int(vd[j][1]), __float_as_int(vd[j][2]));
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+__device__ __forceinline__ int4 ld_stream16(const int4* a, uint64_t pol) {
+    int4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.s32 {%0, %1, %2, %3}, [%4], %5;"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(a), "l"(pol));
+    return v;
+}
+
 template <int K>
-struct alignas(16) ReplaySmem {
+struct alignas(16) ScatterSmem {
     using Shape = CoopShape<K>;
-    float w[32], T[32], dd[32], tc[32], gs[32];
-    int ray[32];
-    unsigned mask[64];  // items per owner lane and parity
+    uint32_t slot[32];
     alignas(16) float rows[32 * Shape::STRIDE + 4];
 };
 
-template <int BD, int BLOCK, class Source>
+template <int BD, int BLOCK>
 __global__ void __launch_bounds__(BLOCK)
-render_replay_kernel(TreeArgs tr, Source src, svoxb_render_options opt, int32_t* __restrict__ log,
-                     const float* __restrict__ grad_out, const float* __restrict__ fwd_out,
-                     float* __restrict__ grad_data, int64_t log_capacity) {
+replay_scatter_kernel(int64_t n_slots, svoxb_render_options opt, float* __restrict__ grad_data,
+                      const int32_t* __restrict__ log, ReplayBins b, int flags) {
     constexpr int K = 3 * BD + 1;
     using Shape = CoopShape<K>;
-    using SM = ReplaySmem<K>;
+    using SM = ScatterSmem<K>;
     extern __shared__ __align__(16) unsigned char s_raw[];
     const int lane = threadIdx.x & 31;
     SM& sm = *reinterpret_cast<SM*>(s_raw + (size_t)(threadIdx.x >> 5) * sizeof(SM));
-    const float d_rgb_pad = 1 + 2 * opt.rgb_padding;
     const int sub = lane / Shape::GROUP, wj = lane % Shape::GROUP;
-    const uint64_t pol_stream = l2_policy_stream();
-    const int n_lists = log[2];
+    const int64_t total = b.offset[kMaxBins];
+    const int shift = log[2];
+    const uint64_t pol_keep = l2_policy_keep(), pol_stream = l2_policy_stream();
+    // Blocks take units of kScatterUnit packets in bin order from one counter, so the
+    // whole grid works within a window much smaller than a bin.
+    __shared__ int64_t s_unit;
+    const int warp = threadIdx.x >> 5;
+    constexpr int PER_WARP = kScatterUnit / (BLOCK / 32);
 
     for (;;) {
-        int list = 0;
-        if (lane == 0) list = atomicAdd(log + 1, 1);
-        list = __shfl_sync(0xffffffffu, list, 0);
-        if (list >= n_lists) break;
-        int64_t c = log[kLogHeads + list];
-        // per owner lane: the ray of each parity and its running accum
-        int cur_ray[2] = {-1, -1};
-        float accum[2] = {0.f, 0.f};
-        int guard = 0;
-        while (c >= 0 && c < log_capacity && ++guard < (1 << 28)) {
-            const int32_t* __restrict__ ch = log + kLogChunks + c * kLogChunkWords;
-            const int n = ch[0];
-            const int64_t nxt = ch[1];
-            if (n <= 0 || n > 32) break;
-            sm.mask[lane] = 0u;
-            sm.mask[32 + lane] = 0u;
-            __syncwarp();
-            // lane i: item i
-            float wk = 0.f, sg[3] = {0.f, 0.f, 0.f}, g[3] = {0.f, 0.f, 0.f};
+    __syncthreads();
+    if (threadIdx.x == 0)
+        s_unit = (int64_t)atomicAdd(reinterpret_cast<unsigned long long*>(b.work),
+                                    (unsigned long long)kScatterUnit);
+    __syncthreads();
+    const int64_t unit = s_unit;
+    if (unit >= total) break;
+    for (int64_t first = unit + warp * PER_WARP; first < unit + (warp + 1) * PER_WARP && first < total;
+         first += 32) {
+        const int n = (int)((total - first) < 32 ? (total - first) : 32);
+        uint32_t slot = 0xffffffffu;
+        int4 pa = make_int4(-1, 0, 0, 0), pb = make_int4(0, 0, 0, 0);
+        if (lane < n) {
+            if (flags & 1) {
+                pa = ld_stream16(b.packet + 2 * (first + lane), pol_stream);
+                pb = ld_stream16(b.packet + 2 * (first + lane) + 1, pol_stream);
+            } else {
+                pa = __ldg(b.packet + 2 * (first + lane));
+                pb = __ldg(b.packet + 2 * (first + lane) + 1);
+            }
+            slot = (uint32_t)pa.x;
+        }
+        // a position the bin pass left unwritten holds stale bytes: a packet counts only
+        // if it lies in the written part of the bin its slot names
+        {
+            const uint32_t bin = slot >> shift;
+            bool ok = (int64_t)slot < n_slots && bin < (uint32_t)kMaxBins;
+            if (ok) {
+                const int64_t rel = first + lane - b.offset[bin];
+                ok = rel >= 0 && rel < b.cursor[bin * kCursorStride];
+            }
+            if (!ok) slot = 0xffffffffu;
+        }
+        sm.slot[lane] = slot;
+        if (slot != 0xffffffffu) {
+            const float f[3] = {__int_as_float(pa.y), __int_as_float(pa.z), __int_as_float(pa.w)};
+            const float vdir[3] = {__int_as_float(pb.y), __int_as_float(pb.z), __int_as_float(pb.w)};
             float basis[BD];
+            sh_basis<BD>(vdir, basis);
 #pragma unroll
-            for (int i = 0; i < BD; ++i) basis[i] = 0.f;
-            if (lane < n) {
-                wk = __int_as_float(ch[32 * 2 + lane]);
-                const float T = __int_as_float(ch[32 * 3 + lane]);
-                const float dd = __int_as_float(ch[32 * 4 + lane]);
-                sg[0] = __int_as_float(ch[32 * 5 + lane]);
-                sg[1] = __int_as_float(ch[32 * 6 + lane]);
-                sg[2] = __int_as_float(ch[32 * 7 + lane]);
-                const int ray = ch[32 * 8 + lane];
-                const int meta = ch[32 * 9 + lane];
-                g[0] = __ldg(grad_out + 3 * (int64_t)ray);
-                g[1] = __ldg(grad_out + 3 * (int64_t)ray + 1);
-                g[2] = __ldg(grad_out + 3 * (int64_t)ray + 2);
-                Ray r;
-                src.load(ray, tr, opt, r);  // only the view direction is used
-                sh_basis<BD>(r.vdir, basis);
+            for (int k = 0; k < BD; ++k)
+                if (k < opt.min_comp || k > opt.max_comp) basis[k] = 0.f;
+            float v[K];
 #pragma unroll
-                for (int i = 0; i < BD; ++i)
-                    if (i < opt.min_comp || i > opt.max_comp) basis[i] = 0.f;
-                float total_color = 0.f;
+            for (int chn = 0; chn < 3; ++chn)
 #pragma unroll
-                for (int chn = 0; chn < 3; ++chn)
-                    total_color += (sg[chn] * d_rgb_pad - opt.rgb_padding) * g[chn];
-                sm.w[lane] = wk; sm.T[lane] = T; sm.dd[lane] = dd; sm.tc[lane] = total_color;
-                sm.ray[lane] = ray;
-                atomicOr(&sm.mask[(meta & 31) + 32 * ((meta >> 5) & 1)], 1u << lane);
+                for (int k = 0; k < BD; ++k) v[chn * BD + k] = basis[k] * f[chn];
+            v[K - 1] = __int_as_float(pb.x);
+            float* row = sm.rows + lane * Shape::STRIDE;
+            if (Shape::VEC) {
+#pragma unroll
+                for (int w = 0; w < K / 4; ++w)
+                    reinterpret_cast<float4*>(row)[w] =
+                        make_float4(v[4 * w], v[4 * w + 1], v[4 * w + 2], v[4 * w + 3]);
+            } else {
+#pragma unroll
+                for (int w = 0; w < K; ++w) row[w] = v[w];
             }
-            __syncwarp();
-            // owner lanes: sequential accum per ray, in log order
+        }
+        __syncwarp();
 #pragma unroll
-            for (int p = 0; p < 2; ++p) {
-                unsigned m = sm.mask[lane + 32 * p];
-                while (m != 0u) {
-                    const int k = __ffs(m) - 1;
-                    m &= m - 1u;
-                    const int ray = sm.ray[k];
-                    if (ray != cur_ray[p]) {
-                        cur_ray[p] = ray;
-                        float a = __ldg(fwd_out + 3 * (int64_t)ray) * __ldg(grad_out + 3 * (int64_t)ray);
-                        a += __ldg(fwd_out + 3 * (int64_t)ray + 1) * __ldg(grad_out + 3 * (int64_t)ray + 1);
-                        a += __ldg(fwd_out + 3 * (int64_t)ray + 2) * __ldg(grad_out + 3 * (int64_t)ray + 2);
-                        accum[p] = a;
-                    }
-                    const float tc = sm.tc[k];
-                    accum[p] -= sm.w[k] * tc;
-                    sm.gs[k] = sm.dd[k] * (tc * sm.T[k] - accum[p]);
-                }
-            }
-            __syncwarp();
-            // lane i forms the gradient of record i
-            if (lane < n) {
-                float* row = sm.rows + lane * Shape::STRIDE;
-                float v[K];
+        for (int p = 0; p < 32 / Shape::IPP; ++p) {
+            const int k = p * Shape::IPP + sub;
+            if (k < n) {
+                const uint32_t sl = sm.slot[k];
+                if ((int64_t)sl < n_slots) {
+                    float* __restrict__ gp = grad_data + (size_t)sl * K;
+                    const float* row = sm.rows + k * Shape::STRIDE;
 #pragma unroll
-                for (int chn = 0; chn < 3; ++chn) {
-                    const float tmp2 = wk * sg[chn] * (1.0 - sg[chn]) * g[chn] * d_rgb_pad;
-#pragma unroll
-                    for (int i = 0; i < BD; ++i) v[chn * BD + i] = basis[i] * tmp2;
-                }
-                v[K - 1] = sm.gs[lane];
-                if (Shape::VEC) {
-#pragma unroll
-                    for (int w = 0; w < K / 4; ++w)
-                        reinterpret_cast<float4*>(row)[w] =
-                            make_float4(v[4 * w], v[4 * w + 1], v[4 * w + 2], v[4 * w + 3]);
-                } else {
-#pragma unroll
-                    for (int w = 0; w < K; ++w) row[w] = v[w];
-                }
-            }
-            __syncwarp();
-            // groups of lanes flush the rows
-#pragma unroll
-            for (int p = 0; p < 32 / Shape::IPP; ++p) {
-                const int k = p * Shape::IPP + sub;
-                if (k < n) {
-                    const uint32_t sl = (uint32_t)ch[32 * 1 + k];
-                    if ((int64_t)sl < tr.M * 8) {
-                        float* __restrict__ gp = grad_data + (size_t)sl * K;
-                        const float* row = sm.rows + k * Shape::STRIDE;
-#pragma unroll
-                        for (int w = 0; w < Shape::WPL; ++w) {
-                            const int word = wj + w * Shape::GROUP;
-                            if (word < Shape::WORDS) {
-                                if (Shape::VEC) {
-                                    const float4 x = reinterpret_cast<const float4*>(row)[word];
-                                    red_add_v4_hint(gp + 4 * word, x.x, x.y, x.z, x.w, pol_stream);
-                                } else {
-                                    atomicAdd(gp + word, row[word]);
-                                }
+                    for (int w = 0; w < Shape::WPL; ++w) {
+                        const int word = wj + w * Shape::GROUP;
+                        if (word < Shape::WORDS) {
+                            if (Shape::VEC) {
+                                const float4 x = reinterpret_cast<const float4*>(row)[word];
+                                if (flags & 2)
+                                    red_add_v4_hint(gp + 4 * word, x.x, x.y, x.z, x.w, pol_keep);
+                                else
+                                    red_add_v4(gp + 4 * word, x.x, x.y, x.z, x.w);
+                            } else {
+                                atomicAdd(gp + word, row[word]);
                             }
                         }
                     }
                 }
             }
-            __syncwarp();
-            c = nxt;
         }
+        __syncwarp();
+    }
     }
 }
 

@@ -148,6 +148,16 @@ static int launch_coop(const RenderCall& c, const Source& src, const TopTable& t
 // per-warp queues fit in shared memory next to the jump table.
 constexpr size_t kMaxSmem = 227 * 1024;
 
+// Replay bins: a bin is a range of 2^shift leaf slots whose gradient spans
+// about g_tuning.replay_bin_mb MB, at most kMaxBins of them.
+static int replay_bin_shift(int64_t M, int K) {
+    const int64_t per_bin = ((int64_t)g_tuning.replay_bin_mb << 20) / (K * 4);
+    int shift = 0;
+    while ((2LL << shift) <= per_bin) ++shift;
+    while (((M * 8 - 1) >> shift) + 1 > kMaxBins) ++shift;
+    return shift;
+}
+
 template <int BD, int BLOCK, class Source>
 static int launch_queue_block(const RenderCall& c, const Source& src, const TreeArgs& tr,
                               const TopTable& top, size_t top_bytes) {
@@ -159,15 +169,15 @@ static int launch_queue_block(const RenderCall& c, const Source& src, const Tree
         const size_t smem = top_bytes + (size_t)(BLOCK / 32) * sizeof(WarpQueue<K, kModeForwardLogged>);
         auto k = render_queue_kernel<BD, BLOCK, kModeForwardLogged, Source>;
         if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
-        if ((int64_t)grid * (BLOCK / 32) > kLogMaxLists) return SVOXB_ERR_TOO_LARGE;
         k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, (int)top_bytes, c.Q, c.out,
-                                          nullptr, nullptr, nullptr, c.log, c.log_capacity);
+                                          nullptr, nullptr, nullptr, c.log, c.log_capacity,
+                                          replay_bin_shift(c.tree->M, K));
     } else if (!c.backward) {
         const size_t smem = top_bytes + (size_t)(BLOCK / 32) * sizeof(WarpQueue<K, kModeForward>);
         auto k = render_queue_kernel<BD, BLOCK, kModeForward, Source>;
         if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
         k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, (int)top_bytes, c.Q, c.out,
-                                          nullptr, nullptr, nullptr, nullptr, 0);
+                                          nullptr, nullptr, nullptr, nullptr, 0, 0);
     } else {
         const size_t smem = top_bytes + (size_t)(BLOCK / 32) * sizeof(WarpQueue<K, kModeBackward>);
         const bool single = c.fwd_out != nullptr && c.opt.sigma_thresh == 0.f &&
@@ -176,26 +186,74 @@ static int launch_queue_block(const RenderCall& c, const Source& src, const Tree
         if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
         k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, (int)top_bytes, c.Q, nullptr,
                                           c.grad_out, single ? c.fwd_out : nullptr, c.grad_data,
-                                          nullptr, 0);
+                                          nullptr, 0, 0);
     }
     SVOXB_CUDA(cudaGetLastError());
     return SVOXB_OK;
 }
 
+// Replay backward (render_replay.cuh): prefix, bin, scatter.  `chunks` is the
+// number of log chunks the forward used; the packet buffer is sized from it.
+// SVOXB_ERR_TOO_LARGE when the packet buffer cannot be had (the caller then
+// marches instead).
 template <int BD, class Source>
-static int launch_replay(const RenderCall& c, const Source& src) {
+static int launch_replay(const RenderCall& c, const Source& src, int64_t chunks) {
     constexpr int K = 3 * BD + 1;
-    constexpr int BLOCK = 512;
-    const size_t smem = (size_t)(BLOCK / 32) * sizeof(ReplaySmem<K>);
-    auto k = render_replay_kernel<BD, BLOCK, Source>;
+    if (chunks > c.log_capacity) chunks = c.log_capacity;
+    if (chunks < 1) return SVOXB_OK;
+    const int64_t packets = chunks * 32;
+    if (packets >= (1LL << 30)) return SVOXB_ERR_TOO_LARGE;
+
+    int st = keep_pool_cached();
+    if (st) return st;
+    // cursors | offsets | work counter | packed rays | packets
+    const size_t head_words = (size_t)kMaxBins * kCursorStride + kMaxBins + 8;  // 32-byte multiple
+    const size_t ray_words = (size_t)c.Q * 12;
+    const size_t pad = (8 - (head_words + ray_words) % 8) % 8;
+    int32_t* base = nullptr;
+    if (cudaMallocAsync((void**)&base,
+                        (head_words + ray_words + pad + 8 * (size_t)packets) * sizeof(int32_t),
+                        c.stream) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return SVOXB_ERR_TOO_LARGE;
+    }
+    ReplayBins b{};
+    b.cursor = base;
+    b.offset = base + (size_t)kMaxBins * kCursorStride;
+    b.work = reinterpret_cast<int64_t*>(b.offset + kMaxBins + 2);  // 8-byte aligned
+    float4* rays = reinterpret_cast<float4*>(base + head_words);
+    b.rays = rays;
+    b.capacity = packets;
+    b.packet = reinterpret_cast<int4*>(base + head_words + ray_words + pad);
+
+    auto finish = [&](int status) {
+        cudaFreeAsync(base, c.stream);
+        return status;
+    };
+    cudaError_t e = cudaSuccess;
+    replay_prefix_kernel<<<1, 256, 0, c.stream>>>(c.log, b);
+    replay_pack_rays_kernel<<<(unsigned)((c.Q + 255) / 256), 256, 0, c.stream>>>(
+        tree_args(c.tree), src, c.opt, c.grad_out, c.fwd_out, c.Q, rays);
+
     unsigned grid = 1;
-    int st;
-    if ((st = persistent_grid(k, BLOCK, smem, (int64_t)kLogMaxLists * 32, &grid))) return st;
-    SVOXB_CUDA(cudaMemsetAsync(c.log + 1, 0, sizeof(int32_t), c.stream));  // replay work counter
-    k<<<grid, BLOCK, smem, c.stream>>>(tree_args(c.tree), src, c.opt, c.log, c.grad_out, c.fwd_out,
-                                      c.grad_data, c.log_capacity);
-    SVOXB_CUDA(cudaGetLastError());
-    return SVOXB_OK;
+    auto run_bin = [&](auto k, int block) {
+        int s2 = persistent_grid(k, block, 0, chunks, &grid);
+        if (s2) return s2;
+        k<<<grid, block, 0, c.stream>>>(c.opt, c.log, chunks, c.Q, b);
+        return (int)SVOXB_OK;
+    };
+    st = run_bin(replay_bin_kernel<256, 2, 6>, 256);
+    if (st) return finish(st);
+    {
+        constexpr int BLOCK = 512;
+        const size_t smem = (size_t)(BLOCK / 32) * sizeof(ScatterSmem<K>);
+        auto k = replay_scatter_kernel<BD, BLOCK>;
+        if ((st = persistent_grid(k, BLOCK, smem, chunks, &grid))) return finish(st);
+        k<<<grid, BLOCK, smem, c.stream>>>(c.tree->M * 8, c.opt, c.grad_data, c.log, b,
+                                          g_tuning.replay_flags);
+    }
+    e = cudaGetLastError();
+    return finish(e != cudaSuccess ? set_cuda_error(e) : SVOXB_OK);
 }
 
 // Per-call scratch of the queue kernels: the annotated child array followed by
@@ -476,7 +534,7 @@ static int logged_forward(const svoxb_tree* tree, const Source& src, int64_t Q,
     if ((st = log_eligible(tree, opt, nullptr))) return st;
     if (!log || capacity_chunks < 1 || Q < 0) return SVOXB_ERR_SHAPE;
     if (Q > 0 && !out) return SVOXB_ERR_NULL;
-    SVOXB_CUDA(cudaMemsetAsync(log, 0, kLogHeads * sizeof(int32_t), (cudaStream_t)stream));
+    SVOXB_CUDA(cudaMemsetAsync(log, 0, kLogChunks * sizeof(int32_t), (cudaStream_t)stream));
     if (Q == 0) return SVOXB_OK;
     RenderCall c{tree, *opt, Q};
     c.out = out;
@@ -497,7 +555,8 @@ template <class Source>
 static int replay_backward(const svoxb_tree* tree, const Source& src, int64_t Q,
                            const svoxb_render_options* opt, const float* grad_output,
                            const float* fwd_out, int32_t* log, int64_t capacity_chunks,
-                           float* grad_data_out, int zero_first, void* stream) {
+                           int64_t chunks_used, float* grad_data_out, int zero_first,
+                           void* stream) {
     int st = validate_tree(tree);
     if (st) return st;
     if ((st = validate_options(tree, *opt))) return st;
@@ -515,14 +574,22 @@ static int replay_backward(const svoxb_tree* tree, const Source& src, int64_t Q,
     c.stream = (cudaStream_t)stream;
     c.log = log;
     c.log_capacity = capacity_chunks;
+    if (chunks_used <= 0 || chunks_used > capacity_chunks) chunks_used = capacity_chunks;
+    st = SVOXB_ERR_FORMAT;
     switch (opt->basis_dim) {
-        case 1: return launch_replay<1>(c, src);
-        case 4: return launch_replay<4>(c, src);
-        case 9: return launch_replay<9>(c, src);
-        case 16: return launch_replay<16>(c, src);
-        case 25: return launch_replay<25>(c, src);
+        case 1: st = launch_replay<1>(c, src, chunks_used); break;
+        case 4: st = launch_replay<4>(c, src, chunks_used); break;
+        case 9: st = launch_replay<9>(c, src, chunks_used); break;
+        case 16: st = launch_replay<16>(c, src, chunks_used); break;
+        case 25: st = launch_replay<25>(c, src, chunks_used); break;
     }
-    return SVOXB_ERR_FORMAT;
+    if (st == SVOXB_ERR_TOO_LARGE) {
+        // no room for the packets: march instead (same result, the log is not used)
+        c.log = nullptr;
+        c.log_capacity = 0;
+        return render_dispatch(c, src);
+    }
+    return st;
 }
 
 extern "C" {
@@ -554,25 +621,26 @@ int svoxb_volume_render_backward_replay(const svoxb_tree* tree, const svoxb_rays
                                         const svoxb_render_options* opt,
                                         const float* grad_output, const float* fwd_out,
                                         int32_t* log, int64_t capacity_chunks,
-                                        float* grad_data_out, int zero_first, void* stream) {
+                                        int64_t chunks_used, float* grad_data_out,
+                                        int zero_first, void* stream) {
     if (!tree || !rays || !opt) return SVOXB_ERR_NULL;
     if (rays->Q > 0 && (!rays->origins || !rays->dirs || !rays->vdirs)) return SVOXB_ERR_NULL;
     return replay_backward(tree, RayBatch{rays->origins, rays->dirs, rays->vdirs}, rays->Q, opt,
-                           grad_output, fwd_out, log, capacity_chunks, grad_data_out, zero_first,
-                           stream);
+                           grad_output, fwd_out, log, capacity_chunks, chunks_used, grad_data_out,
+                           zero_first, stream);
 }
 
 int svoxb_volume_render_image_backward_replay(const svoxb_tree* tree, const svoxb_camera* cam,
                                               const svoxb_render_options* opt,
                                               const float* grad_output, const float* fwd_out,
                                               int32_t* log, int64_t capacity_chunks,
-                                              float* grad_data_out, int zero_first,
-                                              void* stream) {
+                                              int64_t chunks_used, float* grad_data_out,
+                                              int zero_first, void* stream) {
     if (!tree || !cam || !opt || !cam->c2w) return SVOXB_ERR_NULL;
     if (cam->width < 0 || cam->height < 0) return SVOXB_ERR_SHAPE;
     return replay_backward(tree, PixelRays{cam->c2w, cam->fx, cam->fy, cam->width, cam->height},
                            (int64_t)cam->width * cam->height, opt, grad_output, fwd_out, log,
-                           capacity_chunks, grad_data_out, zero_first, stream);
+                           capacity_chunks, chunks_used, grad_data_out, zero_first, stream);
 }
 
 int svoxb_item_log_used(const int32_t* log, int64_t* chunks_used, void* stream) {
@@ -661,6 +729,11 @@ int svoxb_tune(int key, int value) {
         case 1: g_tuning.render_top_level = value; return SVOXB_OK;
         case 2: g_tuning.query_top_level = value; return SVOXB_OK;
         case 3: g_tuning.render_algo = value; return SVOXB_OK;
+        case 6: g_tuning.replay_flags = value; return SVOXB_OK;
+        case 5:
+            if (value < 1 || value > 1024) return SVOXB_ERR_OPTION;
+            g_tuning.replay_bin_mb = value;
+            return SVOXB_OK;
     }
     return SVOXB_ERR_OPTION;
 }
