@@ -226,7 +226,8 @@ const char* svoxb_last_cuda_error(void);
  * render algorithm (2 = item queue, the default; 0 = warp-cooperative; 1 = one
  * thread per ray), key 5 = MB of gradient one bin of the replay backward spans
  * (default 16), key 6 = L2 hint bits of the replay scatter (1 = packets
- * evict-first, 2 = gradient evict-last; default 3). */
+ * evict-first, 2 = gradient evict-last; default 3), key 7 = bricks below the
+ * render leaf table (1 = on, the default; 0 = off). */
 int svoxb_tune(int key, int value);
 
 /* Library version, "major.minor.patch". */

@@ -48,6 +48,7 @@ struct LeafHit {
 struct TopTable {
     const int32_t* cells;  // shared or global memory
     int level;             // L (0 = no table)
+    const int2* bricks = nullptr;  // queue kernels only: see render_queue.cuh
 };
 
 // Descent of query_single_from_root (svox/csrc/include/common.cuh:52-90) for
@@ -148,6 +149,7 @@ struct Tuning {
     int query_top_level = -1;
     int render_algo = 2;        // 2 = item queue, 0 = warp-cooperative, 1 = one thread per ray
     int replay_bin_mb = 16;     // gradient bytes one replay bin spans
+    int render_bricks = 1;      // queue kernels: bricks below the leaf table
     int replay_flags = 3;       // replay scatter: 1 = packets evict-first, 2 = gradient evict-last
 };
 extern Tuning g_tuning;

@@ -10,10 +10,10 @@
 //           was requested during the previous iteration (software-pipelined):
 //           an inner node moves the lane's cursor one level down; a leaf is
 //           sampled (step length, density, transmittance, weight), the ray
-//           advances, and the cursor of the next sample restarts from the
-//           lowest common ancestor kept in a per-lane path cache (or from the
-//           shared-memory jump table).  Lanes never wait for another lane's
-//           longer descent.  The descent reads an ANNOTATED copy of the child
+//           advances, and the cursor of the next sample restarts at the leaf
+//           table, or, while the ray stays inside the same table cell, at the
+//           cell's BRICK, which resolves three more levels with one load (see
+//           below).  Lanes never wait for another lane's longer descent.  The descent reads an ANNOTATED copy of the child
 //           array whose leaf entries carry the density of leaves that pass
 //           the density test (annotate_sigma_kernel, built per call), so the
 //           march itself runs out of L2-resident data and empty leaves never
@@ -78,7 +78,22 @@ constexpr int kLogChunkWords = kLogRows * 32;
 constexpr int kLogGrab = 8;  // chunks a warp takes per bump of the allocation counter
 
 constexpr int kCoordBits = 24;  // integer coordinates: floor(x * 2^24), exact for float x < 1
-constexpr int kPathLevels = 6;  // cached ancestors from the table level down
+
+// Bricks: every inner cell of the leaf table gets the 8x8x8 grid of the three
+// levels below it, 8 bytes per fine cell:
+//   .x  the annotated child entry of the leaf that covers the fine cell (<= 0), or, if
+//       the tree goes deeper there, the id (> 0) of the node three levels down
+//   .y  leaf slot (bits 0-27) and leaf depth minus (table level + 1) (bits 28-29)
+// A table cell with a brick holds kBrickFlag + brick id instead of the node id.
+// Samples in refined regions then cost one dependent load, like samples in
+// empty space; trees deeper than table level + 3 continue from the brick entry
+// through the annotated child array.  Table cells beyond the brick budget keep
+// their node id and are walked level by level.
+constexpr int kBrickLevels = 3;
+constexpr int kBrickCells = 512;
+constexpr int32_t kBrickFlag = 1 << 30;
+constexpr int64_t kBrickMaxNodes = 1 << 25;  // slots must fit 28 bits
+constexpr int kMaxBricks = 1 << 16;
 
 // Annotated child entry: > 0 link; 0 leaf failing the density test; < 0 leaf
 // passing it, with the density's float bits in the low 31 bits when the
@@ -169,6 +184,59 @@ __global__ void build_leaf_table_kernel(const int32_t* __restrict__ annotated, i
     cells[idx] = node >= 0 ? (int32_t)node : entry;
 }
 
+// Gives every table cell that holds a node a brick while the budget lasts.
+__global__ void assign_bricks_kernel(int32_t* __restrict__ cells, int n_cells, int cap,
+                                     int32_t* __restrict__ counter, int32_t* __restrict__ roots) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_cells) return;
+    const int32_t e = cells[idx];
+    if (e <= 0) return;
+    const int id = atomicAdd(counter, 1);
+    if (id >= cap) return;
+    roots[id] = e;
+    cells[idx] = kBrickFlag + id;
+}
+
+// One block per brick, one thread per fine cell.
+__global__ void __launch_bounds__(kBrickCells)
+fill_bricks_kernel(const int32_t* __restrict__ annotated, int64_t M, int L, int cap,
+                   const int32_t* __restrict__ counter, const int32_t* __restrict__ roots,
+                   int2* __restrict__ bricks) {
+    int n = *counter;
+    if (n > cap) n = cap;
+    if ((int)blockIdx.x >= n) return;
+    const int c = threadIdx.x;
+    const int x = c >> 6, y = (c >> 3) & 7, z = c & 7;
+    int64_t node = roots[blockIdx.x];
+    int2 out = make_int2(0, 0);
+    bool done = false;
+    for (int l = 0; l < kBrickLevels && !done; ++l) {
+        const int sh = kBrickLevels - 1 - l;
+        const int cell = (((x >> sh) & 1) << 2) | (((y >> sh) & 1) << 1) | ((z >> sh) & 1);
+        const int32_t e = annotated[node * 8 + cell];
+        if (e <= 0) {
+            out = make_int2(e, (int)((uint32_t)(node * 8 + cell) | ((uint32_t)l << 28)));
+            done = true;
+        } else {
+            node += e;
+            if (node >= M) {  // corrupt link: the marching kernel reports it
+                out = make_int2((int32_t)M, 0);
+                done = true;
+            }
+        }
+    }
+    if (!done) out = make_int2((int32_t)node, 0);
+    bricks[(size_t)blockIdx.x * kBrickCells + c] = out;
+}
+
+__device__ __forceinline__ int2 ld_keep2(const int2* a, uint64_t pol) {
+    int2 v;
+    asm volatile("ld.global.nc.L2::cache_hint.v2.s32 {%0, %1}, [%2], %3;"
+                 : "=r"(v.x), "=r"(v.y)
+                 : "l"(a), "l"(pol));
+    return v;
+}
+
 __device__ __forceinline__ void cp_async_wait_all() {
     asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
 }
@@ -198,6 +266,7 @@ struct alignas(16) WarpQueue {
 };
 
 enum { kNeedRay = 0, kMarching = 1, kDraining = 2, kExhausted = 3 };
+enum { kFromChild = 0, kFromTable = 1, kFromBrick = 2 };
 
 template <int BD, int BLOCK, int MODE, class Source>
 __global__ void __launch_bounds__(BLOCK)
@@ -258,13 +327,10 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
     // cursor of the descent in progress
     int node = 0, lvl = 0, ix = 0, iy = 0, iz = 0;
     float px = 0.f, py = 0.f, pz = 0.f;
-    int32_t e_pre = 0;        // entry at the cursor, requested one iteration ahead ...
-    bool from_tab = false;    // ... from the leaf table (else from the annotated child array)
+    int32_t e_pre = 0, e_aux = 0;  // entry at the cursor, requested one iteration ahead ...
+    int kind = kFromChild;         // ... from the annotated child array, the leaf table or a brick
     int tab_idx = 0;
-
-    int path[kPathLevels];    // path[j]: node at level base + j on the way to the last leaf
-#pragma unroll
-    for (int j = 0; j < kPathLevels; ++j) path[j] = 0;
+    int cur_cell = -1, cur_brick = -1;  // table cell of the last brick used, and that brick
     unsigned mine_lo = 0u;              // my items among queue positions [0, 32)
     unsigned long long mine_hi = 0ull;  // ... among [32, 96)
     int qn = 0;                         // queued items (warp-uniform)
@@ -273,39 +339,32 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
     int64_t log_chunk = 0;
     int log_left = 0;
 
-    // Places the cursor for the sample at parameter t, reusing the deepest cached
-    // ancestor shared with the previous sample (valid down to level `deepest`).
-    auto place_cursor = [&](int deepest) {
+    // Places the cursor for the sample at parameter t: at the brick of the table cell
+    // the ray is in if that is the brick used last, else at the leaf table.
+    auto place_cursor = [&]() {
         px = clamp01(mad_site<FC_POS>(t, r.dx, r.ox));
         py = clamp01(mad_site<FC_POS>(t, r.dy, r.oy));
         pz = clamp01(mad_site<FC_POS>(t, r.dz, r.oz));
-        const int nx = (int)(px * big), ny = (int)(py * big), nz = (int)(pz * big);
-        const int diff = (nx ^ ix) | (ny ^ iy) | (nz ^ iz);
-        int common = __clz(diff) - (32 - kCoordBits);  // leading coordinate bits in common
-        if (common > deepest) common = deepest;
-        if (common > base + kPathLevels - 1) common = base + kPathLevels - 1;
-        ix = nx; iy = ny; iz = nz;
-        if (base > 0 && common >= base) {
-            const int j = common - base;
-            int n = path[0];
-#pragma unroll
-            for (int jj = 1; jj < kPathLevels; ++jj) n = (j == jj) ? path[jj] : n;
-            node = n;
-            lvl = common;
-        } else {
-            node = 0;
-            lvl = 0;
-            if (base > 0) {
-                const int sh = kCoordBits - base;
-                tab_idx = ((((ix >> sh) << base) + (iy >> sh)) << base) + (iz >> sh);
-                from_tab = true;
-            }
+        ix = (int)(px * big); iy = (int)(py * big); iz = (int)(pz * big);
+        node = 0;
+        lvl = 0;
+        kind = kFromChild;
+        if (base > 0) {
+            const int sh = kCoordBits - base;
+            tab_idx = ((((ix >> sh) << base) + (iy >> sh)) << base) + (iz >> sh);
+            kind = (tab_idx == cur_cell && cur_brick >= 0) ? kFromBrick : kFromTable;
         }
     };
 
-    // Requests the entry at the cursor (table cell or child slot).
+    // Requests the entry at the cursor.
     auto request_entry = [&]() {
-        if (from_tab) {
+        if (kind == kFromBrick) {
+            const int sh = kCoordBits - base - kBrickLevels;
+            const int c = (((ix >> sh) & 7) << 6) | (((iy >> sh) & 7) << 3) | ((iz >> sh) & 7);
+            const int2 v = ld_keep2(top.bricks + ((size_t)cur_brick * kBrickCells + c), pol_keep);
+            e_pre = v.x;
+            e_aux = v.y;
+        } else if (kind == kFromTable) {
             e_pre = ld_keep(top.cells + tab_idx, pol_keep);
         } else {
             const int b = kCoordBits - 1 - lvl;
@@ -555,7 +614,7 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                     phase = 1;
                     t = r.tmin; light = 1.f; it = 0;
                     state = kMarching;
-                    place_cursor(0);
+                    place_cursor();
                     request_entry();
                 } else {
                     if (!BWD) write_out(ray, a0, a1, a2, light, stopped);
@@ -599,7 +658,7 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                                 phase = 0;
                             }
                         }
-                        place_cursor(0);
+                        place_cursor();
                         request_entry();
                     }
                 }
@@ -628,17 +687,35 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
         float weight = 0.f, dd = 0.f;
         if (state == kMarching) {
             int32_t e = e_pre;
-            bool go = true, is_leaf = false;
+            bool go = true, is_leaf = false, have_slot = false;
             int depth = 0;
-            if (from_tab) {
-                from_tab = false;
-                if (e > 0) {                    // node at the table level
+            if (kind == kFromBrick) {
+                if (e > 0) {                    // deeper than the brick: go on from that node
+                    node = e;
+                    lvl = base + kBrickLevels;
+                    kind = kFromChild;
+                    if (node >= M || lvl >= kCoordBits) {
+                        report(SVOXB_ERR_TREE);
+                        state = kDraining;
+                        go = false;
+                    }
+                } else {
+                    is_leaf = true;
+                    have_slot = true;
+                    depth = base + 1 + (int)((uint32_t)e_aux >> 28);
+                    slot = (uint32_t)e_aux & 0x0fffffffu;
+                }
+            } else if (kind == kFromTable) {
+                if (e >= kBrickFlag) {          // the cell has a brick: look the sample up there
+                    cur_cell = tab_idx;
+                    cur_brick = e - kBrickFlag;
+                    kind = kFromBrick;
+                } else if (e > 0) {             // node at the table level, no brick
                     node = e;
                     lvl = base;
-                    path[0] = e;
+                    kind = kFromChild;
                 } else if (e == kTabDescend) {  // resolve from the root
-                    node = 0;
-                    lvl = 0;
+                    kind = kFromChild;
                 } else {                        // empty leaf of depth -e: nothing else to read
                     is_leaf = true;
                     depth = -e;
@@ -651,11 +728,6 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                     report(SVOXB_ERR_TREE);
                     state = kDraining;
                     go = false;
-                } else if (base > 0) {
-                    const int j = lvl - base;
-#pragma unroll
-                    for (int jj = 1; jj < kPathLevels; ++jj)
-                        if (j == jj) path[jj] = node;
                 }
             } else {
                 is_leaf = true;
@@ -675,8 +747,10 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                 const float delta_t =
                     __fadd_rn(__fmul_rn(__fsub_rn(smax, smin), inv_cube), opt.step_size);
                 if (e < 0) {
-                    slot = (uint32_t)node * 8u + (uint32_t)((((ix >> b) & 1) << 2) |
-                                                            (((iy >> b) & 1) << 1) | ((iz >> b) & 1));
+                    if (!have_slot)
+                        slot = (uint32_t)node * 8u + (uint32_t)((((ix >> b) & 1) << 2) |
+                                                                (((iy >> b) & 1) << 1) |
+                                                                ((iz >> b) & 1));
                     float sigma = (e == kOccupied) ? __ldg(tr.data + (size_t)slot * K + (K - 1))
                                                    : __uint_as_float((uint32_t)e & 0x7fffffffu);
                     if (opt.density_softplus) sigma = softplus_m1(sigma);
@@ -698,7 +772,7 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                     done = true;
                 }
                 if (!done) {
-                    place_cursor(depth - 1);
+                    place_cursor();
                 } else {
                     go = false;
                     const int pending = cnt_cur + (item ? 1 : 0);

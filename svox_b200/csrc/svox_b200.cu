@@ -261,6 +261,7 @@ static int launch_replay(const RenderCall& c, const Source& src, int64_t chunks)
 struct QueueScratch {
     int32_t* annotated = nullptr;
     int32_t* table = nullptr;
+    int2* bricks = nullptr;
     int level = 0;
     cudaStream_t stream = nullptr;
     int build(const svoxb_tree* t, float thresh, int softplus, int max_level, cudaStream_t s) {
@@ -268,9 +269,20 @@ struct QueueScratch {
         const int64_t n = t->M * 8;
         level = auto_top_level(t->M, max_level);
         const int64_t cells = level > 0 ? ((int64_t)1 << (3 * level)) : 0;
+        // bricks: one per table cell that holds a node, while the budget lasts
+        int64_t cap = 0;
+        if (level > 0 && g_tuning.render_bricks && t->M < kBrickMaxNodes &&
+            level + kBrickLevels < kCoordBits) {
+            cap = cells < t->M ? cells : t->M;
+            if (cap > kMaxBricks) cap = kMaxBricks;
+        }
+        // annotated | table | brick counter (8 words) | brick roots | bricks
+        const size_t head = (size_t)(n + cells) + 8 + (size_t)((cap + 7) & ~(int64_t)7);
         int st = keep_pool_cached();
         if (st) return st;
-        SVOXB_CUDA(cudaMallocAsync((void**)&annotated, (size_t)(n + cells) * sizeof(int32_t), s));
+        SVOXB_CUDA(cudaMallocAsync((void**)&annotated,
+                                   head * sizeof(int32_t) +
+                                       (size_t)cap * kBrickCells * sizeof(int2), s));
         table = annotated + n;
         annotate_sigma_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(
             t->child, t->data, t->K, n, thresh, softplus, annotated);
@@ -278,6 +290,17 @@ struct QueueScratch {
         if (level > 0) {
             build_leaf_table_kernel<<<(unsigned)((cells + 255) / 256), 256, 0, s>>>(
                 annotated, t->M, level, table);
+            SVOXB_CUDA(cudaGetLastError());
+        }
+        if (cap > 0) {
+            int32_t* counter = table + cells;
+            int32_t* roots = counter + 8;
+            bricks = reinterpret_cast<int2*>(annotated + head);
+            SVOXB_CUDA(cudaMemsetAsync(counter, 0, sizeof(int32_t), s));
+            assign_bricks_kernel<<<(unsigned)((cells + 255) / 256), 256, 0, s>>>(
+                table, (int)cells, (int)cap, counter, roots);
+            fill_bricks_kernel<<<(unsigned)cap, kBrickCells, 0, s>>>(annotated, t->M, level,
+                                                                     (int)cap, counter, roots, bricks);
             SVOXB_CUDA(cudaGetLastError());
         }
         return SVOXB_OK;
@@ -295,7 +318,7 @@ static int launch_queue(const RenderCall& c, const Source& src) {
     if (st) return st;
     TreeArgs tr = tree_args(c.tree);
     tr.child = scratch.annotated;
-    const TopTable top{scratch.table, scratch.level};
+    const TopTable top{scratch.table, scratch.level, scratch.bricks};
     const size_t top_bytes = 0;  // the leaf table stays in global memory
     const size_t per_warp = c.backward ? sizeof(WarpQueue<K, kModeBackward>)
                             : c.log    ? sizeof(WarpQueue<K, kModeForwardLogged>)
@@ -730,6 +753,7 @@ int svoxb_tune(int key, int value) {
         case 2: g_tuning.query_top_level = value; return SVOXB_OK;
         case 3: g_tuning.render_algo = value; return SVOXB_OK;
         case 6: g_tuning.replay_flags = value; return SVOXB_OK;
+        case 7: g_tuning.render_bricks = value; return SVOXB_OK;
         case 5:
             if (value < 1 || value > 1024) return SVOXB_ERR_OPTION;
             g_tuning.replay_bin_mb = value;
