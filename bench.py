@@ -5,9 +5,10 @@ SH-degree-2 scene with 2^20 rays per step ("config 4"), on 1..8 B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
 
-Under torchrun (N > 1) every rank holds the whole tree, renders a contiguous
-slice of the rays and the step ends with one NCCL all-reduce of data.grad.
-Rank 0 prints ONE JSON line.  ``--impl reference`` times the CPU oracle (the
+Under torchrun (N > 1) every rank holds the whole tree and renders its own
+2^20 rays per step (weak scaling: the global batch grows with N); the step
+ends with one NCCL all-reduce of data.grad.  Rank 0 prints ONE JSON line whose
+value is the rays of all ranks per second.  ``--impl reference`` times the CPU oracle (the
 C restatement of the reference's algorithm) on the host cores instead.
 
 Inputs are seeded synthetic data (svox_b200/workloads.py): no real scene is
@@ -31,6 +32,10 @@ if ROOT not in sys.path:
 
 METRIC = "Mrays/s volume_render fwd+bwd (SH deg 2, 2^20 rays)"
 UNIT = "Mrays/s"
+# DRAM bytes (read + write) of one launch on the default workload, from the ncu capture
+# summarised in profiles/training_step_config4_ncu_full.md
+NCU_TRAFFIC_FWD = 20.6e9
+NCU_TRAFFIC_BWD = 5.7e9 + 4.1e9
 
 
 def parse():
@@ -39,7 +44,7 @@ def parse():
     p.add_argument("--steps", type=int, default=20)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    p.add_argument("--rays", type=int, default=1 << 20, help="rays per step (whole job)")
+    p.add_argument("--rays", type=int, default=1 << 20, help="rays per step and GPU")
     p.add_argument("--init-refine", type=int, default=5)
     p.add_argument("--extra-levels", type=int, default=3)
     p.add_argument("--no-cpu-baseline", action="store_true")
@@ -50,7 +55,7 @@ def parse():
 def workload_name(a):
     fine = 2 ** (a.init_refine + 1 + a.extra_levels)
     return (f"config4: shell tree {2 ** (a.init_refine + 1)}^3 -> {fine}^3, SH9 (K=28), "
-            f"{a.rays} rays/step, MSE, backward into data.grad")
+            f"{a.rays} rays/step/GPU, MSE, backward into data.grad")
 
 
 def peaks():
@@ -157,7 +162,7 @@ def run_reference(a):
     info["value"] = val
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT,
             "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic", "config": {"workload": workload_name(a),
                                             "l2": "inputs larger than L2"},
             "cpu_baseline": info,
@@ -186,14 +191,17 @@ def run_b200(a):
     tree_cpu, rays_cpu, targets_cpu = W.config4(Q=a.rays, init_refine=a.init_refine,
                                                 extra_levels=a.extra_levels)
     Q = a.rays
-    lo, hi = D.shard_bounds(Q, rank, world)
+    if rank > 0:   # every rank draws its own rays and targets for the same scene
+        gen = torch.Generator().manual_seed(3 + 1000 * rank)
+        rays_cpu = W.sphere_rays(Q, gen, 4.0, 0.2, 0.8)
+        targets_cpu = torch.rand(Q, 3, generator=gen)
     tree = tree_cpu.to(dev)
-    rays_h = [t[lo:hi].contiguous().pin_memory() for t in rays_cpu]
-    tg_h = targets_cpu[lo:hi].contiguous().pin_memory()
+    rays_h = [t.contiguous().pin_memory() for t in rays_cpu]
+    tg_h = targets_cpu.contiguous().pin_memory()
     rays = svox_b200.Rays(*[t.to(dev) for t in rays_h])
     targets = tg_h.to(dev)
     renderer = svox_b200.VolumeRenderer(tree)
-    denom = float(Q * 3)
+    denom = float(Q * world * 3)
 
     def step(r=rays, tg=targets):
         tree.zero_grad(set_to_none=True)
@@ -229,7 +237,7 @@ def run_b200(a):
     # byte model: exact per-ray visit / contribution counts of this rank's rays
     vis, cf, cb = csrc.march_stats(tree._spec(), svox_b200.render._rays_spec_from_rays(rays),
                                    renderer._get_options())
-    n_local = hi - lo
+    n_local = Q
     K = tree.data_dim
     sums = torch.stack([vis.sum(), cf.sum(), cb.sum()]).double()
     fwd_bytes = n_local * 48 + 8 * sums[0].item() + 4 * (K - 1) * sums[1].item()
@@ -262,32 +270,44 @@ def run_b200(a):
                "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e}
 
     peak, peak_src = peaks()
+    total = Q * world
+    if e2e is not None:
+        e2e["value"] = total / e2e["ms_per_step"] / 1e3
     line = {
-        "metric": METRIC, "value": Q / ms_step / 1e3, "unit": UNIT, "n_gpus": world,
+        "metric": METRIC, "value": total / ms_step / 1e3, "unit": UNIT, "n_gpus": world,
         "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms_step,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
         "config": {"workload": workload_name(a), "rays_per_gpu": n_local,
+                   "rays_per_step": total,
                    "parallelism": f"rays sharded x{world}, tree replicated, "
                                   + ("NCCL all-reduce of data.grad" if world > 1 else "no collective"),
                    "l2": "inputs larger than L2 (1.18 GB tree data vs 126 MB)",
                    "visits_per_ray": sums[0].item() / n_local,
                    "contrib_per_ray": sums[2].item() / n_local},
-        "roofline": {"bound": "hbm", "kernel": "render_bwd_sh (volume_render_backward)",
-                     "achieved": bwd_bytes / ms_bwd / 1e6, "peak": peak, "unit": "GB/s",
-                     "frac": bwd_bytes / ms_bwd / 1e6 / peak, "traffic": None,
-                     "peak_source": peak_src, "ms_per_launch": ms_bwd,
-                     "algorithmic_bytes_per_launch": bwd_bytes},
-        "roofline_forward": {"bound": "hbm", "kernel": "render_fwd_sh (volume_render)",
-                             "achieved": fwd_bytes / ms_fwd / 1e6, "peak": peak, "unit": "GB/s",
-                             "frac": fwd_bytes / ms_fwd / 1e6 / peak, "ms_per_launch": ms_fwd,
-                             "algorithmic_bytes_per_launch": fwd_bytes},
+        # dominant kernel: the logged forward march (render_queue_kernel).  `traffic` is the
+        # DRAM read + write of one launch from the committed ncu capture of this workload.
+        "roofline": {"bound": "hbm", "kernel": "render_queue_kernel, logged forward (volume_render)",
+                     "achieved": fwd_bytes / ms_fwd / 1e6, "peak": peak, "unit": "GB/s",
+                     "frac": fwd_bytes / ms_fwd / 1e6 / peak,
+                     "traffic": NCU_TRAFFIC_FWD if Q == 1 << 20 else None,
+                     "peak_source": peak_src, "ms_per_launch": ms_fwd,
+                     "algorithmic_bytes_per_launch": fwd_bytes},
+        "roofline_backward": {"bound": "hbm",
+                              "kernel": "replay_bin_kernel + replay_scatter_kernel "
+                                        "(volume_render_backward)",
+                              "achieved": bwd_bytes / ms_bwd / 1e6, "peak": peak, "unit": "GB/s",
+                              "frac": bwd_bytes / ms_bwd / 1e6 / peak,
+                              "traffic": NCU_TRAFFIC_BWD if Q == 1 << 20 else None,
+                              "ms_per_launch": ms_bwd,
+                              "algorithmic_bytes_per_launch": bwd_bytes},
         "roofline_step": {"algorithmic_bytes": fwd_bytes + bwd_bytes,
                           "achieved": (fwd_bytes + bwd_bytes) / ms_step / 1e6,
                           "frac": (fwd_bytes + bwd_bytes) / ms_step / 1e6 / peak},
         "e2e": e2e,
-        # per step, forward and backward each: jump-table build, annotation pass, render kernel
-        "gpu_launches": 6 * a.steps,
+        # per step: forward = annotate, leaf table, brick assign, brick fill, march;
+        # backward = prefix, ray pack, bin, scatter
+        "gpu_launches": 9 * a.steps,
         "clocks": clocks,
     }
     if rank == 0 and world == 1 and not a.no_cpu_baseline:

@@ -149,6 +149,7 @@ struct Tuning {
     int query_top_level = -1;
     int render_algo = 2;        // 2 = item queue, 0 = warp-cooperative, 1 = one thread per ray
     int replay_bin_mb = 16;     // gradient bytes one replay bin spans
+    int refill_batch = 4;       // queue kernels: lanes that must be idle before rays are loaded
     int render_bricks = 1;      // queue kernels: bricks below the leaf table
     int replay_flags = 3;       // replay scatter: 1 = packets evict-first, 2 = gradient evict-last
 };

@@ -134,6 +134,9 @@ __device__ __forceinline__ int32_t ld_keep(const int32_t* a, uint64_t pol) {
     asm volatile("ld.global.nc.L2::cache_hint.s32 %0, [%1], %2;" : "=r"(v) : "l"(a), "l"(pol));
     return v;
 }
+__device__ __forceinline__ void st_stream(int32_t* a, int32_t v, uint64_t pol) {
+    asm volatile("st.global.L2::cache_hint.s32 [%0], %1, %2;" ::"l"(a), "r"(v), "l"(pol) : "memory");
+}
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, uint64_t pol) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(s),
@@ -274,7 +277,7 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                     int top_bytes, int64_t Q, float* __restrict__ out,
                     const float* __restrict__ grad_out, const float* __restrict__ fwd_out,
                     float* __restrict__ grad_data, int32_t* __restrict__ log,
-                    int64_t log_capacity, int log_shift) {
+                    int64_t log_capacity, int log_shift, int refill_batch) {
     constexpr int K = 3 * BD + 1;
     constexpr bool BWD = MODE == kModeBackward;
     constexpr bool LOG = MODE == kModeForwardLogged;
@@ -489,18 +492,20 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                 if (lane < nb) {
                     const float* res = q.rows + lane * Shape::STRIDE;
                     const uint32_t sl = q.slot[lane];
-                    ch[32 * 1 + lane] = (int32_t)sl;
-                    ch[32 * 2 + lane] = q.rayid[lane];
-                    ch[32 * 3 + lane] = __float_as_int(q.w[lane]);
-                    ch[32 * 4 + lane] = __float_as_int(q.T[lane]);
-                    ch[32 * 5 + lane] = __float_as_int(q.dd[lane]);
-                    ch[32 * 6 + lane] = __float_as_int(sg[0]);
-                    ch[32 * 7 + lane] = __float_as_int(sg[1]);
-                    ch[32 * 8 + lane] = __float_as_int(sg[2]);
-                    ch[32 * 9 + lane] = __float_as_int(res[0]);
-                    ch[32 * 10 + lane] = __float_as_int(res[1]);
-                    ch[32 * 11 + lane] = __float_as_int(res[2]);
-                    const uint32_t bin = sl >> log_shift;
+                    st_stream(ch + 32 * 1 + lane, (int32_t)sl, pol_stream);
+                    st_stream(ch + 32 * 2 + lane, q.rayid[lane], pol_stream);
+                    st_stream(ch + 32 * 3 + lane, __float_as_int(q.w[lane]), pol_stream);
+                    st_stream(ch + 32 * 4 + lane, __float_as_int(q.T[lane]), pol_stream);
+                    st_stream(ch + 32 * 5 + lane, __float_as_int(q.dd[lane]), pol_stream);
+                    st_stream(ch + 32 * 6 + lane, __float_as_int(sg[0]), pol_stream);
+                    st_stream(ch + 32 * 7 + lane, __float_as_int(sg[1]), pol_stream);
+                    st_stream(ch + 32 * 8 + lane, __float_as_int(sg[2]), pol_stream);
+                    st_stream(ch + 32 * 9 + lane, __float_as_int(res[0]), pol_stream);
+                    st_stream(ch + 32 * 10 + lane, __float_as_int(res[1]), pol_stream);
+                    st_stream(ch + 32 * 11 + lane, __float_as_int(res[2]), pol_stream);
+                }
+                if (lane < nb) {
+                    const uint32_t bin = q.slot[lane] >> log_shift;
                     atomicAdd(&s_hist[bin < (uint32_t)kMaxBins ? bin : kMaxBins - 1], 1);
                 }
             }
@@ -621,7 +626,12 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                     state = kNeedRay;
                 }
             }
-            if (state == kNeedRay) {
+            // Refills are taken a few lanes at a time: the set-up of a ray is some hundred
+            // instructions, which a single active lane would make the whole warp pay for.
+            const unsigned need = __ballot_sync(0xffffffffu, state == kNeedRay);
+            const bool refill_now = __popc(need) >= refill_batch ||
+                                    __ballot_sync(0xffffffffu, state == kMarching) == 0u;
+            if (state == kNeedRay && refill_now) {
                 const unsigned ticket = atomicAdd(&s_next, 1u);
                 const int64_t gran = (int64_t)blockIdx.x + (int64_t)gridDim.x * (ticket >> 5);
                 ray = gran * 32 + (ticket & 31);

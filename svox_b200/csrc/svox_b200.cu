@@ -171,13 +171,13 @@ static int launch_queue_block(const RenderCall& c, const Source& src, const Tree
         if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
         k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, (int)top_bytes, c.Q, c.out,
                                           nullptr, nullptr, nullptr, c.log, c.log_capacity,
-                                          replay_bin_shift(c.tree->M, K));
+                                          replay_bin_shift(c.tree->M, K), g_tuning.refill_batch);
     } else if (!c.backward) {
         const size_t smem = top_bytes + (size_t)(BLOCK / 32) * sizeof(WarpQueue<K, kModeForward>);
         auto k = render_queue_kernel<BD, BLOCK, kModeForward, Source>;
         if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
         k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, (int)top_bytes, c.Q, c.out,
-                                          nullptr, nullptr, nullptr, nullptr, 0, 0);
+                                          nullptr, nullptr, nullptr, nullptr, 0, 0, g_tuning.refill_batch);
     } else {
         const size_t smem = top_bytes + (size_t)(BLOCK / 32) * sizeof(WarpQueue<K, kModeBackward>);
         const bool single = c.fwd_out != nullptr && c.opt.sigma_thresh == 0.f &&
@@ -186,7 +186,7 @@ static int launch_queue_block(const RenderCall& c, const Source& src, const Tree
         if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
         k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, (int)top_bytes, c.Q, nullptr,
                                           c.grad_out, single ? c.fwd_out : nullptr, c.grad_data,
-                                          nullptr, 0, 0);
+                                          nullptr, 0, 0, g_tuning.refill_batch);
     }
     SVOXB_CUDA(cudaGetLastError());
     return SVOXB_OK;
@@ -323,11 +323,13 @@ static int launch_queue(const RenderCall& c, const Source& src) {
     const size_t per_warp = c.backward ? sizeof(WarpQueue<K, kModeBackward>)
                             : c.log    ? sizeof(WarpQueue<K, kModeForwardLogged>)
                                        : sizeof(WarpQueue<K, kModeForward>);
-    int want = g_tuning.render_block > 0 ? g_tuning.render_block : 768;
+    // 640 threads: the kernel needs ~90 registers; at 768 (80 registers) it spills in the loop
+    int want = g_tuning.render_block > 0 ? g_tuning.render_block : 640;
     while (want > 256 && top_bytes + (size_t)(want / 32) * per_warp + 64 > kMaxSmem) want -= 128;
     if constexpr (BD <= 9) {
         if (want >= 1024) return launch_queue_block<BD, 1024>(c, src, tr, top, top_bytes);
         if (want >= 768) return launch_queue_block<BD, 768>(c, src, tr, top, top_bytes);
+        if (want >= 640) return launch_queue_block<BD, 640>(c, src, tr, top, top_bytes);
     }
     if constexpr (BD <= 16) {
         if (want >= 512) return launch_queue_block<BD, 512>(c, src, tr, top, top_bytes);
@@ -754,6 +756,7 @@ int svoxb_tune(int key, int value) {
         case 3: g_tuning.render_algo = value; return SVOXB_OK;
         case 6: g_tuning.replay_flags = value; return SVOXB_OK;
         case 7: g_tuning.render_bricks = value; return SVOXB_OK;
+        case 8: g_tuning.refill_batch = value; return SVOXB_OK;
         case 5:
             if (value < 1 || value > 1024) return SVOXB_ERR_OPTION;
             g_tuning.replay_bin_mb = value;
