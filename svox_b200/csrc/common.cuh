@@ -48,7 +48,7 @@ struct LeafHit {
 struct TopTable {
     const int32_t* cells;  // shared or global memory
     int level;             // L (0 = no table)
-    const int2* bricks = nullptr;  // queue kernels only: see render_queue.cuh
+    const int32_t* bricks = nullptr;  // queue kernels only: see render_queue.cuh
 };
 
 // Descent of query_single_from_root (svox/csrc/include/common.cuh:52-90) for

@@ -80,17 +80,21 @@ constexpr int kLogGrab = 8;  // chunks a warp takes per bump of the allocation c
 constexpr int kCoordBits = 24;  // integer coordinates: floor(x * 2^24), exact for float x < 1
 
 // Bricks: every inner cell of the leaf table gets the 8x8x8 grid of the three
-// levels below it, 8 bytes per fine cell:
-//   .x  the annotated child entry of the leaf that covers the fine cell (<= 0), or, if
-//       the tree goes deeper there, the id (> 0) of the node three levels down
-//   .y  leaf slot (bits 0-27) and leaf depth minus (table level + 1) (bits 28-29)
+// levels below it: 512 CELL words followed by 64 GROUP words (one per 2x2x2
+// group of fine cells), 2304 bytes per brick.
+//   cell   the annotated child entry of the leaf that covers the fine cell (<= 0), or, if
+//          the tree goes deeper there, the link (> 0) from the group's node to the child
+//   group  bits 28-29 = k, bits 0-27 = payload: k = 2: the group's fine cells are the
+//          children of node `payload`; k = 1 / k = 0: the whole group lies in a leaf one /
+//          two levels up, whose slot is `payload`
 // A table cell with a brick holds kBrickFlag + brick id instead of the node id.
-// Samples in refined regions then cost one dependent load, like samples in
-// empty space; trees deeper than table level + 3 continue from the brick entry
-// through the annotated child array.  Table cells beyond the brick budget keep
-// their node id and are walked level by level.
+// Samples in refined regions then cost one round trip (two independent loads),
+// like samples in empty space; trees deeper than table level + 3 continue from
+// the brick entry through the annotated child array.  Table cells beyond the
+// brick budget keep their node id and are walked level by level.
 constexpr int kBrickLevels = 3;
 constexpr int kBrickCells = 512;
+constexpr int kBrickWords = kBrickCells + 64;
 constexpr int32_t kBrickFlag = 1 << 30;
 constexpr int64_t kBrickMaxNodes = 1 << 25;  // slots must fit 28 bits
 constexpr int kMaxBricks = 1 << 16;
@@ -204,40 +208,43 @@ __global__ void assign_bricks_kernel(int32_t* __restrict__ cells, int n_cells, i
 __global__ void __launch_bounds__(kBrickCells)
 fill_bricks_kernel(const int32_t* __restrict__ annotated, int64_t M, int L, int cap,
                    const int32_t* __restrict__ counter, const int32_t* __restrict__ roots,
-                   int2* __restrict__ bricks) {
+                   int32_t* __restrict__ bricks) {
     int n = *counter;
     if (n > cap) n = cap;
     if ((int)blockIdx.x >= n) return;
     const int c = threadIdx.x;
     const int x = c >> 6, y = (c >> 3) & 7, z = c & 7;
     int64_t node = roots[blockIdx.x];
-    int2 out = make_int2(0, 0);
+    int32_t cell_word = 0;
+    uint32_t group_word = 0;
     bool done = false;
     for (int l = 0; l < kBrickLevels && !done; ++l) {
         const int sh = kBrickLevels - 1 - l;
         const int cell = (((x >> sh) & 1) << 2) | (((y >> sh) & 1) << 1) | ((z >> sh) & 1);
         const int32_t e = annotated[node * 8 + cell];
-        if (e <= 0) {
-            out = make_int2(e, (int)((uint32_t)(node * 8 + cell) | ((uint32_t)l << 28)));
+        if (l == kBrickLevels - 1) {
+            // fine cell: leaf code or link, both relative to the group's node
+            cell_word = e;
+            if (e > 0 && node + e >= M) cell_word = (int32_t)(M - node);  // reported by the march
+            group_word = (2u << 28) | (uint32_t)node;
+            done = true;
+        } else if (e <= 0) {
+            cell_word = e;
+            group_word = ((uint32_t)l << 28) | (uint32_t)(node * 8 + cell);
             done = true;
         } else {
             node += e;
-            if (node >= M) {  // corrupt link: the marching kernel reports it
-                out = make_int2((int32_t)M, 0);
+            if (node >= M) {  // corrupt link: reported by the march via an out-of-range link
+                cell_word = 1;
+                group_word = (2u << 28) | (uint32_t)(M - 1);
                 done = true;
             }
         }
     }
-    if (!done) out = make_int2((int32_t)node, 0);
-    bricks[(size_t)blockIdx.x * kBrickCells + c] = out;
-}
-
-__device__ __forceinline__ int2 ld_keep2(const int2* a, uint64_t pol) {
-    int2 v;
-    asm volatile("ld.global.nc.L2::cache_hint.v2.s32 {%0, %1}, [%2], %3;"
-                 : "=r"(v.x), "=r"(v.y)
-                 : "l"(a), "l"(pol));
-    return v;
+    int32_t* brick = bricks + (size_t)blockIdx.x * kBrickWords;
+    brick[c] = cell_word;
+    if (((x | y | z) & 1) == 0)
+        brick[kBrickCells + ((x >> 1) << 4 | (y >> 1) << 2 | (z >> 1))] = (int32_t)group_word;
 }
 
 __device__ __forceinline__ void cp_async_wait_all() {
@@ -363,10 +370,11 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
     auto request_entry = [&]() {
         if (kind == kFromBrick) {
             const int sh = kCoordBits - base - kBrickLevels;
-            const int c = (((ix >> sh) & 7) << 6) | (((iy >> sh) & 7) << 3) | ((iz >> sh) & 7);
-            const int2 v = ld_keep2(top.bricks + ((size_t)cur_brick * kBrickCells + c), pol_keep);
-            e_pre = v.x;
-            e_aux = v.y;
+            const int x = (ix >> sh) & 7, y = (iy >> sh) & 7, z = (iz >> sh) & 7;
+            const int32_t* brick = top.bricks + (size_t)cur_brick * kBrickWords;
+            e_pre = ld_keep(brick + ((x << 6) | (y << 3) | z), pol_keep);
+            e_aux = ld_keep(brick + kBrickCells + (((x >> 1) << 4) | ((y >> 1) << 2) | (z >> 1)),
+                            pol_keep);
         } else if (kind == kFromTable) {
             e_pre = ld_keep(top.cells + tab_idx, pol_keep);
         } else {
@@ -700,8 +708,10 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
             bool go = true, is_leaf = false, have_slot = false;
             int depth = 0;
             if (kind == kFromBrick) {
+                const int gk = (int)((uint32_t)e_aux >> 28);
+                const uint32_t payload = (uint32_t)e_aux & 0x0fffffffu;
                 if (e > 0) {                    // deeper than the brick: go on from that node
-                    node = e;
+                    node = (int)payload + e;
                     lvl = base + kBrickLevels;
                     kind = kFromChild;
                     if (node >= M || lvl >= kCoordBits) {
@@ -712,8 +722,14 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                 } else {
                     is_leaf = true;
                     have_slot = true;
-                    depth = base + 1 + (int)((uint32_t)e_aux >> 28);
-                    slot = (uint32_t)e_aux & 0x0fffffffu;
+                    depth = base + 1 + gk;
+                    if (gk == 2) {
+                        const int b = kCoordBits - depth;
+                        slot = payload * 8u + (uint32_t)((((ix >> b) & 1) << 2) |
+                                                         (((iy >> b) & 1) << 1) | ((iz >> b) & 1));
+                    } else {
+                        slot = payload;
+                    }
                 }
             } else if (kind == kFromTable) {
                 if (e >= kBrickFlag) {          // the cell has a brick: look the sample up there

@@ -261,7 +261,7 @@ static int launch_replay(const RenderCall& c, const Source& src, int64_t chunks)
 struct QueueScratch {
     int32_t* annotated = nullptr;
     int32_t* table = nullptr;
-    int2* bricks = nullptr;
+    int32_t* bricks = nullptr;
     int level = 0;
     cudaStream_t stream = nullptr;
     int build(const svoxb_tree* t, float thresh, int softplus, int max_level, cudaStream_t s) {
@@ -282,7 +282,7 @@ struct QueueScratch {
         if (st) return st;
         SVOXB_CUDA(cudaMallocAsync((void**)&annotated,
                                    head * sizeof(int32_t) +
-                                       (size_t)cap * kBrickCells * sizeof(int2), s));
+                                       (size_t)cap * kBrickWords * sizeof(int32_t), s));
         table = annotated + n;
         annotate_sigma_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(
             t->child, t->data, t->K, n, thresh, softplus, annotated);
@@ -295,7 +295,7 @@ struct QueueScratch {
         if (cap > 0) {
             int32_t* counter = table + cells;
             int32_t* roots = counter + 8;
-            bricks = reinterpret_cast<int2*>(annotated + head);
+            bricks = annotated + head;
             SVOXB_CUDA(cudaMemsetAsync(counter, 0, sizeof(int32_t), s));
             assign_bricks_kernel<<<(unsigned)((cells + 255) / 256), 256, 0, s>>>(
                 table, (int)cells, (int)cap, counter, roots);
