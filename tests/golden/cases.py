@@ -225,5 +225,35 @@ CASES = {f.__name__: f for f in [
     opt_comp_range, rgba_rays, sh1_rays, sh25_rays, aniso_rays, aniso_image, ndc_image, n3_rays,
     query_c1, query_aniso, query_shell]}
 
+
+
+def deep_rays():
+    """A thin region refined to depth 10 around one point of a coarse tree: leaves far below the
+    leaf table and its bricks, and leaves of every depth in between.  Oracle only (no fixture)."""
+    gen = _g(120)
+    tree = N3Tree(N=2, data_format="SH4", init_refine=1)
+    p0 = torch.tensor([0.371, 0.412, 0.455])
+    for k in range(8):
+        centers = W._leaf_centers(tree)
+        mask = (centers - p0).abs().max(dim=-1).values < 0.6 * 0.5 ** (k + 2)
+        tree[mask].refine()
+    with torch.no_grad():
+        d = tree.data.data
+        d[..., :-1] = torch.randn(d[..., :-1].shape, generator=gen)
+        sig = torch.rand(d[..., -1].shape, generator=gen) * 40.0
+        sig[torch.rand(sig.shape, generator=gen) < 0.3] = 0.0
+        d[..., -1] = sig
+    Q = 4096
+    origins = 0.5 + 3.0 * _unit(torch.randn(Q, 3, generator=gen))
+    targets = p0 + (torch.rand(Q, 3, generator=gen) - 0.5) * 0.02
+    targets[Q // 2:] = 0.2 + 0.6 * torch.rand(Q - Q // 2, 3, generator=gen)
+    dirs = _unit(targets - origins)
+    return _base(tree, "rays", rays=Rays(origins, dirs, dirs),
+                 grad_out=torch.randn(Q, 3, generator=gen))
+
+
+# Cases without a reference fixture: checked against the oracle only.
+EXTRA_CASES = {f.__name__: f for f in [deep_rays]}
+
 # Cases whose fixtures are cheap enough to check on the CPU in the default test run.
 BIG = {"c4_sample_rays"}

@@ -16,7 +16,7 @@ import torch
 
 import parity_util as P
 import svox_b200 as svox
-from golden.cases import CASES
+from golden.cases import CASES, EXTRA_CASES
 from svox_b200 import csrc
 from svox_b200 import workloads as W
 
@@ -84,6 +84,40 @@ def test_replay_backward_matches_marching_backward(name, cuda_device):
     orc = P.run_oracle(case)
     assert P.grad_excess(a["grad"], orc["grad"], orc["grad_abs"], GRAD_TOL_ORACLE) <= 1.0
     assert P.grad_excess(a["grad"], b["grad"], orc["grad_abs"], GRAD_TOL_REF) <= 2.5
+
+
+@pytest.mark.parametrize("name", list(EXTRA_CASES))
+def test_case_without_fixture_against_oracle(name, cuda_device):
+    # e.g. leaves far below the leaf table and its bricks
+    case = EXTRA_CASES[name]()
+    orc = P.run_oracle(case)
+    for item_log in (True, False):
+        mine = P.run_product(case, cuda_device, item_log=item_log)
+        assert np.abs(mine["out"] - orc["out"]).max() <= RGB_TOL
+        assert P.grad_excess(mine["grad"], orc["grad"], orc["grad_abs"], GRAD_TOL_ORACLE) <= 1.0
+
+
+@pytest.mark.parametrize("name", ["shell_sh9_rays", "aniso_rays", "deep_rays"])
+def test_bricks_and_bin_size_do_not_change_results(name, cuda_device):
+    # The bricks below the leaf table are an index, not data: with and without them
+    # the render is bit-identical.  The replay backward gives the same gradient
+    # whatever the bin size (1 MB bins: hundreds of bins on the shell scene).
+    case = (CASES.get(name) or EXTRA_CASES[name])()
+    lib = csrc.library()
+    orc = P.run_oracle(case)
+    try:
+        base = P.run_product(case, cuda_device)
+        assert lib.svoxb_tune(7, 0) == 0
+        plain = P.run_product(case, cuda_device)
+        assert np.array_equal(base["out"], plain["out"])
+        assert P.grad_excess(base["grad"], plain["grad"], orc["grad_abs"], GRAD_TOL_REF) <= 2.5
+        assert lib.svoxb_tune(7, 1) == 0 and lib.svoxb_tune(5, 1) == 0
+        fine = P.run_product(case, cuda_device)
+        assert np.array_equal(base["out"], fine["out"])
+        assert P.grad_excess(base["grad"], fine["grad"], orc["grad_abs"], GRAD_TOL_REF) <= 2.5
+    finally:
+        lib.svoxb_tune(7, 1)
+        lib.svoxb_tune(5, 16)
 
 
 def test_item_log_overflow_falls_back(cuda_device):
