@@ -67,20 +67,38 @@ query_kernel(TreeArgs tr, TopTable top, const float* __restrict__ pts, int64_t Q
     const int total = nvalid * K;
     int p = 0, e = lane;  // element j = p*K + e of the warp's (nvalid, K) block
     while (e >= K) { e -= K; ++p; }
-#pragma unroll 4
-    for (int base = 0; base < total; base += 32) {
-        const int j = base + lane;
-        const int src_lane = p < nvalid ? p : nvalid - 1;
-        const int64_t s = __shfl_sync(0xffffffffu, slot, src_lane);
-        if (j < total && s >= 0) {
-            if (MODE == 0) {
-                values_out[wb * K + j] = __ldg(tr.data + s * K + e);
-            } else {
-                atomicAdd(grad_data + s * K + e, __ldg(grad_out + wb * K + j));
+    // Batches of kBatch steps: all loads of a batch are issued before the first store, so that
+    // a warp keeps kBatch 128-byte requests in flight (the path is bound by memory latency).
+    constexpr int kBatch = 8;
+    for (int base = 0; base < total; base += 32 * kBatch) {
+        float v[kBatch];
+        int64_t dst[kBatch];
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            const int j = base + 32 * u + lane;
+            const int src_lane = p < nvalid ? p : nvalid - 1;
+            const int64_t s = __shfl_sync(0xffffffffu, slot, src_lane);
+            dst[u] = -1;
+            v[u] = 0.f;
+            if (j < total && s >= 0) {
+                if (MODE == 0) {
+                    v[u] = __ldg(tr.data + s * K + e);
+                    dst[u] = wb * K + j;
+                } else {
+                    v[u] = __ldg(grad_out + wb * K + j);
+                    dst[u] = s * K + e;
+                }
+            }
+            e += 32;
+            while (e >= K) { e -= K; ++p; }
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            if (dst[u] >= 0) {
+                if (MODE == 0) values_out[dst[u]] = v[u];
+                else atomicAdd(grad_data + dst[u], v[u]);
             }
         }
-        e += 32;
-        while (e >= K) { e -= K; ++p; }
     }
 }
 
@@ -91,7 +109,7 @@ static int launch_query(int mode, const svoxb_tree* tree, const float* indices, 
     if (!indices) return SVOXB_ERR_NULL;
     if ((Q + kQueryBlock - 1) / kQueryBlock > 0x7fffffffLL) return SVOXB_ERR_TOO_LARGE;
     TopScratch top;
-    const int max_level = g_tuning.query_top_level >= 0 ? g_tuning.query_top_level : 5;
+    const int max_level = g_tuning.query_top_level >= 0 ? g_tuning.query_top_level : 7;
     int st = top.build(tree, max_level > 7 ? 7 : max_level, stream);
     if (st) return st;
     const TopTable tt{top.cells, top.level};
