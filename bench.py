@@ -49,6 +49,9 @@ def parse():
     p.add_argument("--extra-levels", type=int, default=3)
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--overlap-parts", type=int, default=4,
+                   help="N > 1: leaf ranges whose all-reduce overlaps the backward (0 = one "
+                        "all-reduce after the backward)")
     return p.parse_args()
 
 
@@ -187,6 +190,7 @@ def run_b200(a):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+        D.overlap_grad_allreduce(a.overlap_parts)
 
     tree_cpu, rays_cpu, targets_cpu = W.config4(Q=a.rays, init_refine=a.init_refine,
                                                 extra_levels=a.extra_levels)
@@ -281,7 +285,10 @@ def run_b200(a):
         "config": {"workload": workload_name(a), "rays_per_gpu": n_local,
                    "rays_per_step": total,
                    "parallelism": f"rays sharded x{world}, tree replicated, "
-                                  + ("NCCL all-reduce of data.grad" if world > 1 else "no collective"),
+                                  + ((f"NCCL all-reduce of data.grad in {a.overlap_parts} leaf ranges, "
+                                      "overlapped with the backward scatter" if a.overlap_parts
+                                      else "one NCCL all-reduce of data.grad")
+                                     if world > 1 else "no collective"),
                    "l2": "inputs larger than L2 (1.18 GB tree data vs 126 MB)",
                    "visits_per_ray": sums[0].item() / n_local,
                    "contrib_per_ray": sums[2].item() / n_local},

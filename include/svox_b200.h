@@ -169,6 +169,30 @@ int svoxb_volume_render_image_backward_replay(const svoxb_tree* tree, const svox
                                               int32_t* log, int64_t capacity_chunks,
                                               int64_t chunks_used, float* grad_data_out,
                                               int zero_first, void* stream);
+/* The replay backward in steps, for callers that overlap the all-reduce of the
+ * gradient with its computation (no counterpart in the reference).  _begin
+ * sorts the logged samples by leaf range (arguments as for
+ * svoxb_volume_render_backward_replay; SVOXB_ERR_TOO_LARGE if the scratch
+ * cannot be had) and returns a job.  The leaf slots are cut into `n_parts`
+ * (1..16) consecutive ranges; svoxb_replay_part_range gives the slots
+ * [begin, end) of a part, i.e. rows [begin*K, end*K) of the flat gradient.
+ * svoxb_replay_scatter adds the gradient of one part into grad_data_out (the
+ * caller zeroes it first); with reserve_sms > 0 it leaves that many SMs free
+ * for a collective kernel running beside it.  After a part's scatter the rows
+ * of that part are final.  svoxb_replay_end releases the scratch on `stream`. */
+int svoxb_replay_begin(const svoxb_tree* tree, const svoxb_rays* rays,
+                       const svoxb_render_options* opt, const float* grad_output,
+                       const float* fwd_out, int32_t* log, int64_t capacity_chunks,
+                       int64_t chunks_used, int n_parts, void* stream, void** job);
+int svoxb_replay_image_begin(const svoxb_tree* tree, const svoxb_camera* cam,
+                             const svoxb_render_options* opt, const float* grad_output,
+                             const float* fwd_out, int32_t* log, int64_t capacity_chunks,
+                             int64_t chunks_used, int n_parts, void* stream, void** job);
+int svoxb_replay_part_range(const void* job, int part, int64_t* slot_begin, int64_t* slot_end);
+int svoxb_replay_scatter(const void* job, int part, float* grad_data_out, int reserve_sms,
+                         void* stream);
+int svoxb_replay_end(void* job, void* stream);
+
 /* Chunks the logged forward needed (synchronises `stream`). */
 int svoxb_item_log_used(const int32_t* log, int64_t* chunks_used, void* stream);
 

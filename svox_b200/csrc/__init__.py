@@ -19,6 +19,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libsvox_b200.so")
 
 FORMAT_RGBA, FORMAT_SH, FORMAT_SG, FORMAT_ASG = 0, 1, 2, 3
+ERR_TOO_LARGE = 8   # svoxb status: a size limit or the scratch allocation
 
 
 class _CTree(C.Structure):
@@ -354,21 +355,27 @@ def log_chunks_used(log):
     return used.value
 
 
+def _log_usage(log, cap, n_rays):
+    """Chunks used by the logged forward; adapts the per-ray estimate for the next log."""
+    global _items_per_ray
+    used = log_chunks_used(log)
+    _log_usage.last = used
+    if n_rays:
+        # chunks are 32 items, partly filled ones included: keep 25 % head room
+        need = max(8.0, 1.25 * 32.0 * used / n_rays)
+        _items_per_ray = need if used > cap else max(need, 0.9 * _items_per_ray)
+    return used
+
+
 def volume_render_backward_replay(tree, rays_or_cam, opt, grad_output, fwd_out, logpair,
                                   image=False):
     """Gradient w.r.t. data from the item log of ``volume_render_logged``; returns None if
     the log overflowed (the caller then uses ``volume_render[_image]_backward``)."""
-    global _items_per_ray
     lib = library()
     log, cap = logpair
     dev = tree.data.device
     with torch.cuda.device(dev):
-        used = log_chunks_used(log)
-        n = fwd_out.numel() // 3
-        if n:
-            # chunks are 32 items, partly filled ones included: keep 25 % head room
-            need = max(8.0, 1.25 * 32.0 * used / n)
-            _items_per_ray = need if used > cap else max(need, 0.9 * _items_per_ray)
+        used = _log_usage(log, cap, fwd_out.numel() // 3)
         if used > cap:
             return None
         ct = _pack_tree(tree)
@@ -388,6 +395,64 @@ def volume_render_backward_replay(tree, rays_or_cam, opt, grad_output, fwd_out, 
                     C.c_int64(used), C.c_void_p(grad.data_ptr()), C.c_int(0), _stream())
     if st:
         _raise(st, "volume_render_backward_replay")
+    return grad
+
+
+def volume_render_backward_replay_parts(tree, rays_or_cam, opt, grad_output, fwd_out, logpair,
+                                        n_parts, on_part, agree=None, reserve_sms=0,
+                                        image=False):
+    """The replay backward in ``n_parts`` consecutive leaf ranges.  After each part
+    ``on_part(rows)`` is called with the flat view of the gradient rows that are final
+    (e.g. to start their all-reduce while the next part is computed).  ``agree(ok)``, if
+    given, is called once with whether this process can replay and returns whether all
+    processes can (they must take the same route when ``on_part`` runs a collective).
+    Returns None if the replay was not possible (nothing has been handed to ``on_part``)."""
+    lib = library()
+    log, cap = logpair
+    dev = tree.data.device
+    with torch.cuda.device(dev):
+        ok = _log_usage(log, cap, fwd_out.numel() // 3) <= cap
+        used = _log_usage.last if ok else 0
+        ct = _pack_tree(tree)
+        co = opt._pack()
+        _check_input(grad_output, "grad_output")
+        _check_input(fwd_out, "fwd_out")
+        if image:
+            cs = _pack_camera(rays_or_cam, dev)
+            begin = lib.svoxb_replay_image_begin
+        else:
+            cs = _pack_rays(rays_or_cam, dev)
+            begin = lib.svoxb_replay_begin
+        job = C.c_void_p(None)
+        with _timed("volume_render_backward"):
+            if ok:
+                st = begin(C.byref(ct), C.byref(cs), C.byref(co),
+                           C.c_void_p(grad_output.data_ptr()), C.c_void_p(fwd_out.data_ptr()),
+                           C.c_void_p(log.data_ptr()), C.c_int64(cap), C.c_int64(used),
+                           C.c_int(n_parts), _stream(), C.byref(job))
+                if st and st != ERR_TOO_LARGE:
+                    _raise(st, "replay_begin")
+                ok = st == 0
+            if agree is not None:
+                ok = bool(agree(ok))
+            if not ok:
+                if job:
+                    lib.svoxb_replay_end(job, _stream())
+                return None
+            grad = torch.zeros_like(tree.data, memory_format=torch.contiguous_format)
+            flat = grad.view(-1)
+            K = tree.data.shape[-1]
+            try:
+                lo, hi = C.c_int64(0), C.c_int64(0)
+                for part in range(n_parts):
+                    st = lib.svoxb_replay_scatter(job, C.c_int(part), C.c_void_p(grad.data_ptr()),
+                                                  C.c_int(reserve_sms), _stream())
+                    if st:
+                        _raise(st, "replay_scatter")
+                    lib.svoxb_replay_part_range(job, C.c_int(part), C.byref(lo), C.byref(hi))
+                    on_part(flat[lo.value * K:hi.value * K])
+            finally:
+                lib.svoxb_replay_end(job, _stream())
     return grad
 
 

@@ -33,6 +33,7 @@
 namespace svoxb {
 
 constexpr int kCursorStride = 32;
+constexpr int kMaxParts = 16;        // the scatter can run in up to 16 parts (bin ranges)
 constexpr int kScatterUnit = 2048;  // packets a block of the scatter kernel takes at a time
 
 struct ReplayBins {
@@ -42,12 +43,17 @@ struct ReplayBins {
     // is told by its position (see the scatter kernel)
     int64_t capacity;
     int4* packet;   // [capacity * 2]
-    int64_t* work;  // scatter work counter, zero at start
+    int64_t* work;  // [kMaxParts] scatter work counters, one per part of the bin range
     const float4* rays;  // [3 per ray] {g0,g1,g2,out0} {out1,out2,v0,v1} {v2,-,-,-}
 };
 
+// First bin of part p when n_bins bins are cut into n_parts ranges.
+__host__ __device__ inline int replay_part_first_bin(int p, int n_parts, int n_bins) {
+    return (int)(((int64_t)p * n_bins) / n_parts);
+}
+
 // One block: exclusive prefix of the forward's histogram.
-__global__ void replay_prefix_kernel(const int32_t* __restrict__ log, ReplayBins b) {
+__global__ void replay_prefix_kernel(const int32_t* __restrict__ log, ReplayBins b, int n_parts) {
     __shared__ int s[kMaxBins];
     int n_bins = log[3];
     if (n_bins < 0) n_bins = 0;
@@ -56,7 +62,7 @@ __global__ void replay_prefix_kernel(const int32_t* __restrict__ log, ReplayBins
         s[i] = i < n_bins ? log[kLogHeads + i] : 0;
         b.cursor[i * kCursorStride] = 0;
     }
-    if (threadIdx.x == 0) *b.work = 0;
+
     __syncthreads();
     if (threadIdx.x == 0) {
         int64_t run = 0;
@@ -65,6 +71,9 @@ __global__ void replay_prefix_kernel(const int32_t* __restrict__ log, ReplayBins
             run += s[i] > 0 ? s[i] : 0;
         }
         b.offset[kMaxBins] = (int)(run < b.capacity ? run : b.capacity);
+        // part p of the scatter covers bins [first_bin(p), first_bin(p + 1))
+        for (int p = 0; p < n_parts && p < kMaxParts; ++p)
+            b.work[p] = b.offset[replay_part_first_bin(p, n_parts, n_bins)];
     }
 }
 
@@ -188,7 +197,8 @@ struct alignas(16) ScatterSmem {
 template <int BD, int BLOCK>
 __global__ void __launch_bounds__(BLOCK)
 replay_scatter_kernel(int64_t n_slots, svoxb_render_options opt, float* __restrict__ grad_data,
-                      const int32_t* __restrict__ log, ReplayBins b, int flags) {
+                      const int32_t* __restrict__ log, ReplayBins b, int flags, int part,
+                      int n_parts) {
     constexpr int K = 3 * BD + 1;
     using Shape = CoopShape<K>;
     using SM = ScatterSmem<K>;
@@ -196,7 +206,10 @@ replay_scatter_kernel(int64_t n_slots, svoxb_render_options opt, float* __restri
     const int lane = threadIdx.x & 31;
     SM& sm = *reinterpret_cast<SM*>(s_raw + (size_t)(threadIdx.x >> 5) * sizeof(SM));
     const int sub = lane / Shape::GROUP, wj = lane % Shape::GROUP;
-    const int64_t total = b.offset[kMaxBins];
+    int n_bins = log[3];
+    if (n_bins > kMaxBins) n_bins = kMaxBins;
+    // packets of this part: those of its bin range
+    const int64_t total = b.offset[replay_part_first_bin(part + 1, n_parts, n_bins)];
     const int shift = log[2];
     const uint64_t pol_keep = l2_policy_keep(), pol_stream = l2_policy_stream();
     // Blocks take units of kScatterUnit packets in bin order from one counter, so the
@@ -208,7 +221,7 @@ replay_scatter_kernel(int64_t n_slots, svoxb_render_options opt, float* __restri
     for (;;) {
     __syncthreads();
     if (threadIdx.x == 0)
-        s_unit = (int64_t)atomicAdd(reinterpret_cast<unsigned long long*>(b.work),
+        s_unit = (int64_t)atomicAdd(reinterpret_cast<unsigned long long*>(b.work + part),
                                     (unsigned long long)kScatterUnit);
     __syncthreads();
     const int64_t unit = s_unit;

@@ -8,6 +8,7 @@
 #include "render_coop.cuh"
 #include "render_queue.cuh"
 #include "render_replay.cuh"
+#include <new>
 
 namespace svoxb {
 
@@ -192,22 +193,32 @@ static int launch_queue_block(const RenderCall& c, const Source& src, const Tree
     return SVOXB_OK;
 }
 
-// Replay backward (render_replay.cuh): prefix, bin, scatter.  `chunks` is the
-// number of log chunks the forward used; the packet buffer is sized from it.
-// SVOXB_ERR_TOO_LARGE when the packet buffer cannot be had (the caller then
-// marches instead).
-template <int BD, class Source>
-static int launch_replay(const RenderCall& c, const Source& src, int64_t chunks) {
-    constexpr int K = 3 * BD + 1;
+// Replay backward (render_replay.cuh): prefix, pack, bin, then the scatter in one
+// or several parts (bin ranges).  A ReplayJob holds the scratch between the calls.
+struct ReplayJob {
+    ReplayBins bins{};
+    int32_t* base = nullptr;     // pool allocation
+    const int32_t* log = nullptr;
+    svoxb_render_options opt{};
+    int64_t n_slots = 0, n_rays = 0, chunks = 0;
+    int K = 0, basis_dim = 0, n_parts = 1, shift = 0, n_bins = 1;
+};
+
+// Prefix + pack + bin.  SVOXB_ERR_TOO_LARGE when the packet buffer cannot be had
+// (the caller then marches instead).
+template <class Source>
+static int replay_begin(const RenderCall& c, const Source& src, int64_t chunks, int n_parts,
+                        ReplayJob* job) {
     if (chunks > c.log_capacity) chunks = c.log_capacity;
-    if (chunks < 1) return SVOXB_OK;
-    const int64_t packets = chunks * 32;
+    if (n_parts < 1 || n_parts > kMaxParts) return SVOXB_ERR_OPTION;
+    const int64_t packets = (chunks > 0 ? chunks : 1) * 32;
     if (packets >= (1LL << 30)) return SVOXB_ERR_TOO_LARGE;
 
     int st = keep_pool_cached();
     if (st) return st;
-    // cursors | offsets | work counter | packed rays | packets
-    const size_t head_words = (size_t)kMaxBins * kCursorStride + kMaxBins + 8;  // 32-byte multiple
+    // cursors | offsets | work counters | packed rays | packets
+    const size_t head_words =
+        (size_t)kMaxBins * kCursorStride + kMaxBins + 8 + 2 * kMaxParts;  // 32-byte multiple
     const size_t ray_words = (size_t)c.Q * 12;
     const size_t pad = (8 - (head_words + ray_words) % 8) % 8;
     int32_t* base = nullptr;
@@ -217,7 +228,7 @@ static int launch_replay(const RenderCall& c, const Source& src, int64_t chunks)
         (void)cudaGetLastError();
         return SVOXB_ERR_TOO_LARGE;
     }
-    ReplayBins b{};
+    ReplayBins& b = job->bins;
     b.cursor = base;
     b.offset = base + (size_t)kMaxBins * kCursorStride;
     b.work = reinterpret_cast<int64_t*>(b.offset + kMaxBins + 2);  // 8-byte aligned
@@ -225,35 +236,87 @@ static int launch_replay(const RenderCall& c, const Source& src, int64_t chunks)
     b.rays = rays;
     b.capacity = packets;
     b.packet = reinterpret_cast<int4*>(base + head_words + ray_words + pad);
+    job->base = base;
+    job->log = c.log;
+    job->opt = c.opt;
+    job->n_slots = c.tree->M * 8;
+    job->n_rays = c.Q;
+    job->chunks = chunks;
+    job->K = c.tree->K;
+    job->basis_dim = c.opt.basis_dim;
+    job->n_parts = n_parts;
+    job->shift = replay_bin_shift(c.tree->M, c.tree->K);
+    job->n_bins = (int)(((job->n_slots - 1) >> job->shift) + 1);
 
-    auto finish = [&](int status) {
-        cudaFreeAsync(base, c.stream);
-        return status;
-    };
-    cudaError_t e = cudaSuccess;
-    replay_prefix_kernel<<<1, 256, 0, c.stream>>>(c.log, b);
-    replay_pack_rays_kernel<<<(unsigned)((c.Q + 255) / 256), 256, 0, c.stream>>>(
-        tree_args(c.tree), src, c.opt, c.grad_out, c.fwd_out, c.Q, rays);
-
-    unsigned grid = 1;
-    auto run_bin = [&](auto k, int block) {
-        int s2 = persistent_grid(k, block, 0, chunks, &grid);
-        if (s2) return s2;
-        k<<<grid, block, 0, c.stream>>>(c.opt, c.log, chunks, c.Q, b);
-        return (int)SVOXB_OK;
-    };
-    st = run_bin(replay_bin_kernel<256, 2, 6>, 256);
-    if (st) return finish(st);
-    {
-        constexpr int BLOCK = 512;
-        const size_t smem = (size_t)(BLOCK / 32) * sizeof(ScatterSmem<K>);
-        auto k = replay_scatter_kernel<BD, BLOCK>;
-        if ((st = persistent_grid(k, BLOCK, smem, chunks, &grid))) return finish(st);
-        k<<<grid, BLOCK, smem, c.stream>>>(c.tree->M * 8, c.opt, c.grad_data, c.log, b,
-                                          g_tuning.replay_flags);
+    replay_prefix_kernel<<<1, 256, 0, c.stream>>>(c.log, b, n_parts);
+    if (chunks > 0) {
+        replay_pack_rays_kernel<<<(unsigned)((c.Q + 255) / 256), 256, 0, c.stream>>>(
+            tree_args(c.tree), src, c.opt, c.grad_out, c.fwd_out, c.Q, rays);
+        unsigned grid = 1;
+        auto k = replay_bin_kernel<256, 2, 6>;
+        st = persistent_grid(k, 256, 0, chunks, &grid);
+        if (st == SVOXB_OK) k<<<grid, 256, 0, c.stream>>>(c.opt, c.log, chunks, c.Q, b);
     }
-    e = cudaGetLastError();
-    return finish(e != cudaSuccess ? set_cuda_error(e) : SVOXB_OK);
+    const cudaError_t e = cudaGetLastError();
+    if (st == SVOXB_OK && e != cudaSuccess) st = set_cuda_error(e);
+    if (st != SVOXB_OK) {
+        cudaFreeAsync(base, c.stream);
+        job->base = nullptr;
+    }
+    return st;
+}
+
+// Scatter of one part.  With `reserve_sms` > 0 that many SMs are left without a block
+// (for a collective that runs beside the scatter); small records then use one 1024-thread
+// block per SM, so that the SMs left out are really empty.
+template <int BD, int BLOCK>
+static int replay_scatter_block(const ReplayJob& job, int part, float* grad, int reserve_sms,
+                                cudaStream_t stream) {
+    constexpr int K = 3 * BD + 1;
+    const size_t smem = (size_t)(BLOCK / 32) * sizeof(ScatterSmem<K>);
+    auto k = replay_scatter_kernel<BD, BLOCK>;
+    unsigned grid = 1;
+    int st = persistent_grid(k, BLOCK, smem, job.chunks, &grid);
+    if (st) return st;
+    if (reserve_sms > 0) {
+        const int sms = sm_count();
+        const int64_t per_sm = ((int64_t)grid + sms - 1) / sms;
+        const int64_t most = ((int64_t)sms - reserve_sms) * per_sm;
+        if ((int64_t)grid > most) grid = (unsigned)(most > 1 ? most : 1);
+    }
+    k<<<grid, BLOCK, smem, stream>>>(job.n_slots, job.opt, grad, job.log, job.bins,
+                                    g_tuning.replay_flags, part, job.n_parts);
+    const cudaError_t e = cudaGetLastError();
+    return e != cudaSuccess ? set_cuda_error(e) : SVOXB_OK;
+}
+
+template <int BD>
+static int replay_scatter_bd(const ReplayJob& job, int part, float* grad, int reserve_sms,
+                             cudaStream_t stream) {
+    if constexpr (BD <= 9) {
+        if (reserve_sms > 0)
+            return replay_scatter_block<BD, 1024>(job, part, grad, reserve_sms, stream);
+    }
+    return replay_scatter_block<BD, 512>(job, part, grad, reserve_sms, stream);
+}
+
+static int replay_scatter(const ReplayJob& job, int part, float* grad, int reserve_sms,
+                          cudaStream_t stream) {
+    if (part < 0 || part >= job.n_parts) return SVOXB_ERR_OPTION;
+    if (job.chunks < 1) return SVOXB_OK;
+    switch (job.basis_dim) {
+        case 1: return replay_scatter_bd<1>(job, part, grad, reserve_sms, stream);
+        case 4: return replay_scatter_bd<4>(job, part, grad, reserve_sms, stream);
+        case 9: return replay_scatter_bd<9>(job, part, grad, reserve_sms, stream);
+        case 16: return replay_scatter_bd<16>(job, part, grad, reserve_sms, stream);
+        case 25: return replay_scatter_bd<25>(job, part, grad, reserve_sms, stream);
+    }
+    return SVOXB_ERR_FORMAT;
+}
+
+static void replay_end(ReplayJob* job, cudaStream_t stream) {
+    if (job->base) cudaFreeAsync(job->base, stream);
+    job->base = nullptr;
 }
 
 // Per-call scratch of the queue kernels: the annotated child array followed by
@@ -600,13 +663,11 @@ static int replay_backward(const svoxb_tree* tree, const Source& src, int64_t Q,
     c.log = log;
     c.log_capacity = capacity_chunks;
     if (chunks_used <= 0 || chunks_used > capacity_chunks) chunks_used = capacity_chunks;
-    st = SVOXB_ERR_FORMAT;
-    switch (opt->basis_dim) {
-        case 1: st = launch_replay<1>(c, src, chunks_used); break;
-        case 4: st = launch_replay<4>(c, src, chunks_used); break;
-        case 9: st = launch_replay<9>(c, src, chunks_used); break;
-        case 16: st = launch_replay<16>(c, src, chunks_used); break;
-        case 25: st = launch_replay<25>(c, src, chunks_used); break;
+    ReplayJob job;
+    st = replay_begin(c, src, chunks_used, 1, &job);
+    if (st == SVOXB_OK) {
+        st = replay_scatter(job, 0, grad_data_out, 0, c.stream);
+        replay_end(&job, c.stream);
     }
     if (st == SVOXB_ERR_TOO_LARGE) {
         // no room for the packets: march instead (same result, the log is not used)
@@ -666,6 +727,93 @@ int svoxb_volume_render_image_backward_replay(const svoxb_tree* tree, const svox
     return replay_backward(tree, PixelRays{cam->c2w, cam->fx, cam->fy, cam->width, cam->height},
                            (int64_t)cam->width * cam->height, opt, grad_output, fwd_out, log,
                            capacity_chunks, chunks_used, grad_data_out, zero_first, stream);
+}
+
+}  // extern "C"
+
+template <class Source>
+static int replay_begin_checked(const svoxb_tree* tree, const Source& src, int64_t Q,
+                                const svoxb_render_options* opt, const float* grad_output,
+                                const float* fwd_out, int32_t* log, int64_t capacity_chunks,
+                                int64_t chunks_used, int n_parts, void* stream, void** job_out) {
+    if (!job_out) return SVOXB_ERR_NULL;
+    *job_out = nullptr;
+    int st = validate_tree(tree);
+    if (st) return st;
+    if ((st = validate_options(tree, *opt))) return st;
+    if (!log || (Q > 0 && (!grad_output || !fwd_out))) return SVOXB_ERR_NULL;
+    if ((st = log_eligible(tree, opt, nullptr))) return st;
+    RenderCall c{tree, *opt, Q};
+    c.backward = true;
+    c.grad_out = grad_output;
+    c.fwd_out = fwd_out;
+    c.stream = (cudaStream_t)stream;
+    c.log = log;
+    c.log_capacity = capacity_chunks;
+    if (chunks_used <= 0 || chunks_used > capacity_chunks) chunks_used = capacity_chunks;
+    if (Q == 0) chunks_used = 0;
+    ReplayJob* job = new (std::nothrow) ReplayJob;
+    if (!job) return SVOXB_ERR_TOO_LARGE;
+    st = replay_begin(c, src, chunks_used, n_parts, job);
+    if (st != SVOXB_OK) {
+        delete job;
+        return st;
+    }
+    *job_out = job;
+    return SVOXB_OK;
+}
+
+extern "C" {
+
+int svoxb_replay_begin(const svoxb_tree* tree, const svoxb_rays* rays,
+                       const svoxb_render_options* opt, const float* grad_output,
+                       const float* fwd_out, int32_t* log, int64_t capacity_chunks,
+                       int64_t chunks_used, int n_parts, void* stream, void** job) {
+    if (!tree || !rays || !opt) return SVOXB_ERR_NULL;
+    if (rays->Q > 0 && (!rays->origins || !rays->dirs || !rays->vdirs)) return SVOXB_ERR_NULL;
+    return replay_begin_checked(tree, RayBatch{rays->origins, rays->dirs, rays->vdirs}, rays->Q,
+                                opt, grad_output, fwd_out, log, capacity_chunks, chunks_used,
+                                n_parts, stream, job);
+}
+
+int svoxb_replay_image_begin(const svoxb_tree* tree, const svoxb_camera* cam,
+                             const svoxb_render_options* opt, const float* grad_output,
+                             const float* fwd_out, int32_t* log, int64_t capacity_chunks,
+                             int64_t chunks_used, int n_parts, void* stream, void** job) {
+    if (!tree || !cam || !opt || !cam->c2w) return SVOXB_ERR_NULL;
+    if (cam->width < 0 || cam->height < 0) return SVOXB_ERR_SHAPE;
+    return replay_begin_checked(tree,
+                                PixelRays{cam->c2w, cam->fx, cam->fy, cam->width, cam->height},
+                                (int64_t)cam->width * cam->height, opt, grad_output, fwd_out, log,
+                                capacity_chunks, chunks_used, n_parts, stream, job);
+}
+
+int svoxb_replay_part_range(const void* job, int part, int64_t* slot_begin, int64_t* slot_end) {
+    if (!job || !slot_begin || !slot_end) return SVOXB_ERR_NULL;
+    const ReplayJob* j = static_cast<const ReplayJob*>(job);
+    if (part < 0 || part >= j->n_parts) return SVOXB_ERR_OPTION;
+    const int64_t lo = (int64_t)replay_part_first_bin(part, j->n_parts, j->n_bins) << j->shift;
+    int64_t hi = (int64_t)replay_part_first_bin(part + 1, j->n_parts, j->n_bins) << j->shift;
+    if (part == j->n_parts - 1 || hi > j->n_slots) hi = j->n_slots;
+    *slot_begin = lo < j->n_slots ? lo : j->n_slots;
+    *slot_end = hi;
+    return SVOXB_OK;
+}
+
+int svoxb_replay_scatter(const void* job, int part, float* grad_data_out, int reserve_sms,
+                         void* stream) {
+    if (!job || !grad_data_out) return SVOXB_ERR_NULL;
+    const ReplayJob* j = static_cast<const ReplayJob*>(job);
+    if (j->K % 4 == 0 && (uintptr_t)grad_data_out % 16 != 0) return SVOXB_ERR_FORMAT;
+    return replay_scatter(*j, part, grad_data_out, reserve_sms, (cudaStream_t)stream);
+}
+
+int svoxb_replay_end(void* job, void* stream) {
+    if (!job) return SVOXB_ERR_NULL;
+    ReplayJob* j = static_cast<ReplayJob*>(job);
+    replay_end(j, (cudaStream_t)stream);
+    delete j;
+    return SVOXB_OK;
 }
 
 int svoxb_item_log_used(const int32_t* log, int64_t* chunks_used, void* stream) {

@@ -12,7 +12,7 @@ import torch.distributed as dist
 from .render import Rays
 
 __all__ = ["shard_bounds", "shard_rays", "shard_rows", "allreduce_grad", "broadcast_tree",
-           "gather_rows"]
+           "gather_rows", "overlap_grad_allreduce"]
 
 
 def _rank_world(rank, world):
@@ -39,12 +39,66 @@ def shard_rays(rays, rank=None, world=None):
     return Rays(*[shard_rows(t, rank, world) for t in rays])
 
 
+class _Overlap:
+    """State of the overlapped gradient all-reduce (see ``overlap_grad_allreduce``)."""
+    group = None
+    works = []
+    reduced = False     # the gradient of the last backward left the renderer already summed
+
+    @classmethod
+    def on_part(cls, rows):
+        cls.works.append(dist.all_reduce(rows, op=dist.ReduceOp.SUM, group=cls.group,
+                                         async_op=True))
+
+    @classmethod
+    def agree(cls, ok):
+        # every rank must take the same route: the parts run one collective each
+        flag = torch.tensor([1 if ok else 0], dtype=torch.int32,
+                            device=torch.device("cuda", torch.cuda.current_device()))
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=cls.group)
+        return bool(flag.item())
+
+    @classmethod
+    def on_done(cls):
+        for w in cls.works:
+            w.wait()            # the current stream waits for the collective's stream
+        cls.works = []
+        cls.reduced = True
+
+
+def overlap_grad_allreduce(n_parts=4, group=None, reserve_sms=16):
+    """Overlap the all-reduce of ``data.grad`` with its computation.
+
+    The replay backward of the renderer produces the gradient leaf range by leaf range;
+    with this switched on, the rows of a finished range are all-reduced (asynchronously, on
+    the backend's stream) while the next range is computed, and ``reserve_sms`` SMs are left
+    to the collective's kernel.  ``allreduce_grad`` then finds the gradient already summed
+    and does nothing.  Steps whose backward cannot take that route on some rank (log overflow, options
+    the replay does not cover) still get the plain all-reduce; the ranks agree on the route
+    with a one-word all-reduce per step.  ``n_parts=0`` switches it off.
+    Every rank must make the same call.
+    """
+    from . import render
+    if not n_parts or not (dist.is_available() and dist.is_initialized()) \
+            or dist.get_world_size(group) == 1:
+        render.GRAD_PARTS = None
+        return
+    _Overlap.group = group
+    _Overlap.works = []
+    _Overlap.reduced = False
+    render.GRAD_PARTS = (int(n_parts), _Overlap.on_part, _Overlap.on_done, _Overlap.agree,
+                         int(reserve_sms))
+
+
 def allreduce_grad(tree, group=None, async_op=False):
     """Sum ``tree.data.grad`` over all ranks (the one collective of a training step).
 
     A rank whose rays all missed the tree has no gradient yet: it contributes zeros.
     """
     if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return None
+    if _Overlap.reduced:        # summed range by range inside the backward pass
+        _Overlap.reduced = False
         return None
     if tree.data.grad is None:
         tree.data.grad = torch.zeros_like(tree.data)

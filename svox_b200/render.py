@@ -23,6 +23,24 @@ __all__ = ["VolumeRenderer", "NDCConfig", "Rays", "_VolumeRenderFunction",
 # memory: about 40 bytes per contributing sample until the backward has run).
 USE_ITEM_LOG = True
 
+# Set by ``svox_b200.distributed.overlap_grad_allreduce``: (n_parts, on_part, on_done,
+# agree, reserve_sms).  The replay backward then produces the gradient in n_parts consecutive
+# leaf ranges and hands each finished range to on_part (which starts its all-reduce).
+GRAD_PARTS = None
+
+
+def _replay(tree, src, opt, grad_out, fwd, log, image):
+    """Replay backward, in parts when a gradient hook is installed; None -> caller marches."""
+    if GRAD_PARTS is not None:
+        n_parts, on_part, on_done, agree, reserve = GRAD_PARTS
+        grad = _C.volume_render_backward_replay_parts(tree, src, opt, grad_out, fwd, log, n_parts,
+                                                      on_part, agree=agree, reserve_sms=reserve,
+                                                      image=image)
+        if grad is not None:
+            on_done()
+        return grad
+    return _C.volume_render_backward_replay(tree, src, opt, grad_out, fwd, log, image=image)
+
 NDCConfig = namedtuple("NDCConfig", ["width", "height", "focal"])
 Rays = namedtuple("Rays", ["origins", "dirs", "viewdirs"])
 
@@ -77,8 +95,7 @@ class _VolumeRenderFunction(autograd.Function):
             fwd = ctx.fwd[0]
         grad_out = grad_out.contiguous()
         if fwd is not None and ctx.log is not None:
-            grad = _C.volume_render_backward_replay(ctx.tree, ctx.rays, ctx.opt, grad_out, fwd,
-                                                    ctx.log)
+            grad = _replay(ctx.tree, ctx.rays, ctx.opt, grad_out, fwd, ctx.log, False)
             ctx.log = None
             if grad is not None:
                 return grad, None, None, None
@@ -109,8 +126,7 @@ class _VolumeRenderImageFunction(autograd.Function):
             fwd = ctx.fwd[0]
         grad_out = grad_out.contiguous()
         if fwd is not None and ctx.log is not None:
-            grad = _C.volume_render_backward_replay(ctx.tree, ctx.cam, ctx.opt, grad_out, fwd,
-                                                    ctx.log, image=True)
+            grad = _replay(ctx.tree, ctx.cam, ctx.opt, grad_out, fwd, ctx.log, True)
             ctx.log = None
             if grad is not None:
                 return grad, None, None, None

@@ -295,3 +295,20 @@ def test_full_size_properties_config2_slice(cuda_device):
     lut[corner[:, 0], corner[:, 1], corner[:, 2]] = packed
     assert torch.equal(lut[cell[:, 0], cell[:, 1], cell[:, 2]], ids)
     csrc.check_device_status()
+
+
+def test_multi_gpu_overlapped_allreduce_matches_plain(cuda_device):
+    # Two ranks, NVLS off and a short collective timeout: the gradient summed leaf range
+    # by leaf range inside the backward equals the one summed by a single all-reduce.
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import subprocess
+    import sys
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    worker = os.path.join(os.path.dirname(__file__), "dist_overlap_worker.py")
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
+                          "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                          "--master-port", "29533", worker],
+                         capture_output=True, text=True, timeout=600, env=env)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    assert "ok 1" in res.stdout
