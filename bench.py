@@ -49,7 +49,7 @@ def parse():
     p.add_argument("--extra-levels", type=int, default=3)
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
-    p.add_argument("--overlap-parts", type=int, default=4,
+    p.add_argument("--overlap-parts", type=int, default=8,
                    help="N > 1: leaf ranges whose all-reduce overlaps the backward (0 = one "
                         "all-reduce after the backward)")
     return p.parse_args()

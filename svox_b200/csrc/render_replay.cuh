@@ -19,7 +19,7 @@
 //            leaf slots whose gradient spans a few MB) into bin offsets;
 //   bin      streams the log; lane i turns item i into a 32-byte packet (slot,
 //            the three colour factors, the density gradient, the ray's view
-//            direction) and appends it to its bin.  A block reserves room for the packets of 16 chunks at a
+//            direction) and appends it to its bin.  A block reserves room for the packets of 8 chunks at a
 //            time, so the bin cursors see one atomic per bin and block step;
 //   scatter  walks the packets bin after bin: all SMs work on the same few bins
 //            at a time, so the gradient lines they reduce into stay in L2 and

@@ -253,9 +253,12 @@ static int replay_begin(const RenderCall& c, const Source& src, int64_t chunks, 
         replay_pack_rays_kernel<<<(unsigned)((c.Q + 255) / 256), 256, 0, c.stream>>>(
             tree_args(c.tree), src, c.opt, c.grad_out, c.fwd_out, c.Q, rays);
         unsigned grid = 1;
-        auto k = replay_bin_kernel<256, 2, 6>;
-        st = persistent_grid(k, 256, 0, chunks, &grid);
-        if (st == SVOXB_OK) k<<<grid, 256, 0, c.stream>>>(c.opt, c.log, chunks, c.Q, b);
+        auto run_bin = [&](auto k, int block) {
+            int s2 = persistent_grid(k, block, 0, chunks, &grid);
+            if (s2 == SVOXB_OK) k<<<grid, block, 0, c.stream>>>(c.opt, c.log, chunks, c.Q, b);
+            return s2;
+        };
+        st = run_bin(replay_bin_kernel<128, 2, 12>, 128);
     }
     const cudaError_t e = cudaGetLastError();
     if (st == SVOXB_OK && e != cudaSuccess) st = set_cuda_error(e);

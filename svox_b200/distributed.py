@@ -66,7 +66,7 @@ class _Overlap:
         cls.reduced = True
 
 
-def overlap_grad_allreduce(n_parts=4, group=None, reserve_sms=16):
+def overlap_grad_allreduce(n_parts=8, group=None, reserve_sms=16):
     """Overlap the all-reduce of ``data.grad`` with its computation.
 
     The replay backward of the renderer produces the gradient leaf range by leaf range;
