@@ -51,6 +51,13 @@ typedef struct {
     int64_t M;  /* number of nodes (capacity)  */
     int32_t N;  /* branching factor per axis   */
     int32_t K;  /* floats per leaf record      */
+    /* Weight accumulation of the forward render (TreeSpec::_weight_accum,
+     * svox/csrc/rt_kernel.cu:298-304): optional (M,N,N,N) float buffer; every
+     * contributing sample adds its weight to the entry of its leaf, or raises it
+     * to the weight if weight_accum_max is set.  Null: off. */
+    float* weight_accum;
+    int32_t weight_accum_max;
+    int32_t reserved_;
 } svoxb_tree;
 
 /* Replaces RaysSpec (svox/csrc/include/data_spec.hpp:51-64): three (Q, 3)

@@ -157,6 +157,25 @@ def volume_render(tree, origins, dirs, vdirs, opt, want_counts=False):
     return (out, vis, con) if want_counts else out
 
 
+class weight_accumulation:
+    """``with weight_accumulation(tree, "sum") as acc:`` -- forward renders inside the block
+    accumulate every contributing sample's weight per leaf into ``acc`` (float64, shape of
+    ``child``), as the reference does with ``tree.accumulate_weights``
+    (svox/svox.py:810-832, svox/csrc/rt_kernel.cu:298-304)."""
+
+    def __init__(self, tree, op="sum"):
+        assert op in ("sum", "max")
+        self.buf = np.zeros(tree.child.shape, np.float64)
+        self.op = op
+
+    def __enter__(self):
+        lib().orc_set_weight_accum(_ptr(self.buf), C.c_int(1 if self.op == "max" else 0))
+        return self.buf
+
+    def __exit__(self, *exc):
+        lib().orc_set_weight_accum(None, C.c_int(0))
+
+
 def trace_log(tree, origin, dir, vdir, opt, cap=4096):
     o, d, v = _f32(origin), _f32(dir), _f32(vdir)
     slots = np.zeros(cap, np.int64)

@@ -321,6 +321,29 @@ static inline int ray_setup(const OrcTree* tr, const float* origin, float* dir, 
 
 /* svox/csrc/rt_kernel.cu:222-321 (trace_ray).  origin in tree space, dir is
  * modified in place as in the reference. */
+/* Weight accumulation of the forward render (svox/csrc/rt_kernel.cu:298-304,
+ * TreeSpec::_weight_accum): when set, every contributing sample adds its
+ * weight to (or, with `max`, raises) the entry of its leaf.  The sum is kept
+ * in double so that it does not depend on the order of the rays. */
+static double* g_weight_accum = NULL;
+static int g_weight_accum_max = 0;
+
+void orc_set_weight_accum(double* buf, int use_max) {
+    g_weight_accum = buf;
+    g_weight_accum_max = use_max;
+}
+
+static inline void accumulate_weight(int64_t slot, float weight) {
+    if (!g_weight_accum) return;
+    if (g_weight_accum_max) {
+#pragma omp critical(orc_weight_max)
+        if ((double)weight > g_weight_accum[slot]) g_weight_accum[slot] = (double)weight;
+    } else {
+#pragma omp atomic
+        g_weight_accum[slot] += (double)weight;
+    }
+}
+
 static int trace_ray(const OrcTree* tr, const float* origin, float* dir, const float* vdir,
                      const OrcOptions* opt, float* out, OrcRayStats* st) {
     const int out_dim = out_dim_of(tr, opt);
@@ -379,6 +402,7 @@ static int trace_ray(const OrcTree* tr, const float* origin, float* dir, const f
                 }
             }
             light *= att;
+            accumulate_weight(slot, weight);
             if (light <= opt->stop_thresh) {
                 const float scale = (float)(1.0 / (1.0 - (double)light));
                 for (int j = 0; j < out_dim; ++j) out[j] *= scale;

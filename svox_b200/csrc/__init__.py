@@ -24,7 +24,9 @@ ERR_TOO_LARGE = 8   # svoxb status: a size limit or the scratch allocation
 
 class _CTree(C.Structure):
     _fields_ = [("data", C.c_void_p), ("child", C.c_void_p), ("offset", C.c_void_p),
-                ("scaling", C.c_void_p), ("M", C.c_int64), ("N", C.c_int32), ("K", C.c_int32)]
+                ("scaling", C.c_void_p), ("M", C.c_int64), ("N", C.c_int32), ("K", C.c_int32),
+                ("weight_accum", C.c_void_p), ("weight_accum_max", C.c_int32),
+                ("reserved_", C.c_int32)]
 
 
 class _CRays(C.Structure):
@@ -179,10 +181,16 @@ def _pack_tree(tree):
     for n in ("child", "offset", "scaling"):
         if getattr(tree, n).device != dev:
             raise RuntimeError(f"{n} must be on the same device as data")
-    if tree._weight_accum is not None and tree._weight_accum.numel():
-        raise RuntimeError("weight accumulation is not implemented by svox_b200")
+    wa = tree._weight_accum
+    wa_ptr = 0
+    if wa is not None and wa.numel():
+        _check_input(wa, "_weight_accum")
+        if tuple(wa.shape) != tuple(tree.child.shape) or wa.device != dev:
+            raise RuntimeError("_weight_accum must have the shape and device of child")
+        wa_ptr = wa.data_ptr()
     return _CTree(d.data_ptr(), tree.child.data_ptr(), tree.offset.data_ptr(),
-                  tree.scaling.data_ptr(), d.shape[0], d.shape[1], d.shape[4])
+                  tree.scaling.data_ptr(), d.shape[0], d.shape[1], d.shape[4], wa_ptr,
+                  1 if tree._weight_accum_max else 0, 0)
 
 
 def _pack_rays(rays, dev):

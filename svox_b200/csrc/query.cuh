@@ -27,10 +27,35 @@ struct TreeArgs {
     int64_t M;
     int32_t N;
     int32_t K;
+    float* weight_accum;      // forward render only (null: off)
+    int32_t weight_accum_max;
 };
 
 static inline TreeArgs tree_args(const svoxb_tree* t) {
-    return TreeArgs{t->data, t->child, t->offset, t->scaling, t->M, t->N, t->K};
+    return TreeArgs{t->data, t->child, t->offset, t->scaling, t->M, t->N, t->K,
+                    t->weight_accum, t->weight_accum_max};
+}
+
+// One sample's weight into the accumulator of its leaf (svox/csrc/rt_kernel.cu:298-304).
+// Weights are >= 0 unless the density is negative; for those the maximum goes through a
+// compare-and-swap like the reference's (svox/csrc/include/common.cuh:152-161).
+__device__ __forceinline__ void accumulate_weight(const TreeArgs& tr, int64_t slot, float w) {
+    float* p = tr.weight_accum + slot;
+    if (!tr.weight_accum_max) {
+        atomicAdd(p, w);
+    } else if (w >= 0.f) {
+        // non-negative floats order like their bit patterns; the buffer starts at +0
+        if (__float_as_int(*reinterpret_cast<volatile float*>(p)) < __float_as_int(w))
+            atomicMax(reinterpret_cast<int*>(p), __float_as_int(w));
+    } else {
+        unsigned* u = reinterpret_cast<unsigned*>(p);
+        unsigned old = *u, assumed;
+        int guard = 0;
+        do {
+            assumed = old;
+            old = atomicCAS(u, assumed, __float_as_uint(fmaxf(w, __uint_as_float(assumed))));
+        } while (old != assumed && ++guard < 1024);
+    }
 }
 
 __device__ __forceinline__ int64_t locate_point(const TreeArgs& tr, const TopTable& top,

@@ -356,6 +356,7 @@ render_fwd_sh(TreeArgs tr, Source src, svoxb_render_options opt, TopTable topg, 
                     if (sigma > opt.sigma_thresh) {
                         const float att = expf(-s.delta_t * r.delta_scale * sigma);
                         const float weight = light * (1.f - att);
+                        if (tr.weight_accum != nullptr) accumulate_weight(tr, s.leaf.slot, weight);
                         float v[K];
                         load_record<K, VEC>(rec, v);
                         float c[3];
@@ -640,6 +641,7 @@ render_fwd_generic(TreeArgs tr, Source src, svoxb_render_options opt, TopTable t
                 if (sigma > opt.sigma_thresh) {
                     const float att = expf(-s.delta_t * r.delta_scale * sigma);
                     const float weight = light * (1.f - att);
+                    if (tr.weight_accum != nullptr) accumulate_weight(tr, s.leaf.slot, weight);
                     for (int ch = 0; ch < out_dim; ++ch) {
                         float tmp;
                         if (sh) {

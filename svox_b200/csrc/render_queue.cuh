@@ -432,6 +432,7 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
             }
             if (!BWD) {
                 row[0] = col[0]; row[1] = col[1]; row[2] = col[2];
+                if (tr.weight_accum != nullptr) accumulate_weight(tr, q.slot[lane], q.w[lane]);
             } else {
                 float total_color = 0.f;
 #pragma unroll

@@ -437,7 +437,8 @@ static int dispatch_layout(const RenderCall& c, const Source& src, const TopTabl
     const bool vec = aligned && (t->K % 4 == 0);
     // Warp-cooperative kernels: octrees whose records allow the chosen word
     // size (any K with 32-bit words; 16-byte aligned buffers for K % 4 == 0).
-    if (g_tuning.render_algo == 0 && t->N == 2 && (aligned || t->K % 4 != 0) &&
+    if (g_tuning.render_algo == 0 && t->weight_accum == nullptr && t->N == 2 &&
+        (aligned || t->K % 4 != 0) &&
         t->M * 8 < 0xffffffffLL) {
         switch (c.opt.basis_dim) {
             case 1: return launch_coop<1, BLOCK>(c, src, top, in_smem, smem);

@@ -27,7 +27,7 @@ from . import csrc as _C
 from .formats import DataFormat, LocalIndex
 from .view import N3TreeView
 
-__all__ = ["N3Tree", "_QueryVerticalFunction"]
+__all__ = ["N3Tree", "WeightAccumulator", "_QueryVerticalFunction"]
 
 
 class _QueryVerticalFunction(autograd.Function):
@@ -243,6 +243,17 @@ class N3Tree(nn.Module):
 
     # ------------------------------------------------------------------
     # Persistence (svox/svox.py:835-865, 899-938): same npz keys, data as fp16
+    def accumulate_weights(self, op: str = "sum"):
+        """Begin weight accumulation (svox/svox.py:810-832): forward renders inside the
+        ``with`` block add (``op="sum"``) every contributing sample's weight to its leaf,
+        or keep the largest (``op="max"``).
+
+            with tree.accumulate_weights() as accum:
+                renderer(rays)
+            w = accum()          # (n_leaves,), in the order of ``tree.values``
+        """
+        return WeightAccumulator(self, op)
+
     def save(self, path, shrink=True, compress=True):
         if shrink:
             self.shrink_to_fit()
@@ -436,3 +447,32 @@ def _install_view_redirects():
 
 
 _install_view_redirects()
+
+
+class WeightAccumulator:
+    """Context manager behind ``N3Tree.accumulate_weights`` (svox/svox.py:1136-1161)."""
+
+    def __init__(self, tree, op):
+        assert op in ["sum", "max"], "Unsupported accumulation"
+        self.tree = tree
+        self.op = op
+
+    def __enter__(self):
+        self.tree._lock_tree_structure = True
+        self.tree._weight_accum = torch.zeros(self.tree.child.shape, dtype=self.tree.data.dtype,
+                                              device=self.tree.data.device)
+        self.tree._weight_accum_op = self.op
+        self.weight_accum = self.tree._weight_accum
+        return self
+
+    def __exit__(self, type, value, traceback):
+        self.tree._weight_accum = None
+        self.tree._weight_accum_op = None
+        self.tree._lock_tree_structure = False
+
+    @property
+    def value(self):
+        return self.weight_accum
+
+    def __call__(self):
+        return self.tree[:].aux(self.weight_accum)

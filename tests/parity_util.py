@@ -82,6 +82,17 @@ def _run_product(case, device, backward, single_march):
 
 
 # ---------------------------------------------------------------------------
+def _oracle_options(case):
+    from oracle import oracle as orc
+    po = options_of(case)
+    return orc.options(step_size=po.step_size, background_brightness=po.background_brightness,
+                       format=po.format, basis_dim=po.basis_dim, ndc_width=po.ndc_width,
+                       ndc_height=po.ndc_height, ndc_focal=po.ndc_focal, min_comp=po.min_comp,
+                       max_comp=po.max_comp, sigma_thresh=po.sigma_thresh,
+                       stop_thresh=po.stop_thresh, density_softplus=po.density_softplus,
+                       rgb_padding=po.rgb_padding)
+
+
 def run_oracle(case, backward=True, want_counts=False):
     """Also returns ``grad_abs``: per element the sum of |contributions|, the scale
     against which a sum formed by float atomics in any order may differ."""
@@ -98,13 +109,7 @@ def run_oracle(case, backward=True, want_counts=False):
             res["grad_abs"] = orc.query_vertical_backward(ot, pts, np.abs(g))
         return res
     ot = orc.Tree.from_n3tree(tree, world=True)
-    po = options_of(case)
-    opt = orc.options(step_size=po.step_size, background_brightness=po.background_brightness,
-                      format=po.format, basis_dim=po.basis_dim, ndc_width=po.ndc_width,
-                      ndc_height=po.ndc_height, ndc_focal=po.ndc_focal, min_comp=po.min_comp,
-                      max_comp=po.max_comp, sigma_thresh=po.sigma_thresh,
-                      stop_thresh=po.stop_thresh, density_softplus=po.density_softplus,
-                      rgb_padding=po.rgb_padding)
+    opt = _oracle_options(case)
     if case["kind"] == "rays":
         o, d, v = [t.numpy() for t in case["rays"]]
         r = orc.volume_render(ot, o, d, v, opt, want_counts=want_counts)
@@ -221,3 +226,39 @@ def grad_error(grad, ref_grad):
     big = np.abs(r) > 1e-3 * scale
     rel = float((err[big] / np.abs(r[big])).max()) if big.any() else 0.0
     return float(err.max() / scale), rel
+
+
+def run_weight_accumulation(case, op, device=None):
+    """Per-leaf weight accumulator of one forward render: product (``device`` given) or
+    oracle (``device`` None), as a flat float64 array over (M, N, N, N)."""
+    tree = case["tree"]
+    if device is None:
+        from oracle import oracle as orc
+        ot = orc.Tree.from_n3tree(tree, world=True)
+        opt = _oracle_options(case)
+        with orc.weight_accumulation(ot, op) as acc:
+            if case["kind"] == "rays":
+                o, d, v = [t.numpy() for t in case["rays"]]
+                orc.volume_render(ot, o, d, v, opt)
+            else:
+                cam = case["camera"]
+                orc.volume_render_image(ot, cam["c2w"].numpy(), cam["fx"], cam["fy"],
+                                        cam["width"], cam["height"], opt)
+        return acc.reshape(-1).copy()
+    t = tree.to(device)
+    try:
+        r = _renderer(t, case)
+        with torch.no_grad(), t.accumulate_weights(op=op) as accum:
+            if case["kind"] == "rays":
+                r(svox_b200.Rays(*[x.to(device) for x in case["rays"]]), fast=case["fast"])
+            else:
+                cam = case["camera"]
+                r.render_persp(cam["c2w"].to(device), width=cam["width"], height=cam["height"],
+                               fx=cam["fx"], fy=cam["fy"], fast=case["fast"])
+            dense = accum.value.double().cpu().numpy().reshape(-1)
+            per_leaf = accum().double().cpu().numpy()
+        _C.check_device_status()
+        n = t.n_internal * t.N ** 3
+        return dense[:n], per_leaf
+    finally:
+        case["tree"].to("cpu")

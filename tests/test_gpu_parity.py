@@ -120,6 +120,25 @@ def test_bricks_and_bin_size_do_not_change_results(name, cuda_device):
         lib.svoxb_tune(5, 16)
 
 
+@pytest.mark.parametrize("name", ["c1_rays", "shell_sh9_rays", "shell_sh16_image", "opt_fast",
+                                  "rgba_rays", "n3_rays", "aniso_rays"])
+@pytest.mark.parametrize("op", ["sum", "max"])
+def test_weight_accumulation_matches_oracle(name, op, cuda_device):
+    # tree.accumulate_weights (svox/svox.py:810-832): per-leaf sum / maximum of the sample
+    # weights of a forward render; queue kernel, generic kernel (RGBA, N = 3) and image path.
+    case = CASES[name]()
+    want = P.run_weight_accumulation(case, op)
+    dense, per_leaf = P.run_weight_accumulation(case, op, cuda_device)
+    assert want.sum() > 0
+    tol = 1e-5 * (1.0 + np.abs(want)) if op == "sum" else 2e-6
+    assert np.all(np.abs(dense - want[:dense.size]) <= tol)
+    assert np.all(want[dense.size:] == 0)
+    # accum() lists the leaves in the order of tree.values
+    leaves = case["tree"]._all_leaves()
+    flat = case["tree"]._pack_index(leaves).numpy()
+    assert np.array_equal(per_leaf, dense[flat])
+
+
 def test_item_log_overflow_falls_back(cuda_device):
     # A log that is too small must not be replayed: the backward marches instead.
     case = CASES["shell_sh9_rays"]()

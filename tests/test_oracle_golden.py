@@ -129,3 +129,35 @@ def test_corrupt_tree_is_reported_not_followed():
     ot = orc.Tree(t.data.detach().numpy(), child)
     with pytest.raises(RuntimeError, match="corrupt"):
         orc.query_vertical(ot, np.array([[0.1, 0.1, 0.1]], np.float32))
+
+
+def test_weight_accumulation_matches_a_per_ray_recomputation():
+    # svox/csrc/rt_kernel.cu:298-304: every contributing sample adds light * (1 - att) to its
+    # leaf.  Recompute that from the oracle's own per-visit log for a few rays of config 1
+    # (unit cube, unit directions: delta_scale = 1).
+    from oracle import oracle as orc
+    case = CASES["c1_rays"]()
+    tree = orc.Tree.from_n3tree(case["tree"])
+    opt = orc.options(basis_dim=4)
+    o, d, v = [t.numpy()[:8] for t in case["rays"]]
+    with orc.weight_accumulation(tree, "sum") as acc_sum:
+        orc.volume_render(tree, o, d, v, opt)
+    with orc.weight_accumulation(tree, "max") as acc_max:
+        orc.volume_render(tree, o, d, v, opt)
+    want_sum = np.zeros(acc_sum.size)
+    want_max = np.zeros(acc_sum.size)
+    sigma = tree.data.reshape(-1, tree.K)[:, -1]
+    for i in range(8):
+        slots, dts, _, _ = orc.trace_log(tree, o[i], d[i], v[i], opt)
+        light = np.float32(1.0)
+        for s_, dt in zip(slots, dts):
+            sg = sigma[s_]
+            if sg > 0:
+                att = np.exp(np.float32(-dt) * np.float32(1.0) * sg, dtype=np.float32)
+                w = light * (np.float32(1.0) - att)
+                want_sum[s_] += float(w)
+                want_max[s_] = max(want_max[s_], float(w))
+                light = light * att
+    assert want_sum.sum() > 1.0
+    assert np.abs(acc_sum.reshape(-1) - want_sum).max() < 1e-6
+    assert np.abs(acc_max.reshape(-1) - want_max).max() < 1e-6
