@@ -10,7 +10,14 @@ outputs as ``ref_cuda_<case>.npz``:
     grad_*         digest of the gradient w.r.t. tree.data (see
                    tests/parity_util.grad_digest)
 
+and, for WEIGHT_CASES, the reference's weight accumulator after one forward
+render as ``ref_cuda_weights_<case>.npz`` (non-zero entries only):
+
+    idx            flat indices into (M, N, N, N)
+    sum, max       accumulated weight per index with op "sum" / "max"
+
 Usage: python tests/golden/make_ref_cuda_golden.py [out_dir] [case ...]
+       python tests/golden/make_ref_cuda_golden.py [out_dir] --weights
 """
 import os
 import sys
@@ -25,10 +32,27 @@ from golden.cases import CASES  # noqa: E402
 import parity_util as P  # noqa: E402
 
 
+WEIGHT_CASES = ["c1_rays", "shell_sh9_rays", "shell_sh16_image", "rgba_rays"]
+
+
+def weights(out_dir):
+    for name in WEIGHT_CASES:
+        case = CASES[name]()
+        s = P.run_ref_cuda(case, weight_op="sum")["weights"]
+        m = P.run_ref_cuda(case, weight_op="max")["weights"]
+        idx = np.flatnonzero((s != 0) | (m != 0)).astype(np.int64)
+        np.savez_compressed(os.path.join(out_dir, f"ref_cuda_weights_{name}.npz"), idx=idx,
+                            sum=s[idx].astype(np.float32), max=m[idx].astype(np.float32),
+                            size=np.int64(s.size))
+        print(name, "weights: non-zero", idx.size, "of", s.size, flush=True)
+
+
 def main():
-    out_dir = sys.argv[1] if len(sys.argv) > 1 else HERE
-    names = sys.argv[2:] or list(CASES)
+    out_dir = sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("--") else HERE
     os.makedirs(out_dir, exist_ok=True)
+    if "--weights" in sys.argv:
+        return weights(out_dir)
+    names = sys.argv[2:] or list(CASES)
     for name in names:
         case = CASES[name]()
         res = P.run_ref_cuda(case)

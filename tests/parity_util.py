@@ -146,7 +146,9 @@ def ref_module():
     return _ref_mod
 
 
-def run_ref_cuda(case, device="cuda:0", backward=True):
+def run_ref_cuda(case, device="cuda:0", backward=True, weight_op=None):
+    """``weight_op`` ("sum" / "max"): forward only, with the reference's weight accumulator
+    switched on; the flat accumulator comes back as ``weights``."""
     ref = ref_module()
     assert ref is not None, "oracle/_ref is not built"
     tree = case["tree"].to(device)
@@ -156,6 +158,10 @@ def run_ref_cuda(case, device="cuda:0", backward=True):
     spec.offset, spec.scaling = tree.offset, tree.invradius
     spec._weight_accum = torch.empty(0, device=device)
     spec._weight_accum_max = False
+    if weight_op is not None:
+        spec._weight_accum = torch.zeros(tree.child.shape, device=device)
+        spec._weight_accum_max = weight_op == "max"
+        backward = False
     res = {"ids": None, "grad": None}
     if case["kind"] == "query":
         pts = case["points"].to(device)
@@ -190,6 +196,8 @@ def run_ref_cuda(case, device="cuda:0", backward=True):
                 g = ref.volume_render_image_backward(spec, cs, opt, case["grad_out"].to(device))
                 res["grad"] = g.double().cpu().numpy()
     torch.cuda.synchronize()
+    if weight_op is not None:
+        res["weights"] = spec._weight_accum.cpu().numpy().reshape(-1)
     case["tree"].to("cpu")
     return res
 

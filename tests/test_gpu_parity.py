@@ -133,6 +133,12 @@ def test_weight_accumulation_matches_oracle(name, op, cuda_device):
     tol = 1e-5 * (1.0 + np.abs(want)) if op == "sum" else 2e-6
     assert np.all(np.abs(dense - want[:dense.size]) <= tol)
     assert np.all(want[dense.size:] == 0)
+    path = os.path.join(GOLD, f"ref_cuda_weights_{name}.npz")
+    if os.path.exists(path):    # the reference's CUDA extension on the same inputs
+        z = np.load(path)
+        ref = np.zeros(int(z["size"]))
+        ref[z["idx"]] = z[op]
+        assert np.all(np.abs(dense - ref[:dense.size]) <= tol)
     # accum() lists the leaves in the order of tree.values
     leaves = case["tree"]._all_leaves()
     flat = case["tree"]._pack_index(leaves).numpy()

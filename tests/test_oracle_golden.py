@@ -161,3 +161,18 @@ def test_weight_accumulation_matches_a_per_ray_recomputation():
     assert want_sum.sum() > 1.0
     assert np.abs(acc_sum.reshape(-1) - want_sum).max() < 1e-6
     assert np.abs(acc_max.reshape(-1) - want_max).max() < 1e-6
+
+
+@pytest.mark.parametrize("name", ["c1_rays", "shell_sh9_rays", "shell_sh16_image", "rgba_rays"])
+def test_weight_accumulation_against_reference_cuda_fixture(name):
+    # Fixtures: the reference's CUDA extension with tree._weight_accum switched on
+    # (tests/golden/make_ref_cuda_golden.py --weights).
+    z = np.load(os.path.join(GOLD, f"ref_cuda_weights_{name}.npz"))
+    case = CASES[name]()
+    for op in ("sum", "max"):
+        mine = P.run_weight_accumulation(case, op)
+        assert mine.size == int(z["size"])
+        want = np.zeros(mine.size)
+        want[z["idx"]] = z[op]
+        tol = 1e-5 * (1.0 + np.abs(want)) if op == "sum" else 2e-6
+        assert np.all(np.abs(mine - want) <= tol), np.abs(mine - want).max()
