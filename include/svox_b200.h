@@ -176,6 +176,26 @@ int svoxb_volume_render_image_backward_replay(const svoxb_tree* tree, const svox
                                               int32_t* log, int64_t capacity_chunks,
                                               int64_t chunks_used, float* grad_data_out,
                                               int zero_first, void* stream);
+/* Third result of se_grad / se_grad_persp (svox/csrc/rt_kernel.cu:479-715,
+ * 1111-1173): the diagonal of the Gauss-Newton matrix of the squared error
+ * 1/2 sum (render - colour)^2, i.e. for every element of data the sum over rays
+ * and channels of (d render / d element)^2.  Computed from the item log of a
+ * logged forward like the replay backward (same restrictions, same scratch);
+ * SVOXB_ERR_TOO_LARGE if the scratch cannot be had.  The first two results of
+ * se_grad are the logged forward's output and the replay backward with
+ * grad_output = render - colour. */
+int svoxb_volume_render_hessdiag_replay(const svoxb_tree* tree, const svoxb_rays* rays,
+                                        const svoxb_render_options* opt, const float* fwd_out,
+                                        int32_t* log, int64_t capacity_chunks,
+                                        int64_t chunks_used, float* hessdiag_out,
+                                        int zero_first, void* stream);
+int svoxb_volume_render_image_hessdiag_replay(const svoxb_tree* tree, const svoxb_camera* cam,
+                                              const svoxb_render_options* opt,
+                                              const float* fwd_out, int32_t* log,
+                                              int64_t capacity_chunks, int64_t chunks_used,
+                                              float* hessdiag_out, int zero_first,
+                                              void* stream);
+
 /* The replay backward in steps, for callers that overlap the all-reduce of the
  * gradient with its computation (no counterpart in the reference).  _begin
  * sorts the logged samples by leaf range (arguments as for

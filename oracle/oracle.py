@@ -216,6 +216,21 @@ def volume_render_backward(tree, origins, dirs, vdirs, opt, grad_out, want_count
     return (grad, vis, con) if want_counts else grad
 
 
+def se_grad(tree, origins, dirs, vdirs, opt, colors, want_abs=False):
+    """Rendered colour (float32), gradient and Gauss-Newton diagonal (float64) of
+    1/2 sum (render - colors)^2 -- the reference's ``se_grad`` (svox/renderer.py:324-349).
+    ``want_abs`` also returns the per-element sum of |gradient contributions|."""
+    o, d, v, c = _f32(origins), _f32(dirs), _f32(vdirs), _f32(colors)
+    Q = o.shape[0]
+    out = np.zeros((Q, out_dim(tree, opt)), np.float32)
+    grad, gabs = _grad_buffers(tree.data.shape, want_abs)
+    hess = np.zeros(tree.data.shape, np.float64)
+    _check(lib().orc_se_grad(C.byref(tree.c), _ptr(o), _ptr(d), _ptr(v), C.c_int64(Q),
+                             C.byref(opt), _ptr(c), _ptr(out), _ptr(grad), _ptr(hess)), "se_grad")
+    lib().orc_set_grad_abs(None, None)
+    return (out, grad, hess, gabs) if want_abs else (out, grad, hess)
+
+
 def _c2w34(c2w):
     c = _f32(np.asarray(c2w)[:3, :4])
     assert c.shape == (3, 4)

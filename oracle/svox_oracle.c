@@ -632,6 +632,184 @@ int orc_volume_render(const OrcTree* tr, const float* origins, const float* dirs
     return bad;
 }
 
+/* svox/csrc/rt_kernel.cu:479-715 (trace_ray_se_grad_hess): rendered colour,
+ * gradient and Gauss-Newton diagonal of 1/2 (render - color_ref)^2 for one
+ * ray, in three marches like the reference.  Per-ray arithmetic is float;
+ * grad and hess are double sums.  Colour formats with at most 4 outputs. */
+static int trace_ray_se_grad(const OrcTree* tr, const float* origin, float* dir,
+                             const float* vdir, const OrcOptions* opt, const float* color_ref,
+                             float* color_out, double* grad, double* hess) {
+    const int out_dim = out_dim_of(tr, opt);
+    const int K = tr->K;
+    float invdir[3], delta_scale, tmin, tmax;
+    if (!ray_setup(tr, origin, dir, invdir, &delta_scale, &tmin, &tmax)) {
+        for (int j = 0; j < out_dim; ++j) color_out[j] = opt->background_brightness;
+        return 0;
+    }
+    float pos[3], basis_fn[25];
+    if (opt->format == ORC_FORMAT_SH) sh_basis(opt->basis_dim, vdir, basis_fn);
+    const float d_rgb_pad = 1 + 2 * opt->rgb_padding;
+    const int sh = opt->format != ORC_FORMAT_RGBA;
+    for (int j = 0; j < out_dim; ++j) color_out[j] = 0.f;
+    /* PASS 1 (:517-563): residual */
+    {
+        float light = 1.f, t = tmin, cube_sz;
+        while (t < tmax) {
+            for (int j = 0; j < 3; ++j) pos[j] = madd(g_fc.pos, t, dir[j], origin[j]);
+            int64_t slot = descend(tr, pos, &cube_sz);
+            if (slot < 0) return 1;
+            const float* val = tr->data + slot * K;
+            float smin, smax;
+            dda_unit(g_fc.dda_leaf, pos, invdir, &smin, &smax);
+            const float delta_t = (smax - smin) / cube_sz + opt->step_size;
+            float sigma = val[K - 1];
+            if (opt->density_softplus) sigma = softplus_m1(sigma);
+            if (sigma > 0.0f) {
+                const float att = expf(-delta_t * delta_scale * sigma);
+                const float weight = light * (1.f - att);
+                for (int c = 0; c < out_dim; ++c) {
+                    float tmp = 0.0f;
+                    if (sh) {
+                        const int off = c * opt->basis_dim;
+                        for (int i = opt->min_comp; i <= opt->max_comp; ++i)
+                            tmp = madd(g_fc.sh_dot, basis_fn[i], val[off + i], tmp);
+                    } else {
+                        tmp = val[c];
+                    }
+                    color_out[c] += weight * (sigmoidf(tmp) * d_rgb_pad - opt->rgb_padding);
+                }
+                light *= att;
+            }
+            t += delta_t;
+        }
+        for (int j = 0; j < out_dim; ++j)
+            color_out[j] += light * opt->background_brightness - color_ref[j];
+    }
+    /* PASS 2 (:566-633): colour gradient and the full colour sum */
+    float color_accum[4] = {0, 0, 0, 0};
+    {
+        float light = 1.f, t = tmin, cube_sz;
+        while (t < tmax) {
+            for (int j = 0; j < 3; ++j) pos[j] = madd(g_fc.pos, t, dir[j], origin[j]);
+            int64_t slot = descend(tr, pos, &cube_sz);
+            if (slot < 0) return 1;
+            const float* val = tr->data + slot * K;
+            double* gval = grad + slot * K;
+            double* hval = hess + slot * K;
+            float smin, smax;
+            dda_unit(g_fc.dda_leaf, pos, invdir, &smin, &smax);
+            const float delta_t = (smax - smin) / cube_sz + opt->step_size;
+            float sigma = val[K - 1];
+            if (opt->density_softplus) sigma = softplus_m1(sigma);
+            if (sigma > 0.0f) {
+                const float att = expf(-delta_t * sigma * delta_scale);
+                const float weight = light * (1.f - att);
+                for (int c = 0; c < out_dim; ++c) {
+                    const int off = sh ? c * opt->basis_dim : c;
+                    float tmp = 0.0f;
+                    if (sh) {
+                        for (int i = opt->min_comp; i <= opt->max_comp; ++i)
+                            tmp = madd(g_fc.sh_dot, basis_fn[i], val[off + i], tmp);
+                    } else {
+                        tmp = val[c];
+                    }
+                    const float sg = sigmoidf(tmp);
+                    const float grad_ci = (float)((double)(weight * sg) * (1.0 - (double)sg) *
+                                                  (double)d_rgb_pad);
+                    if (sh) {
+                        for (int i = opt->min_comp; i <= opt->max_comp; ++i) {
+                            const float grad_wi = basis_fn[i] * grad_ci;
+                            scatter(&gval[off + i], grad_wi * color_out[c]);
+#pragma omp atomic
+                            hval[off + i] += (double)(grad_wi * grad_wi);
+                        }
+                    } else {
+                        scatter(&gval[c], grad_ci * color_out[c]);
+#pragma omp atomic
+                        hval[c] += (double)(grad_ci * grad_ci);
+                    }
+                    color_accum[c] += weight * (sg * d_rgb_pad - opt->rgb_padding);
+                }
+                light *= att;
+            }
+            t += delta_t;
+        }
+        for (int j = 0; j < out_dim; ++j) color_accum[j] += light * opt->background_brightness;
+    }
+    /* PASS 3 (:636-709): density gradient */
+    {
+        float light = 1.f, t = tmin, cube_sz, color_curr[4];
+        while (t < tmax) {
+            for (int j = 0; j < 3; ++j) pos[j] = madd(g_fc.pos, t, dir[j], origin[j]);
+            int64_t slot = descend(tr, pos, &cube_sz);
+            if (slot < 0) return 1;
+            const float* val = tr->data + slot * K;
+            double* gval = grad + slot * K;
+            double* hval = hess + slot * K;
+            float smin, smax;
+            dda_unit(g_fc.dda_leaf, pos, invdir, &smin, &smax);
+            const float delta_t = (smax - smin) / cube_sz + opt->step_size;
+            float sigma = val[K - 1];
+            const float raw_sigma = sigma;
+            if (opt->density_softplus) sigma = softplus_m1(sigma);
+            if (sigma > 0.0f) {
+                const float att = expf(-delta_t * sigma * delta_scale);
+                const float weight = light * (1.f - att);
+                for (int c = 0; c < out_dim; ++c) {
+                    float tmp = 0.0f;
+                    if (sh) {
+                        const int off = c * opt->basis_dim;
+                        for (int i = opt->min_comp; i <= opt->max_comp; ++i)
+                            tmp = madd(g_fc.sh_dot, basis_fn[i], val[off + i], tmp);
+                    } else {
+                        tmp = val[c];
+                    }
+                    color_curr[c] = sigmoidf(tmp) * d_rgb_pad - opt->rgb_padding;
+                    color_accum[c] -= weight * color_curr[c];
+                }
+                light *= att;
+                for (int j = 0; j < out_dim; ++j) {
+                    const float grad_sigma =
+                        delta_t * delta_scale * (color_curr[j] * light - color_accum[j]);
+                    const float grad2_sigma = grad_sigma * grad_sigma;
+                    if (opt->density_softplus) {
+                        const float sgm = sigmoidf(raw_sigma - 1);
+                        const float d_sgm = sgm * (1.f - sgm);
+                        scatter(&gval[K - 1], grad_sigma * color_out[j] * sgm);
+#pragma omp atomic
+                        hval[K - 1] += (double)(grad2_sigma * sgm * sgm + grad_sigma * d_sgm);
+                    } else {
+                        scatter(&gval[K - 1], grad_sigma * color_out[j]);
+#pragma omp atomic
+                        hval[K - 1] += (double)grad2_sigma;
+                    }
+                }
+            }
+            t += delta_t;
+        }
+    }
+    for (int j = 0; j < out_dim; ++j) color_out[j] += color_ref[j];
+    return 0;
+}
+
+/* svox/csrc/rt_kernel.cu:846-870 + 1111-1141 (se_grad). */
+int orc_se_grad(const OrcTree* tr, const float* origins, const float* dirs, const float* vdirs,
+                int64_t Q, const OrcOptions* opt, const float* colors, float* out, double* grad,
+                double* hess) {
+    const int od = out_dim_of(tr, opt);
+    if (od > 4) return 2;
+    int bad = 0;
+#pragma omp parallel for schedule(dynamic, 64) reduction(| : bad)
+    for (int64_t i = 0; i < Q; ++i) {
+        float o[3] = {origins[3 * i], origins[3 * i + 1], origins[3 * i + 2]};
+        float d[3] = {dirs[3 * i], dirs[3 * i + 1], dirs[3 * i + 2]};
+        transform_coord(o, tr->offset, tr->scaling);
+        bad |= trace_ray_se_grad(tr, o, d, vdirs + 3 * i, opt, colors + i * od, out + i * od,
+                                 grad, hess);
+    }
+    return bad;
+}
+
 /* Per-visit log of one ray (leaf slot, delta_t, t at entry): returns the
  * number of visits; at most cap are stored. */
 int64_t orc_trace_log(const OrcTree* tr, const float* origin, const float* dir,

@@ -406,6 +406,34 @@ def volume_render_backward_replay(tree, rays_or_cam, opt, grad_output, fwd_out, 
     return grad
 
 
+def volume_render_hessdiag_replay(tree, rays_or_cam, opt, fwd_out, logpair, image=False):
+    """Gauss-Newton diagonal of the squared error from the item log (third result of the
+    reference's ``se_grad``); None if the log overflowed."""
+    lib = library()
+    log, cap = logpair
+    dev = tree.data.device
+    with torch.cuda.device(dev):
+        used = _log_usage(log, cap, fwd_out.numel() // 3)
+        if used > cap:
+            return None
+        ct = _pack_tree(tree)
+        co = opt._pack()
+        _check_input(fwd_out, "fwd_out")
+        hess = torch.zeros_like(tree.data, memory_format=torch.contiguous_format)
+        if image:
+            cs = _pack_camera(rays_or_cam, dev)
+            fn = lib.svoxb_volume_render_image_hessdiag_replay
+        else:
+            cs = _pack_rays(rays_or_cam, dev)
+            fn = lib.svoxb_volume_render_hessdiag_replay
+        st = fn(C.byref(ct), C.byref(cs), C.byref(co), C.c_void_p(fwd_out.data_ptr()),
+                C.c_void_p(log.data_ptr()), C.c_int64(cap), C.c_int64(used),
+                C.c_void_p(hess.data_ptr()), C.c_int(0), _stream())
+    if st:
+        _raise(st, "volume_render_hessdiag_replay")
+    return hess
+
+
 def volume_render_backward_replay_parts(tree, rays_or_cam, opt, grad_output, fwd_out, logpair,
                                         n_parts, on_part, agree=None, reserve_sms=0,
                                         image=False):

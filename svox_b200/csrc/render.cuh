@@ -609,65 +609,76 @@ render_fwd_generic(TreeArgs tr, Source src, svoxb_render_options opt, TopTable t
         const int64_t gran = next_granule(&s_next, lane);
         if (gran >= n_gran) break;
         const int64_t ray = gran * 32 + lane;
-        if (ray >= Q) continue;
+        const bool valid = ray < Q;
         Ray r;
-        src.load(ray, tr, opt, r);
-        ray_setup(r, tr.scaling);
-        float o[kMaxGenericOut];
-        if (!r.hit) {
-            for (int j = 0; j < out_dim; ++j) o[j] = opt.background_brightness;
-        } else {
-            for (int j = 0; j < out_dim; ++j) o[j] = 0.f;
-            float basis[25];
-            if (sh) {
-                switch (opt.basis_dim) {
-                    case 25: sh_basis<25>(r.vdir, basis); break;
-                    case 16: sh_basis<16>(r.vdir, basis); break;
-                    case 9: sh_basis<9>(r.vdir, basis); break;
-                    case 4: sh_basis<4>(r.vdir, basis); break;
-                    default: sh_basis<1>(r.vdir, basis); break;
-                }
-            }
-            float light = 1.f, t = r.tmin;
-            bool stopped = false;
-            int it = 0;
-            while (t < r.tmax) {
-                if (++it > kMaxSteps) { report(SVOXB_ERR_MARCH); break; }
-                Step s;
-                if (!march_step(tr, top, r, t, opt.step_size, s)) break;
-                const float* __restrict__ rec = tr.data + s.leaf.slot * K;
-                float sigma = __ldg(rec + (K - 1));
-                if (opt.density_softplus) sigma = softplus_m1(sigma);
-                if (sigma > opt.sigma_thresh) {
-                    const float att = expf(-s.delta_t * r.delta_scale * sigma);
-                    const float weight = light * (1.f - att);
-                    if (tr.weight_accum != nullptr) accumulate_weight(tr, s.leaf.slot, weight);
-                    for (int ch = 0; ch < out_dim; ++ch) {
-                        float tmp;
-                        if (sh) {
-                            tmp = 0.0f;
-                            const int off = ch * opt.basis_dim;
-                            for (int i = opt.min_comp; i <= opt.max_comp; ++i)
-                                tmp += basis[i] * __ldg(rec + off + i);
-                        } else {
-                            tmp = __ldg(rec + ch);
-                        }
-                        o[ch] += weight * (sigmoid_ref(tmp) * d_rgb_pad - opt.rgb_padding);
-                    }
-                    light *= att;
-                    if (light <= opt.stop_thresh) {
-                        const float scale = 1.0 / (1.0 - light);
-                        for (int j = 0; j < out_dim; ++j) o[j] *= scale;
-                        stopped = true;
-                        break;
-                    }
-                }
-                t = __fadd_rn(t, s.delta_t);
-            }
-            if (!stopped)
-                for (int j = 0; j < out_dim; ++j) o[j] += light * opt.background_brightness;
+        r.hit = false;
+        if (valid) {
+            src.load(ray, tr, opt, r);
+            ray_setup(r, tr.scaling);
         }
-        for (int j = 0; j < out_dim; ++j) out[ray * out_dim + j] = o[j];
+        float o[kMaxGenericOut];
+        for (int j = 0; j < out_dim; ++j) o[j] = r.hit ? 0.f : opt.background_brightness;
+        float basis[25];
+        if (r.hit && sh) {
+            switch (opt.basis_dim) {
+                case 25: sh_basis<25>(r.vdir, basis); break;
+                case 16: sh_basis<16>(r.vdir, basis); break;
+                case 9: sh_basis<9>(r.vdir, basis); break;
+                case 4: sh_basis<4>(r.vdir, basis); break;
+                default: sh_basis<1>(r.vdir, basis); break;
+            }
+        }
+        float light = 1.f, t = r.tmin;
+        bool stopped = false;
+        int it = 0;
+        // Warp-uniform loop: the vote makes the warp reconverge every step.
+        bool go = r.hit && t < r.tmax;
+        while (__any_sync(0xffffffffu, go)) {
+            if (go) {
+                Step s;
+                if (++it > kMaxSteps) {
+                    report(SVOXB_ERR_MARCH);
+                    go = false;
+                } else if (!march_step(tr, top, r, t, opt.step_size, s)) {
+                    go = false;
+                } else {
+                    const float* __restrict__ rec = tr.data + s.leaf.slot * K;
+                    float sigma = __ldg(rec + (K - 1));
+                    if (opt.density_softplus) sigma = softplus_m1(sigma);
+                    if (sigma > opt.sigma_thresh) {
+                        const float att = expf(-s.delta_t * r.delta_scale * sigma);
+                        const float weight = light * (1.f - att);
+                        if (tr.weight_accum != nullptr)
+                            accumulate_weight(tr, s.leaf.slot, weight);
+                        for (int ch = 0; ch < out_dim; ++ch) {
+                            float tmp;
+                            if (sh) {
+                                tmp = 0.0f;
+                                const int off = ch * opt.basis_dim;
+                                for (int i = opt.min_comp; i <= opt.max_comp; ++i)
+                                    tmp += basis[i] * __ldg(rec + off + i);
+                            } else {
+                                tmp = __ldg(rec + ch);
+                            }
+                            o[ch] += weight * (sigmoid_ref(tmp) * d_rgb_pad - opt.rgb_padding);
+                        }
+                        light *= att;
+                        if (light <= opt.stop_thresh) {
+                            const float scale = 1.0 / (1.0 - light);
+                            for (int j = 0; j < out_dim; ++j) o[j] *= scale;
+                            stopped = true;
+                            go = false;
+                        }
+                    }
+                    t = __fadd_rn(t, s.delta_t);
+                    if (!(t < r.tmax)) go = false;
+                }
+            }
+        }
+        if (r.hit && !stopped)
+            for (int j = 0; j < out_dim; ++j) o[j] += light * opt.background_brightness;
+        if (valid)
+            for (int j = 0; j < out_dim; ++j) out[ray * out_dim + j] = o[j];
     }
 }
 
@@ -692,13 +703,14 @@ render_bwd_generic(TreeArgs tr, Source src, svoxb_render_options opt, TopTable t
         const int64_t gran = next_granule(&s_next, lane);
         if (gran >= n_gran) break;
         const int64_t ray = gran * 32 + lane;
-        if (ray >= Q) continue;
         Ray r;
-        src.load(ray, tr, opt, r);
-        ray_setup(r, tr.scaling);
-        if (!r.hit) continue;
+        r.hit = false;
+        if (ray < Q) {
+            src.load(ray, tr, opt, r);
+            ray_setup(r, tr.scaling);
+        }
         float basis[25];
-        if (sh) {
+        if (r.hit && sh) {
             switch (opt.basis_dim) {
                 case 25: sh_basis<25>(r.vdir, basis); break;
                 case 16: sh_basis<16>(r.vdir, basis); break;
@@ -707,61 +719,74 @@ render_bwd_generic(TreeArgs tr, Source src, svoxb_render_options opt, TopTable t
                 default: sh_basis<1>(r.vdir, basis); break;
             }
         }
-        const float* __restrict__ g = grad_out + ray * out_dim;
+        const float* __restrict__ g = grad_out + (r.hit ? ray : 0) * out_dim;
         float accum = 0.f;
         for (int pass = 0; pass < 2; ++pass) {
             float light = 1.f, t = r.tmin;
             int it = 0;
-            while (t < r.tmax) {
-                if (++it > kMaxSteps) { report(SVOXB_ERR_MARCH); break; }
-                Step s;
-                if (!march_step(tr, top, r, t, opt.step_size, s)) break;
-                const int64_t off = s.leaf.slot * K;
-                const float* __restrict__ rec = tr.data + off;
-                float sigma = __ldg(rec + (K - 1));
-                const float raw_sigma = sigma;
-                if (opt.density_softplus) sigma = softplus_m1(sigma);
-                if (sigma > 0.0f) {
-                    const float att = expf(-s.delta_t * sigma * r.delta_scale);
-                    const float weight = light * (1.f - att);
-                    float total_color = 0.f;
-                    for (int ch = 0; ch < out_dim; ++ch) {
-                        float tmp;
-                        const int coff = sh ? ch * opt.basis_dim : ch;
-                        if (sh) {
-                            tmp = 0.0f;
-                            for (int i = opt.min_comp; i <= opt.max_comp; ++i)
-                                tmp += basis[i] * __ldg(rec + coff + i);
-                        } else {
-                            tmp = __ldg(rec + ch);
-                        }
-                        const float sg = sigmoid_ref(tmp);
-                        const float gc = __ldg(g + ch);
-                        if (pass == 0) {
-                            if (sh) {
-                                const float tmp2 = weight * sg * (1.0 - sg) * gc * d_rgb_pad;
-                                for (int i = opt.min_comp; i <= opt.max_comp; ++i)
-                                    atomicAdd(grad_data + off + coff + i, basis[i] * tmp2);
+            // Warp-uniform loop: the vote makes the warp reconverge every step.
+            bool go = r.hit && t < r.tmax;
+            while (__any_sync(0xffffffffu, go)) {
+                if (go) {
+                    Step s;
+                    if (++it > kMaxSteps) {
+                        report(SVOXB_ERR_MARCH);
+                        go = false;
+                    } else if (!march_step(tr, top, r, t, opt.step_size, s)) {
+                        go = false;
+                    } else {
+                        const int64_t off = s.leaf.slot * K;
+                        const float* __restrict__ rec = tr.data + off;
+                        float sigma = __ldg(rec + (K - 1));
+                        const float raw_sigma = sigma;
+                        if (opt.density_softplus) sigma = softplus_m1(sigma);
+                        if (sigma > 0.0f) {
+                            const float att = expf(-s.delta_t * sigma * r.delta_scale);
+                            const float weight = light * (1.f - att);
+                            float total_color = 0.f;
+                            for (int ch = 0; ch < out_dim; ++ch) {
+                                float tmp;
+                                const int coff = sh ? ch * opt.basis_dim : ch;
+                                if (sh) {
+                                    tmp = 0.0f;
+                                    for (int i = opt.min_comp; i <= opt.max_comp; ++i)
+                                        tmp += basis[i] * __ldg(rec + coff + i);
+                                } else {
+                                    tmp = __ldg(rec + ch);
+                                }
+                                const float sg = sigmoid_ref(tmp);
+                                const float gc = __ldg(g + ch);
+                                if (pass == 0) {
+                                    if (sh) {
+                                        const float tmp2 =
+                                            weight * sg * (1.0 - sg) * gc * d_rgb_pad;
+                                        for (int i = opt.min_comp; i <= opt.max_comp; ++i)
+                                            atomicAdd(grad_data + off + coff + i, basis[i] * tmp2);
+                                    } else {
+                                        atomicAdd(grad_data + off + ch,
+                                                  weight * sg * (1.f - sg) * gc * d_rgb_pad);
+                                    }
+                                }
+                                total_color += (sg * d_rgb_pad - opt.rgb_padding) * gc;
+                            }
+                            light *= att;
+                            if (pass == 0) {
+                                accum += weight * total_color;
                             } else {
-                                atomicAdd(grad_data + off + ch,
-                                          weight * sg * (1.f - sg) * gc * d_rgb_pad);
+                                accum -= weight * total_color;
+                                atomicAdd(grad_data + off + (K - 1),
+                                          s.delta_t * r.delta_scale *
+                                              (total_color * light - accum) *
+                                              (opt.density_softplus ? sigmoid_ref(raw_sigma - 1)
+                                                                    : 1));
                             }
                         }
-                        total_color += (sg * d_rgb_pad - opt.rgb_padding) * gc;
-                    }
-                    light *= att;
-                    if (pass == 0) {
-                        accum += weight * total_color;
-                    } else {
-                        accum -= weight * total_color;
-                        atomicAdd(grad_data + off + (K - 1),
-                                  s.delta_t * r.delta_scale * (total_color * light - accum) *
-                                      (opt.density_softplus ? sigmoid_ref(raw_sigma - 1) : 1));
+                        t = __fadd_rn(t, s.delta_t);
+                        if (!(t < r.tmax)) go = false;
                     }
                 }
-                t = __fadd_rn(t, s.delta_t);
             }
-            if (pass == 0) {
+            if (pass == 0 && r.hit) {
                 float total_grad = 0.f;
                 for (int j = 0; j < out_dim; ++j) total_grad += __ldg(g + j);
                 accum += light * opt.background_brightness * total_grad;

@@ -88,13 +88,20 @@ __global__ void replay_pack_rays_kernel(TreeArgs tr, Source src, svoxb_render_op
     if (i >= n_rays) return;
     float v[3];
     src.load_vdir(i, tr, opt, v);
-    rays[3 * i] = make_float4(grad_out[3 * i], grad_out[3 * i + 1], grad_out[3 * i + 2],
-                              fwd_out[3 * i]);
+    float g[3] = {0.f, 0.f, 0.f};
+    if (grad_out != nullptr) {
+        g[0] = grad_out[3 * i]; g[1] = grad_out[3 * i + 1]; g[2] = grad_out[3 * i + 2];
+    }
+    rays[3 * i] = make_float4(g[0], g[1], g[2], fwd_out[3 * i]);
     rays[3 * i + 1] = make_float4(fwd_out[3 * i + 1], fwd_out[3 * i + 2], v[0], v[1]);
     rays[3 * i + 2] = make_float4(v[2], 0.f, 0.f, 0.f);
 }
 
-template <int BLOCK, int CPW, int MINB>   // CPW: chunks per warp and block step
+// HESS: instead of the gradient for an upstream grad_out, the packets carry what the
+// diagonal of the Gauss-Newton matrix of the squared error needs, i.e. the square of each
+// output's derivative summed over the three outputs (svox/csrc/rt_kernel.cu:596-605, 683-698):
+// the colour factor without grad_out, and sum_j (d out_j / d sigma)^2.
+template <int BLOCK, int CPW, int MINB, bool HESS>   // CPW: chunks per warp and block step
 __global__ void __launch_bounds__(BLOCK, MINB)
 replay_bin_kernel(svoxb_render_options opt, const int32_t* __restrict__ log, int64_t n_chunks,
                   int64_t n_rays, ReplayBins b) {
@@ -146,12 +153,19 @@ replay_bin_kernel(svoxb_render_options opt, const int32_t* __restrict__ log, int
                     const float sg = __int_as_float(ch[32 * (6 + chn) + lane]);
                     const float part = __int_as_float(ch[32 * (9 + chn) + lane]);
                     const float g = gg[chn];
-                    total_color += (sg * d_rgb_pad - opt.rgb_padding) * g;
-                    accum += (oo[chn] - part) * g;
-                    // colour-coefficient factor (rt_kernel.cu:390)
-                    f[j][chn] = wk * sg * (1.0 - sg) * g * d_rgb_pad;
+                    if (!HESS) {
+                        total_color += (sg * d_rgb_pad - opt.rgb_padding) * g;
+                        accum += (oo[chn] - part) * g;
+                        // colour-coefficient factor (rt_kernel.cu:390)
+                        f[j][chn] = wk * sg * (1.0 - sg) * g * d_rgb_pad;
+                    } else {
+                        f[j][chn] = wk * sg * (1.0 - sg) * d_rgb_pad;
+                        const float ds = dd * ((sg * d_rgb_pad - opt.rgb_padding) * T -
+                                               (oo[chn] - part));
+                        total_color += ds * ds;
+                    }
                 }
-                gs[j] = dd * (total_color * T - accum);
+                gs[j] = HESS ? total_color : dd * (total_color * T - accum);
                 rank[j] = atomicAdd(&s_cnt[bin[j]], 1);
             }
         }
@@ -194,7 +208,7 @@ struct alignas(16) ScatterSmem {
     alignas(16) float rows[32 * Shape::STRIDE + 4];
 };
 
-template <int BD, int BLOCK>
+template <int BD, int BLOCK, bool HESS>
 __global__ void __launch_bounds__(BLOCK)
 replay_scatter_kernel(int64_t n_slots, svoxb_render_options opt, float* __restrict__ grad_data,
                       const int32_t* __restrict__ log, ReplayBins b, int flags, int part,
@@ -265,7 +279,10 @@ replay_scatter_kernel(int64_t n_slots, svoxb_render_options opt, float* __restri
 #pragma unroll
             for (int chn = 0; chn < 3; ++chn)
 #pragma unroll
-                for (int k = 0; k < BD; ++k) v[chn * BD + k] = basis[k] * f[chn];
+                for (int k = 0; k < BD; ++k) {
+                    const float gw = basis[k] * f[chn];
+                    v[chn * BD + k] = HESS ? gw * gw : gw;
+                }
             v[K - 1] = __int_as_float(pb.x);
             float* row = sm.rows + lane * Shape::STRIDE;
             if (Shape::VEC) {

@@ -202,13 +202,14 @@ struct ReplayJob {
     svoxb_render_options opt{};
     int64_t n_slots = 0, n_rays = 0, chunks = 0;
     int K = 0, basis_dim = 0, n_parts = 1, shift = 0, n_bins = 1;
+    bool hess = false;   // Gauss-Newton diagonal instead of the gradient
 };
 
 // Prefix + pack + bin.  SVOXB_ERR_TOO_LARGE when the packet buffer cannot be had
 // (the caller then marches instead).
 template <class Source>
 static int replay_begin(const RenderCall& c, const Source& src, int64_t chunks, int n_parts,
-                        ReplayJob* job) {
+                        ReplayJob* job, bool hess = false) {
     if (chunks > c.log_capacity) chunks = c.log_capacity;
     if (n_parts < 1 || n_parts > kMaxParts) return SVOXB_ERR_OPTION;
     const int64_t packets = (chunks > 0 ? chunks : 1) * 32;
@@ -245,6 +246,7 @@ static int replay_begin(const RenderCall& c, const Source& src, int64_t chunks, 
     job->K = c.tree->K;
     job->basis_dim = c.opt.basis_dim;
     job->n_parts = n_parts;
+    job->hess = hess;
     job->shift = replay_bin_shift(c.tree->M, c.tree->K);
     job->n_bins = (int)(((job->n_slots - 1) >> job->shift) + 1);
 
@@ -258,7 +260,8 @@ static int replay_begin(const RenderCall& c, const Source& src, int64_t chunks, 
             if (s2 == SVOXB_OK) k<<<grid, block, 0, c.stream>>>(c.opt, c.log, chunks, c.Q, b);
             return s2;
         };
-        st = run_bin(replay_bin_kernel<128, 2, 12>, 128);
+        st = hess ? run_bin(replay_bin_kernel<128, 2, 12, true>, 128)
+                  : run_bin(replay_bin_kernel<128, 2, 12, false>, 128);
     }
     const cudaError_t e = cudaGetLastError();
     if (st == SVOXB_OK && e != cudaSuccess) st = set_cuda_error(e);
@@ -272,12 +275,12 @@ static int replay_begin(const RenderCall& c, const Source& src, int64_t chunks, 
 // Scatter of one part.  With `reserve_sms` > 0 that many SMs are left without a block
 // (for a collective that runs beside the scatter); small records then use one 1024-thread
 // block per SM, so that the SMs left out are really empty.
-template <int BD, int BLOCK>
+template <int BD, int BLOCK, bool HESS>
 static int replay_scatter_block(const ReplayJob& job, int part, float* grad, int reserve_sms,
                                 cudaStream_t stream) {
     constexpr int K = 3 * BD + 1;
     const size_t smem = (size_t)(BLOCK / 32) * sizeof(ScatterSmem<K>);
-    auto k = replay_scatter_kernel<BD, BLOCK>;
+    auto k = replay_scatter_kernel<BD, BLOCK, HESS>;
     unsigned grid = 1;
     int st = persistent_grid(k, BLOCK, smem, job.chunks, &grid);
     if (st) return st;
@@ -296,11 +299,12 @@ static int replay_scatter_block(const ReplayJob& job, int part, float* grad, int
 template <int BD>
 static int replay_scatter_bd(const ReplayJob& job, int part, float* grad, int reserve_sms,
                              cudaStream_t stream) {
+    if (job.hess) return replay_scatter_block<BD, 512, true>(job, part, grad, 0, stream);
     if constexpr (BD <= 9) {
         if (reserve_sms > 0)
-            return replay_scatter_block<BD, 1024>(job, part, grad, reserve_sms, stream);
+            return replay_scatter_block<BD, 1024, false>(job, part, grad, reserve_sms, stream);
     }
-    return replay_scatter_block<BD, 512>(job, part, grad, reserve_sms, stream);
+    return replay_scatter_block<BD, 512, false>(job, part, grad, reserve_sms, stream);
 }
 
 static int replay_scatter(const ReplayJob& job, int part, float* grad, int reserve_sms,
@@ -648,7 +652,7 @@ static int replay_backward(const svoxb_tree* tree, const Source& src, int64_t Q,
                            const svoxb_render_options* opt, const float* grad_output,
                            const float* fwd_out, int32_t* log, int64_t capacity_chunks,
                            int64_t chunks_used, float* grad_data_out, int zero_first,
-                           void* stream) {
+                           void* stream, bool hess = false) {
     int st = validate_tree(tree);
     if (st) return st;
     if ((st = validate_options(tree, *opt))) return st;
@@ -657,7 +661,7 @@ static int replay_backward(const svoxb_tree* tree, const Source& src, int64_t Q,
     if (zero_first && (st = zero_grad(tree, grad_data_out, tree->K, (cudaStream_t)stream)))
         return st;
     if (Q == 0) return SVOXB_OK;
-    if (!grad_output || !fwd_out) return SVOXB_ERR_NULL;
+    if ((!hess && !grad_output) || !fwd_out) return SVOXB_ERR_NULL;
     RenderCall c{tree, *opt, Q};
     c.backward = true;
     c.grad_out = grad_output;
@@ -668,12 +672,12 @@ static int replay_backward(const svoxb_tree* tree, const Source& src, int64_t Q,
     c.log_capacity = capacity_chunks;
     if (chunks_used <= 0 || chunks_used > capacity_chunks) chunks_used = capacity_chunks;
     ReplayJob job;
-    st = replay_begin(c, src, chunks_used, 1, &job);
+    st = replay_begin(c, src, chunks_used, 1, &job, hess);
     if (st == SVOXB_OK) {
         st = replay_scatter(job, 0, grad_data_out, 0, c.stream);
         replay_end(&job, c.stream);
     }
-    if (st == SVOXB_ERR_TOO_LARGE) {
+    if (st == SVOXB_ERR_TOO_LARGE && !hess) {
         // no room for the packets: march instead (same result, the log is not used)
         c.log = nullptr;
         c.log_capacity = 0;
@@ -731,6 +735,33 @@ int svoxb_volume_render_image_backward_replay(const svoxb_tree* tree, const svox
     return replay_backward(tree, PixelRays{cam->c2w, cam->fx, cam->fy, cam->width, cam->height},
                            (int64_t)cam->width * cam->height, opt, grad_output, fwd_out, log,
                            capacity_chunks, chunks_used, grad_data_out, zero_first, stream);
+}
+
+/* Gauss-Newton diagonal of the squared error from the item log (the third result of the
+ * reference's se_grad, svox/csrc/rt_kernel.cu:479-715, 1111-1173). */
+int svoxb_volume_render_hessdiag_replay(const svoxb_tree* tree, const svoxb_rays* rays,
+                                        const svoxb_render_options* opt, const float* fwd_out,
+                                        int32_t* log, int64_t capacity_chunks,
+                                        int64_t chunks_used, float* hessdiag_out,
+                                        int zero_first, void* stream) {
+    if (!tree || !rays || !opt) return SVOXB_ERR_NULL;
+    if (rays->Q > 0 && (!rays->origins || !rays->dirs || !rays->vdirs)) return SVOXB_ERR_NULL;
+    return replay_backward(tree, RayBatch{rays->origins, rays->dirs, rays->vdirs}, rays->Q, opt,
+                           nullptr, fwd_out, log, capacity_chunks, chunks_used, hessdiag_out,
+                           zero_first, stream, true);
+}
+
+int svoxb_volume_render_image_hessdiag_replay(const svoxb_tree* tree, const svoxb_camera* cam,
+                                              const svoxb_render_options* opt,
+                                              const float* fwd_out, int32_t* log,
+                                              int64_t capacity_chunks, int64_t chunks_used,
+                                              float* hessdiag_out, int zero_first,
+                                              void* stream) {
+    if (!tree || !cam || !opt || !cam->c2w) return SVOXB_ERR_NULL;
+    if (cam->width < 0 || cam->height < 0) return SVOXB_ERR_SHAPE;
+    return replay_backward(tree, PixelRays{cam->c2w, cam->fx, cam->fy, cam->width, cam->height},
+                           (int64_t)cam->width * cam->height, opt, nullptr, fwd_out, log,
+                           capacity_chunks, chunks_used, hessdiag_out, zero_first, stream, true);
 }
 
 }  // extern "C"

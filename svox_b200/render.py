@@ -182,6 +182,48 @@ class VolumeRenderer(nn.Module):
             self.tree.data, self.tree._spec(),
             _make_camera_spec(c2w, width, height, fx, fy), self._get_options(fast))
 
+    def se_grad(self, rays: Rays, colors):
+        """Rendered colour, gradient and Gauss-Newton diagonal of the total squared error
+        ``1/2 sum_r (C_hat(r) - C(r))^2`` (svox/renderer.py:324-349).
+
+        -> ``colors (B, 3), grad (shape of tree.data), diag_hessian (shape of tree.data)``.
+        The diagonal is the squared norm of the Jacobian's columns, as in the reference.
+        Octrees with SH colour, without density_softplus (the route through the item log).
+        """
+        self._require_cuda(True)
+        return self._se_grad(_rays_spec_from_rays(rays), colors, False)
+
+    def se_grad_persp(self, c2w, colors, width=800, height=800, fx=1111.111, fy=None):
+        """Image version of :meth:`se_grad` (svox/renderer.py:351-385); ``colors (H, W, 3)``."""
+        self._require_cuda(True)
+        if fy is None:
+            fy = fx
+        c2w = c2w.to(dtype=self.tree.data.dtype, device=self.tree.data.device).contiguous()
+        return self._se_grad(_make_camera_spec(c2w, width, height, fx, fy), colors, True)
+
+    def _se_grad(self, src, colors, image):
+        opt = self._get_options(False)
+        # the reference's kernel knows no thresholds (svox/csrc/rt_kernel.cu:537, 590)
+        opt.sigma_thresh = opt.stop_thresh = 0.0
+        tree = self.tree._spec()
+        if not _C.log_eligible(tree, opt):
+            raise NotImplementedError(
+                "se_grad needs an octree (N = 2) with SH colour, zero thresholds and no "
+                "density_softplus")
+        with torch.no_grad():
+            colors = colors.to(device=self.tree.data.device, dtype=self.tree.data.dtype)
+            for _ in range(4):      # a log that was too small is enlarged and the render redone
+                out, log = _C.volume_render_logged(tree, src, opt, image=image)
+                resid = (out - colors.reshape(out.shape)).contiguous()
+                grad = _C.volume_render_backward_replay(tree, src, opt, resid, out, log,
+                                                        image=image)
+                if grad is None:
+                    continue
+                hess = _C.volume_render_hessdiag_replay(tree, src, opt, out, log, image=image)
+                if hess is not None:
+                    return out, grad, hess
+        raise RuntimeError("se_grad: the item log kept overflowing")
+
     @staticmethod
     def persp_rays(c2w, width=800, height=800, fx=1111.111, fy=None):
         """Row-major perspective rays for :meth:`forward` (svox/renderer.py:387-426)."""

@@ -16,8 +16,16 @@ render as ``ref_cuda_weights_<case>.npz`` (non-zero entries only):
     idx            flat indices into (M, N, N, N)
     sum, max       accumulated weight per index with op "sum" / "max"
 
+and, for SE_GRAD_CASES, the reference's se_grad / se_grad_persp on the seeded
+colours of tests/parity_util.se_grad_colors as ``ref_cuda_se_grad_<case>.npz``:
+
+    out            returned colours
+    grad_*         digest of the gradient
+    hess_*         digest of the Gauss-Newton diagonal
+
 Usage: python tests/golden/make_ref_cuda_golden.py [out_dir] [case ...]
        python tests/golden/make_ref_cuda_golden.py [out_dir] --weights
+       python tests/golden/make_ref_cuda_golden.py [out_dir] --se-grad
 """
 import os
 import sys
@@ -47,11 +55,28 @@ def weights(out_dir):
         print(name, "weights: non-zero", idx.size, "of", s.size, flush=True)
 
 
+SE_GRAD_CASES = ["c1_rays", "shell_sh9_rays", "shell_sh16_image", "opt_comp_range"]
+
+
+def se_grad(out_dir):
+    for name in SE_GRAD_CASES:
+        case = CASES[name]()
+        res = P.run_se_grad(case, "ref_cuda")
+        blob = {"out": res["out"]}
+        blob.update(P.grad_digest(res["grad"]))
+        blob.update({"hess" + k[4:]: v for k, v in P.grad_digest(res["hess"]).items()})
+        np.savez_compressed(os.path.join(out_dir, f"ref_cuda_se_grad_{name}.npz"), **blob)
+        print(name, "se_grad out", res["out"].shape, "grad nnz", int(blob["grad_nnz"]),
+              "hess nnz", int(blob["hess_nnz"]), flush=True)
+
+
 def main():
     out_dir = sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("--") else HERE
     os.makedirs(out_dir, exist_ok=True)
     if "--weights" in sys.argv:
         return weights(out_dir)
+    if "--se-grad" in sys.argv:
+        return se_grad(out_dir)
     names = sys.argv[2:] or list(CASES)
     for name in names:
         case = CASES[name]()

@@ -270,3 +270,80 @@ def run_weight_accumulation(case, op, device=None):
         return dense[:n], per_leaf
     finally:
         case["tree"].to("cpu")
+
+
+# ---------------------------------------------------------------------------
+# se_grad: rendered colour, gradient and Gauss-Newton diagonal of the squared error
+
+def se_grad_colors(case):
+    """Seeded reference colours for a case: (Q, 3) for rays, (H, W, 3) for a camera."""
+    gen = torch.Generator().manual_seed(977)
+    if case["kind"] == "rays":
+        return torch.rand(case["rays"][0].shape[0], 3, generator=gen)
+    cam = case["camera"]
+    return torch.rand(cam["height"], cam["width"], 3, generator=gen)
+
+
+def run_se_grad(case, which, device="cuda:0"):
+    """``which``: "product", "oracle" or "ref_cuda" -> dict(out, grad, hess[, grad_abs])."""
+    tree = case["tree"]
+    colors = se_grad_colors(case)
+    if which == "oracle":
+        from oracle import oracle as orc
+        ot = orc.Tree.from_n3tree(tree, world=True)
+        opt = _oracle_options(case)
+        if case["kind"] == "rays":
+            o, d, v = [t.numpy() for t in case["rays"]]
+        else:
+            cam = case["camera"]
+            o, d = orc.pixel_rays(cam["c2w"].numpy(), cam["fx"], cam["fy"], cam["width"],
+                                  cam["height"])
+            v = d
+        out, grad, hess, gabs = orc.se_grad(ot, o, d, v, opt, colors.reshape(-1, 3).numpy(),
+                                            want_abs=True)
+        return dict(out=out.reshape(colors.shape), grad=grad, hess=hess, grad_abs=gabs)
+    t = tree.to(device)
+    try:
+        if which == "product":
+            r = _renderer(t, case)
+            if case["kind"] == "rays":
+                res = r.se_grad(svox_b200.Rays(*[x.to(device) for x in case["rays"]]),
+                                colors.to(device))
+            else:
+                cam = case["camera"]
+                res = r.se_grad_persp(cam["c2w"].to(device), colors.to(device),
+                                      width=cam["width"], height=cam["height"], fx=cam["fx"],
+                                      fy=cam["fy"])
+            _C.check_device_status()
+        else:
+            ref = ref_module()
+            assert ref is not None, "oracle/_ref is not built"
+            spec = ref.TreeSpec()
+            spec.data, spec.child, spec.parent_depth = t.data.data, t.child, t.parent_depth
+            spec.extra_data = torch.empty((0, 0), device=device)
+            spec.offset, spec.scaling = t.offset, t.invradius
+            spec._weight_accum = torch.empty(0, device=device)
+            spec._weight_accum_max = False
+            po = options_of(case)
+            opt = ref.RenderOptions()
+            for k in ("step_size", "background_brightness", "format", "basis_dim", "ndc_width",
+                      "ndc_height", "ndc_focal", "min_comp", "max_comp", "sigma_thresh",
+                      "stop_thresh", "density_softplus", "rgb_padding"):
+                setattr(opt, k, getattr(po, k))
+            if case["kind"] == "rays":
+                rs = ref.RaysSpec()
+                rs.origins, rs.dirs, rs.vdirs = [x.to(device).contiguous() for x in case["rays"]]
+                res = ref.se_grad(spec, rs, colors.to(device), opt)
+            else:
+                cam = case["camera"]
+                cs = ref.CameraSpec()
+                cs.c2w = cam["c2w"].to(device).contiguous()
+                cs.width, cs.height, cs.fx, cs.fy = (cam["width"], cam["height"], cam["fx"],
+                                                     cam["fy"])
+                res = ref.se_grad_persp(spec, cs, opt, colors.to(device))
+            torch.cuda.synchronize()
+        out, grad, hess = res
+        return dict(out=out.cpu().numpy(), grad=grad.double().cpu().numpy(),
+                    hess=hess.double().cpu().numpy())
+    finally:
+        case["tree"].to("cpu")

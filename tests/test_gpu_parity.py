@@ -145,6 +145,30 @@ def test_weight_accumulation_matches_oracle(name, op, cuda_device):
     assert np.array_equal(per_leaf, dense[flat])
 
 
+@pytest.mark.parametrize("name", ["c1_rays", "shell_sh9_rays", "shell_sh16_image",
+                                  "opt_comp_range", "aniso_rays"])
+def test_se_grad_matches_oracle_and_reference_fixture(name, cuda_device):
+    # VolumeRenderer.se_grad / se_grad_persp (svox/renderer.py:324-385): colour, gradient and
+    # Gauss-Newton diagonal of the squared error against seeded colours.
+    case = CASES[name]()
+    mine = P.run_se_grad(case, "product", cuda_device)
+    orc = P.run_se_grad(case, "oracle")
+    assert np.abs(mine["out"] - orc["out"]).max() <= RGB_TOL
+    assert P.grad_excess(mine["grad"], orc["grad"], orc["grad_abs"], GRAD_TOL_ORACLE) <= 1.0
+    hmax = np.abs(orc["hess"]).max()
+    assert np.all(np.abs(mine["hess"] - orc["hess"]) <= 1e-3 * orc["hess"] + 1e-4 * hmax)
+    path = os.path.join(GOLD, f"ref_cuda_se_grad_{name}.npz")
+    if os.path.exists(path):
+        z = np.load(path)
+        assert np.abs(mine["out"] - z["out"]).max() <= RGB_TOL
+        gi, hi = z["grad_idx"], z["hess_idx"]
+        worst = P.grad_excess(mine["grad"].reshape(-1)[gi], z["grad_val"],
+                              orc["grad_abs"].reshape(-1)[gi], GRAD_TOL_REF)
+        assert worst <= 2.5, f"gradient off by {worst:.2f} x tolerance"
+        h, want = mine["hess"].reshape(-1)[hi], z["hess_val"]
+        assert np.all(np.abs(h - want) <= 1e-4 * want + 1e-5 * np.abs(want).max())
+
+
 def test_item_log_overflow_falls_back(cuda_device):
     # A log that is too small must not be replayed: the backward marches instead.
     case = CASES["shell_sh9_rays"]()

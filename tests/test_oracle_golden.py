@@ -176,3 +176,20 @@ def test_weight_accumulation_against_reference_cuda_fixture(name):
         want[z["idx"]] = z[op]
         tol = 1e-5 * (1.0 + np.abs(want)) if op == "sum" else 2e-6
         assert np.all(np.abs(mine - want) <= tol), np.abs(mine - want).max()
+
+
+@pytest.mark.parametrize("name", ["c1_rays", "opt_comp_range", "shell_sh16_image"])
+def test_se_grad_against_reference_cuda_fixture(name):
+    # Fixtures: the reference's se_grad / se_grad_persp (CUDA) on seeded colours
+    # (tests/golden/make_ref_cuda_golden.py --se-grad).
+    z = np.load(os.path.join(GOLD, f"ref_cuda_se_grad_{name}.npz"))
+    case = CASES[name]()
+    mine = P.run_se_grad(case, "oracle")
+    assert np.abs(mine["out"] - z["out"]).max() <= 1e-5
+    gi, hi = z["grad_idx"], z["hess_idx"]
+    worst = P.grad_excess(mine["grad"].reshape(-1)[gi], z["grad_val"],
+                          mine["grad_abs"].reshape(-1)[gi], 1e-3)
+    assert worst <= 1.0, worst
+    h, want = mine["hess"].reshape(-1)[hi], z["hess_val"]
+    assert np.all(np.abs(h - want) <= 1e-3 * want + 1e-4 * np.abs(want).max())
+    assert abs(mine["hess"].sum() - float(z["hess_sum"])) <= 1e-3 * float(z["hess_sum"])
