@@ -34,7 +34,7 @@ METRIC = "Mrays/s volume_render fwd+bwd (SH deg 2, 2^20 rays)"
 UNIT = "Mrays/s"
 # DRAM bytes (read + write) of one launch on the default workload, from the ncu capture
 # summarised in profiles/training_step_config4_ncu_full.md
-NCU_TRAFFIC_FWD = 20.6e9
+NCU_TRAFFIC_FWD = 18.7e9
 NCU_TRAFFIC_BWD = 5.7e9 + 4.1e9
 
 
@@ -81,7 +81,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+                 "-lms", "50", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
         except OSError:
