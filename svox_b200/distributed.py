@@ -47,6 +47,8 @@ class _Overlap:
 
     @classmethod
     def on_part(cls, rows):
+        if rows.numel() == 0:       # the same ranges are empty on every rank
+            return
         cls.works.append(dist.all_reduce(rows, op=dist.ReduceOp.SUM, group=cls.group,
                                          async_op=True))
 

@@ -169,6 +169,54 @@ def test_se_grad_matches_oracle_and_reference_fixture(name, cuda_device):
         assert np.all(np.abs(h - want) <= 1e-4 * want + 1e-5 * np.abs(want).max())
 
 
+@pytest.mark.parametrize("name,image", [("shell_sh9_rays", False), ("shell_sh16_image", True)])
+def test_replay_in_parts_equals_replay_in_one_go(name, image, cuda_device):
+    # svoxb_replay_begin / _scatter / _end: the gradient produced leaf range by leaf range.
+    # After part p only rows of parts <= p may be non-zero, the ranges tile the tree, and the
+    # result equals the one-shot replay.
+    case = CASES[name]()
+    tree = case["tree"].to(cuda_device)
+    try:
+        r = P._renderer(tree, case)
+        opt = r._get_options(False)
+        opt.sigma_thresh = opt.stop_thresh = 0.0           # the log needs both off
+        spec = tree._spec()
+        if image:
+            cam = case["camera"]
+            src = svox.render._make_camera_spec(cam["c2w"].to(cuda_device).contiguous(),
+                                                cam["width"], cam["height"], cam["fx"], cam["fy"])
+        else:
+            src = svox.render._rays_spec_from_rays(
+                svox.Rays(*[t.to(cuda_device) for t in case["rays"]]))
+        gout = case["grad_out"].to(cuda_device).contiguous()
+        for _ in range(3):
+            out, log = csrc.volume_render_logged(spec, src, opt, image=image)
+            whole = csrc.volume_render_backward_replay(spec, src, opt, gout, out, log, image=image)
+            if whole is not None:
+                break
+        assert whole is not None
+        seen = []
+
+        def on_part(rows):
+            seen.append((rows.data_ptr(), rows.numel(), float(rows.abs().sum())))
+
+        parts = csrc.volume_render_backward_replay_parts(spec, src, opt, gout, out, log, 5,
+                                                         on_part, agree=lambda ok: ok,
+                                                         reserve_sms=8, image=image)
+        assert parts is not None and len(seen) == 5
+        filled = [x for x in seen if x[1] > 0]             # an empty view has no address
+        assert filled[0][0] == parts.data_ptr()
+        for (p0, n0, _), (p1, _, _) in zip(filled, filled[1:]):
+            assert p1 == p0 + 4 * n0                       # consecutive, no gaps
+        assert sum(n for _, n, _ in seen) == parts.numel()
+        assert any(a > 0 for _, _, a in seen)
+        scale = whole.abs().max().item()
+        assert (parts - whole).abs().max().item() <= 1e-5 * scale
+        csrc.check_device_status()
+    finally:
+        case["tree"].to("cpu")
+
+
 def test_item_log_overflow_falls_back(cuda_device):
     # A log that is too small must not be replayed: the backward marches instead.
     case = CASES["shell_sh9_rays"]()
