@@ -271,14 +271,18 @@ const char* svoxb_strerror(int status);
  * thread (empty string if none). */
 const char* svoxb_last_cuda_error(void);
 
-/* Experiment hook (no counterpart in the reference): key 0 = render block
- * size (256 or 1024, 0 = automatic), key 1 = cap on the render jump-table
- * level (-1 = automatic), key 2 = cap on the query jump-table level, key 3 =
- * render algorithm (2 = item queue, the default; 0 = warp-cooperative; 1 = one
- * thread per ray), key 5 = MB of gradient one bin of the replay backward spans
- * (default 16), key 6 = L2 hint bits of the replay scatter (1 = packets
- * evict-first, 2 = gradient evict-last; default 3), key 7 = bricks below the
- * render leaf table (1 = on, the default; 0 = off). */
+/* Experiment hook (no counterpart in the reference).  Keys:
+ *   0  threads per block of the render kernels (0 = automatic: 640)
+ *   1  cap on the level of the render leaf table (-1 = automatic: 6)
+ *   2  cap on the level of the query jump table (-1 = automatic: 7)
+ *   3  render algorithm (2 = item queue, the default; 0 = warp-cooperative;
+ *      1 = one thread per ray)
+ *   5  MB of gradient one bin of the replay backward spans (default 16)
+ *   6  L2 hint bits of the replay scatter (1 = packets evict-first,
+ *      2 = gradient evict-last; default 3)
+ *   7  bricks below the render leaf table (1 = on, the default; 0 = off)
+ *   8  lanes of a warp that must be idle before new rays are loaded (default 4)
+ * Unknown keys return SVOXB_ERR_OPTION. */
 int svoxb_tune(int key, int value);
 
 /* Library version, "major.minor.patch". */
