@@ -285,6 +285,23 @@ def test_empty_and_ragged_inputs(cuda_device):
         assert torch.equal(part, full[:q])
     pts = torch.rand(77, 3, device=cuda_device)
     assert torch.equal(tree(pts), tree(pts.repeat(3, 1))[:77])
+    # training steps on ragged batches: the replayed gradient equals the marched one
+    from svox_b200 import render as _render
+    for q in (0, 1, 33):
+        grads = []
+        for use_log in (True, False):
+            _render.USE_ITEM_LOG = use_log
+            try:
+                tree.zero_grad(set_to_none=True)
+                out = r(svox.Rays(*[t[:q].to(cuda_device) for t in rays]))
+                (out * out).sum().backward()
+                g = tree.data.grad
+                grads.append(torch.zeros_like(tree.data) if g is None else g.clone())
+            finally:
+                _render.USE_ITEM_LOG = True
+        scale = max(grads[1].abs().max().item(), 1e-30)
+        assert (grads[0] - grads[1]).abs().max().item() <= 1e-5 * scale
+    csrc.check_device_status()
 
 
 def test_rays_missing_the_cube_get_background(cuda_device):
