@@ -1,7 +1,7 @@
 """Generate fixtures from the reference's own Python (CPU tensor) path.
 
-Imports the unmodified reference package from a checkout (default
-/root/reference; it has no compiled extension there, so every call takes the
+Imports the unmodified reference package from a checkout (first argument, or
+the default below; it has no compiled extension there, so every call takes the
 pure-PyTorch path of svox/svox.py:224-268 and svox/renderer.py:205-282) and
 stores its outputs for the seeded cases it can express: zero thresholds,
 unit-cube world box, SH / RGBA colour.  Trees are built with the reference's
