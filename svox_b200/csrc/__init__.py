@@ -307,7 +307,7 @@ def volume_render_image(tree, cam, opt):
 # Logged forward / replay backward (training step without a second march)
 
 _items_per_ray = 48.0   # running estimate used to size the item log
-_LOG_LIST_SLACK = 2 * 16384
+_LOG_SLACK_CHUNKS = 2 * 16384   # every warp of the forward takes log chunks 8 at a time
 
 
 def log_eligible(tree, opt):
@@ -321,7 +321,7 @@ def log_eligible(tree, opt):
 def _log_alloc(n_rays, device):
     lib = library()
     lib.svoxb_item_log_words.restype = C.c_int64
-    cap = int(n_rays * _items_per_ray / 32) + _LOG_LIST_SLACK
+    cap = int(n_rays * _items_per_ray / 32) + _LOG_SLACK_CHUNKS
     words = lib.svoxb_item_log_words(C.c_int64(cap))
     return torch.empty(words, dtype=torch.int32, device=device), cap
 

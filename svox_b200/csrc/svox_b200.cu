@@ -395,7 +395,9 @@ static int launch_queue(const RenderCall& c, const Source& src) {
                                        : sizeof(WarpQueue<K, kModeForward>);
     // 640 threads: the kernel needs ~90 registers; at 768 (80 registers) it spills in the loop
     int want = g_tuning.render_block > 0 ? g_tuning.render_block : 640;
-    while (want > 256 && top_bytes + (size_t)(want / 32) * per_warp + 64 > kMaxSmem) want -= 128;
+    // static shared memory: the ticket counter, and the bin histogram of the logged forward
+    const size_t fixed = 64 + (c.log ? (size_t)kMaxBins * sizeof(int) : 0);
+    while (want > 256 && top_bytes + (size_t)(want / 32) * per_warp + fixed > kMaxSmem) want -= 128;
     if constexpr (BD <= 9) {
         if (want >= 1024) return launch_queue_block<BD, 1024>(c, src, tr, top, top_bytes);
         if (want >= 768) return launch_queue_block<BD, 768>(c, src, tr, top, top_bytes);

@@ -223,17 +223,17 @@ def test_item_log_overflow_falls_back(cuda_device):
     old = csrc._items_per_ray
     try:
         csrc._items_per_ray = 0.0
-        slack = csrc._LOG_LIST_SLACK
-        csrc._LOG_LIST_SLACK = 64                       # far fewer chunks than needed
+        slack = csrc._LOG_SLACK_CHUNKS
+        csrc._LOG_SLACK_CHUNKS = 64                       # far fewer chunks than needed
         a = P.run_product(case, cuda_device)
-        csrc._LOG_LIST_SLACK = slack
+        csrc._LOG_SLACK_CHUNKS = slack
         assert csrc._items_per_ray > 1.0                # the estimate was raised for next time
         b = P.run_product(case, cuda_device, item_log=False)
         orc = P.run_oracle(case)
         assert P.grad_excess(a["grad"], b["grad"], orc["grad_abs"], GRAD_TOL_REF) <= 2.5
     finally:
         csrc._items_per_ray = old
-        csrc._LOG_LIST_SLACK = slack
+        csrc._LOG_SLACK_CHUNKS = slack
 
 
 def test_toy_example_known_answer(cuda_device):
