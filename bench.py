@@ -51,8 +51,8 @@ def parse():
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--overlap-parts", type=int, default=-1,
                    help="N > 1: leaf ranges whose all-reduce overlaps the backward (0 = one "
-                        "all-reduce after the backward; -1 = 8 up to 4 GPUs, else 0: measured "
-                        "+4 %% at N = 2, -1 %% at N = 8)")
+                        "all-reduce of the whole gradient after the backward; 1 = one all-reduce "
+                        "of the leaf ranges that hold samples; -1 = 8 up to 4 GPUs, else 1)")
     return p.parse_args()
 
 
@@ -192,7 +192,7 @@ def run_b200(a):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
         if a.overlap_parts < 0:
-            a.overlap_parts = 8 if world <= 4 else 0
+            a.overlap_parts = 8 if world <= 4 else 1
         D.overlap_grad_allreduce(a.overlap_parts)
 
     tree_cpu, rays_cpu, targets_cpu = W.config4(Q=a.rays, init_refine=a.init_refine,
@@ -288,8 +288,9 @@ def run_b200(a):
         "config": {"workload": workload_name(a), "rays_per_gpu": n_local,
                    "rays_per_step": total,
                    "parallelism": f"rays sharded x{world}, tree replicated, "
-                                  + ((f"NCCL all-reduce of data.grad in {a.overlap_parts} leaf ranges, "
-                                      "overlapped with the backward scatter" if a.overlap_parts
+                                  + ((f"NCCL all-reduce of the leaf ranges of data.grad that hold "
+                                      f"samples, in {a.overlap_parts} part(s) overlapped with the "
+                                      "backward scatter" if a.overlap_parts
                                       else "one NCCL all-reduce of data.grad")
                                      if world > 1 else "no collective"),
                    "l2": "inputs larger than L2 (1.18 GB tree data vs 126 MB)",

@@ -201,7 +201,7 @@ int svoxb_volume_render_image_hessdiag_replay(const svoxb_tree* tree, const svox
  * sorts the logged samples by leaf range (arguments as for
  * svoxb_volume_render_backward_replay; SVOXB_ERR_TOO_LARGE if the scratch
  * cannot be had) and returns a job.  The leaf slots are cut into `n_parts`
- * (1..16) consecutive ranges; svoxb_replay_part_range gives the slots
+ * (1..16) consecutive ranges (whole bins); svoxb_replay_part_range gives the slots
  * [begin, end) of a part, i.e. rows [begin*K, end*K) of the flat gradient.
  * svoxb_replay_scatter adds the gradient of one part into grad_data_out (the
  * caller zeroes it first); with reserve_sms > 0 it leaves that many SMs free
@@ -216,6 +216,13 @@ int svoxb_replay_image_begin(const svoxb_tree* tree, const svoxb_camera* cam,
                              const float* fwd_out, int32_t* log, int64_t capacity_chunks,
                              int64_t chunks_used, int n_parts, void* stream, void** job);
 int svoxb_replay_part_range(const void* job, int part, int64_t* slot_begin, int64_t* slot_end);
+/* Optional, before the first scatter: let the parts tile only the bins
+ * [bin_begin, bin_end) (bin = leaf slot >> svoxb_replay_bin_shift; the forward's
+ * per-bin sample counts are words 32.. of the log).  Rows outside receive no
+ * sample; a caller that knows them empty on every process need not reduce them. */
+int svoxb_replay_set_span(void* job, int bin_begin, int bin_end, void* stream);
+/* log2 of the leaf slots per bin for a tree of M nodes and K floats per record. */
+int svoxb_replay_bin_shift(int64_t M, int32_t K);
 int svoxb_replay_scatter(const void* job, int part, float* grad_data_out, int reserve_sms,
                          void* stream);
 int svoxb_replay_end(void* job, void* stream);

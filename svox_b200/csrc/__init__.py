@@ -307,6 +307,9 @@ def volume_render_image(tree, cam, opt):
 # Logged forward / replay backward (training step without a second march)
 
 _items_per_ray = 48.0   # running estimate used to size the item log
+# Layout of the log's head (render_queue.cuh): word 2 = bin shift, word 3 = number of bins,
+# words LOG_HIST .. LOG_HIST + LOG_MAX_BINS = samples per bin of the last logged forward.
+LOG_HIST, LOG_MAX_BINS = 32, 1024
 _LOG_SLACK_CHUNKS = 2 * 16384   # every warp of the forward takes log chunks 8 at a time
 
 
@@ -440,8 +443,11 @@ def volume_render_backward_replay_parts(tree, rays_or_cam, opt, grad_output, fwd
     """The replay backward in ``n_parts`` consecutive leaf ranges.  After each part
     ``on_part(rows)`` is called with the flat view of the gradient rows that are final
     (e.g. to start their all-reduce while the next part is computed).  ``agree(ok)``, if
-    given, is called once with whether this process can replay and returns whether all
-    processes can (they must take the same route when ``on_part`` runs a collective).
+    given, is called once as ``agree(ok, log)`` with whether this process can replay and
+    the log (words ``LOG_HIST`` on hold the samples per bin) and returns False (some process
+    cannot: they must take the same route when ``on_part`` runs a collective), True, or
+    ``(bin_begin, bin_end)``: the parts then tile only those bins -- the rows outside
+    receive no sample from this process.
     Returns None if the replay was not possible (nothing has been handed to ``on_part``)."""
     lib = library()
     log, cap = logpair
@@ -469,12 +475,22 @@ def volume_render_backward_replay_parts(tree, rays_or_cam, opt, grad_output, fwd
                 if st and st != ERR_TOO_LARGE:
                     _raise(st, "replay_begin")
                 ok = st == 0
+            span = None
             if agree is not None:
-                ok = bool(agree(ok))
+                verdict = agree(ok, log)
+                ok = verdict is not False and verdict is not None
+                if ok and verdict is not True:
+                    span = verdict
             if not ok:
                 if job:
                     lib.svoxb_replay_end(job, _stream())
                 return None
+            if span is not None:
+                st = lib.svoxb_replay_set_span(job, C.c_int(int(span[0])), C.c_int(int(span[1])),
+                                               _stream())
+                if st:
+                    lib.svoxb_replay_end(job, _stream())
+                    _raise(st, "replay_set_span")
             grad = torch.zeros_like(tree.data, memory_format=torch.contiguous_format)
             flat = grad.view(-1)
             K = tree.data.shape[-1]

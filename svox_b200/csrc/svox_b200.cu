@@ -203,6 +203,7 @@ struct ReplayJob {
     int64_t n_slots = 0, n_rays = 0, chunks = 0;
     int K = 0, basis_dim = 0, n_parts = 1, shift = 0, n_bins = 1;
     bool hess = false;   // Gauss-Newton diagonal instead of the gradient
+    int bin_begin = 0, bin_end = -1;  // bins the parts tile (-1: all)
 };
 
 // Prefix + pack + bin.  SVOXB_ERR_TOO_LARGE when the packet buffer cannot be had
@@ -291,7 +292,8 @@ static int replay_scatter_block(const ReplayJob& job, int part, float* grad, int
         if ((int64_t)grid > most) grid = (unsigned)(most > 1 ? most : 1);
     }
     k<<<grid, BLOCK, smem, stream>>>(job.n_slots, job.opt, grad, job.log, job.bins,
-                                    g_tuning.replay_flags, part, job.n_parts);
+                                    g_tuning.replay_flags, part, job.n_parts, job.bin_begin,
+                                    job.bin_end);
     const cudaError_t e = cudaGetLastError();
     return e != cudaSuccess ? set_cuda_error(e) : SVOXB_OK;
 }
@@ -825,13 +827,31 @@ int svoxb_replay_image_begin(const svoxb_tree* tree, const svoxb_camera* cam,
                                 capacity_chunks, chunks_used, n_parts, stream, job);
 }
 
+int svoxb_replay_bin_shift(int64_t M, int32_t K) {
+    if (M < 1 || K < 1) return 0;
+    return replay_bin_shift(M, K);
+}
+
+int svoxb_replay_set_span(void* job, int bin_begin, int bin_end, void* stream) {
+    if (!job) return SVOXB_ERR_NULL;
+    ReplayJob* j = static_cast<ReplayJob*>(job);
+    if (bin_begin < 0 || bin_end < bin_begin || bin_end > j->n_bins) return SVOXB_ERR_OPTION;
+    j->bin_begin = bin_begin;
+    j->bin_end = bin_end;
+    replay_parts_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(j->bins, j->n_parts, bin_begin,
+                                                           bin_end);
+    const cudaError_t e = cudaGetLastError();
+    return e != cudaSuccess ? set_cuda_error(e) : SVOXB_OK;
+}
+
 int svoxb_replay_part_range(const void* job, int part, int64_t* slot_begin, int64_t* slot_end) {
     if (!job || !slot_begin || !slot_end) return SVOXB_ERR_NULL;
     const ReplayJob* j = static_cast<const ReplayJob*>(job);
     if (part < 0 || part >= j->n_parts) return SVOXB_ERR_OPTION;
-    const int64_t lo = (int64_t)replay_part_first_bin(part, j->n_parts, j->n_bins) << j->shift;
-    int64_t hi = (int64_t)replay_part_first_bin(part + 1, j->n_parts, j->n_bins) << j->shift;
-    if (part == j->n_parts - 1 || hi > j->n_slots) hi = j->n_slots;
+    const int b0 = j->bin_begin, b1 = j->bin_end < 0 ? j->n_bins : j->bin_end;
+    const int64_t lo = (int64_t)replay_part_first_bin(part, j->n_parts, b0, b1) << j->shift;
+    int64_t hi = (int64_t)replay_part_first_bin(part + 1, j->n_parts, b0, b1) << j->shift;
+    if (hi > j->n_slots) hi = j->n_slots;
     *slot_begin = lo < j->n_slots ? lo : j->n_slots;
     *slot_end = hi;
     return SVOXB_OK;

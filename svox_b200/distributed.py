@@ -53,12 +53,23 @@ class _Overlap:
                                          async_op=True))
 
     @classmethod
-    def agree(cls, ok):
-        # every rank must take the same route: the parts run one collective each
-        flag = torch.tensor([1 if ok else 0], dtype=torch.int32,
-                            device=torch.device("cuda", torch.cuda.current_device()))
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=cls.group)
-        return bool(flag.item())
+    def agree(cls, ok, log):
+        # Every rank must take the same route (the parts run one collective each), and only
+        # the leaf ranges that received samples on SOME rank need reducing: sum the ranks'
+        # "cannot replay" flags and their per-bin sample counts in one small all-reduce.
+        from .csrc import LOG_HIST, LOG_MAX_BINS
+        vec = torch.empty(1 + LOG_MAX_BINS, dtype=torch.int64, device=log.device)
+        vec[0] = 0 if ok else 1
+        vec[1:] = log[LOG_HIST:LOG_HIST + LOG_MAX_BINS]
+        dist.all_reduce(vec, op=dist.ReduceOp.SUM, group=cls.group)
+        host = vec.cpu()
+        n_bins = int(log[3].item())
+        if int(host[0]) != 0:
+            return False
+        used = torch.nonzero(host[1:1 + n_bins]).flatten()
+        if used.numel() == 0:
+            return (0, 0)
+        return (int(used[0]), int(used[-1]) + 1)
 
     @classmethod
     def on_done(cls):
@@ -69,7 +80,9 @@ class _Overlap:
 
 
 def overlap_grad_allreduce(n_parts=8, group=None, reserve_sms=16):
-    """Overlap the all-reduce of ``data.grad`` with its computation.
+    """Overlap the all-reduce of ``data.grad`` with its computation, and reduce only the
+    leaf ranges that received samples on some rank (the rest of the gradient is zero
+    everywhere).  ``n_parts=1`` keeps the second saving without the overlap.
 
     The replay backward of the renderer produces the gradient leaf range by leaf range;
     with this switched on, the rows of a finished range are all-reduced (asynchronously, on

@@ -201,7 +201,7 @@ def test_replay_in_parts_equals_replay_in_one_go(name, image, cuda_device):
             seen.append((rows.data_ptr(), rows.numel(), float(rows.abs().sum())))
 
         parts = csrc.volume_render_backward_replay_parts(spec, src, opt, gout, out, log, 5,
-                                                         on_part, agree=lambda ok: ok,
+                                                         on_part, agree=lambda ok, log: ok,
                                                          reserve_sms=8, image=image)
         assert parts is not None and len(seen) == 5
         filled = [x for x in seen if x[1] > 0]             # an empty view has no address
@@ -212,6 +212,21 @@ def test_replay_in_parts_equals_replay_in_one_go(name, image, cuda_device):
         assert any(a > 0 for _, _, a in seen)
         scale = whole.abs().max().item()
         assert (parts - whole).abs().max().item() <= 1e-5 * scale
+
+        # the same over the span of bins that hold samples only (what a multi-GPU caller
+        # reduces): the rows outside stay zero, as they are in the one-shot gradient
+        def used_span(ok, log_words):
+            n_bins = int(log_words[3].item())
+            hist = log_words[csrc.LOG_HIST:csrc.LOG_HIST + n_bins].cpu()
+            used = torch.nonzero(hist).flatten()
+            return (int(used[0]), int(used[-1]) + 1)
+
+        del seen[:]
+        span = csrc.volume_render_backward_replay_parts(spec, src, opt, gout, out, log, 3,
+                                                        on_part, agree=used_span, image=image)
+        assert span is not None and len(seen) == 3
+        assert sum(n for _, n, _ in seen) <= parts.numel()
+        assert (span - whole).abs().max().item() <= 1e-5 * scale
         csrc.check_device_status()
     finally:
         case["tree"].to("cpu")
