@@ -102,7 +102,7 @@ def overlap_grad_allreduce(n_parts=8, group=None, reserve_sms=16):
     _Overlap.works = []
     _Overlap.reduced = False
     render.GRAD_PARTS = (int(n_parts), _Overlap.on_part, _Overlap.on_done, _Overlap.agree,
-                         int(reserve_sms))
+                         int(reserve_sms) if n_parts > 1 else 0)   # one part: nothing overlaps
 
 
 def allreduce_grad(tree, group=None, async_op=False):
