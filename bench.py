@@ -52,7 +52,7 @@ def parse():
     p.add_argument("--overlap-parts", type=int, default=-1,
                    help="N > 1: leaf ranges whose all-reduce overlaps the backward (0 = one "
                         "all-reduce of the whole gradient after the backward; 1 = one all-reduce "
-                        "of the leaf ranges that hold samples; -1 = 8 up to 4 GPUs, else 1)")
+                        "of the leaf ranges that hold samples; -1 = 8 up to 4 GPUs, else 0)")
     return p.parse_args()
 
 
@@ -192,7 +192,7 @@ def run_b200(a):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
         if a.overlap_parts < 0:
-            a.overlap_parts = 8 if world <= 4 else 1
+            a.overlap_parts = 8 if world <= 4 else 0
         D.overlap_grad_allreduce(a.overlap_parts)
 
     tree_cpu, rays_cpu, targets_cpu = W.config4(Q=a.rays, init_refine=a.init_refine,
