@@ -139,6 +139,26 @@ int svoxb_volume_render_image_backward(const svoxb_tree* tree, const svoxb_camer
                                        const float* grad_output, const float* fwd_out,
                                        float* grad_data_out, int zero_first, void* stream);
 
+/* Rendering many views of a tree that does not change in between (no
+ * counterpart in the reference).  The forward render needs an index of the
+ * tree (density-annotated child array, leaf table, bricks) that depends on
+ * child, data's densities, opt->sigma_thresh and opt->density_softplus; the
+ * plain entry points rebuild it on every call because data may have changed.
+ * Here the caller keeps it: svoxb_render_scratch_words int32 words of device
+ * memory, filled once by svoxb_render_scratch_build and passed to any number
+ * of svoxb_volume_render[_image]_prepared calls -- valid until the tree, those
+ * two options or svoxb_tune change.  Octrees with SH colour in three channels
+ * only (else SVOXB_ERR_FORMAT: use the plain entry points). */
+int64_t svoxb_render_scratch_words(const svoxb_tree* tree);
+int svoxb_render_scratch_build(const svoxb_tree* tree, const svoxb_render_options* opt,
+                               int32_t* scratch, void* stream);
+int svoxb_volume_render_prepared(const svoxb_tree* tree, const svoxb_rays* rays,
+                                 const svoxb_render_options* opt, const int32_t* scratch,
+                                 float* out, void* stream);
+int svoxb_volume_render_image_prepared(const svoxb_tree* tree, const svoxb_camera* cam,
+                                       const svoxb_render_options* opt, const int32_t* scratch,
+                                       float* out, void* stream);
+
 /* Logged forward + replay backward (no counterpart in the reference; the
  * pair computes what volume_render followed by volume_render_backward
  * computes, svox/csrc/rt_kernel.cu:1019-1083).  The logged forward also

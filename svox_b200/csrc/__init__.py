@@ -270,8 +270,32 @@ def query_vertical_backward(tree, indices, grad_output):
     return grad
 
 
-def volume_render(tree, rays, opt):
-    """-> (Q, out_dim); svox/csrc/rt_kernel.cu:1019-1036."""
+def render_scratch(tree, opt):
+    """The forward render's index of the tree (density-annotated child array, leaf table,
+    bricks) as an int32 tensor, for ``volume_render[_image](..., prepared=...)``: valid until
+    the tree, ``opt.sigma_thresh`` or ``opt.density_softplus`` change.  None if this tree /
+    format renders through kernels that keep no such index."""
+    lib = library()
+    ct = _pack_tree(tree)
+    co = opt._pack()
+    lib.svoxb_render_scratch_words.restype = C.c_int64
+    words = lib.svoxb_render_scratch_words(C.byref(ct))
+    if words <= 0:
+        return None
+    with torch.cuda.device(tree.data.device):
+        scratch = torch.empty(words, dtype=torch.int32, device=tree.data.device)
+        st = lib.svoxb_render_scratch_build(C.byref(ct), C.byref(co),
+                                            C.c_void_p(scratch.data_ptr()), _stream())
+    if st in (3, 4, ERR_TOO_LARGE):      # format / option / size the queue kernels do not take
+        return None
+    if st:
+        _raise(st, "render_scratch_build")
+    return scratch
+
+
+def volume_render(tree, rays, opt, prepared=None):
+    """-> (Q, out_dim); svox/csrc/rt_kernel.cu:1019-1036.  ``prepared``: a tensor from
+    ``render_scratch`` for the same tree and options (skips the per-call index build)."""
     lib = library()
     ct = _pack_tree(tree)
     cr = _pack_rays(rays, tree.data.device)
@@ -280,15 +304,21 @@ def volume_render(tree, rays, opt):
         out = torch.empty((cr.Q, _out_dim(opt, ct.K)), dtype=torch.float32,
                           device=tree.data.device)
         with _timed("volume_render"):
-            st = lib.svoxb_volume_render(C.byref(ct), C.byref(cr), C.byref(co),
-                                         C.c_void_p(out.data_ptr()), _stream())
+            if prepared is not None:
+                st = lib.svoxb_volume_render_prepared(
+                    C.byref(ct), C.byref(cr), C.byref(co), C.c_void_p(prepared.data_ptr()),
+                    C.c_void_p(out.data_ptr()), _stream())
+            else:
+                st = lib.svoxb_volume_render(C.byref(ct), C.byref(cr), C.byref(co),
+                                             C.c_void_p(out.data_ptr()), _stream())
     if st:
         _raise(st, "volume_render")
     return out
 
 
-def volume_render_image(tree, cam, opt):
-    """-> (height, width, out_dim); svox/csrc/rt_kernel.cu:1038-1057."""
+def volume_render_image(tree, cam, opt, prepared=None):
+    """-> (height, width, out_dim); svox/csrc/rt_kernel.cu:1038-1057.  ``prepared`` as for
+    ``volume_render``."""
     lib = library()
     ct = _pack_tree(tree)
     cc = _pack_camera(cam, tree.data.device)
@@ -296,8 +326,13 @@ def volume_render_image(tree, cam, opt):
     with torch.cuda.device(tree.data.device):
         out = torch.empty((cc.height, cc.width, _out_dim(opt, ct.K)), dtype=torch.float32,
                           device=tree.data.device)
-        st = lib.svoxb_volume_render_image(C.byref(ct), C.byref(cc), C.byref(co),
-                                           C.c_void_p(out.data_ptr()), _stream())
+        if prepared is not None:
+            st = lib.svoxb_volume_render_image_prepared(
+                C.byref(ct), C.byref(cc), C.byref(co), C.c_void_p(prepared.data_ptr()),
+                C.c_void_p(out.data_ptr()), _stream())
+        else:
+            st = lib.svoxb_volume_render_image(C.byref(ct), C.byref(cc), C.byref(co),
+                                               C.c_void_p(out.data_ptr()), _stream())
     if st:
         _raise(st, "volume_render_image")
     return out

@@ -27,6 +27,8 @@ struct RenderCall {
     // item log (logged forward / replay backward)
     int32_t* log = nullptr;
     int64_t log_capacity = 0;
+    // forward with a scratch built earlier by svoxb_render_scratch_build (else per call)
+    int32_t* prepared = nullptr;
 };
 
 static int out_dim_of(const svoxb_tree* t, const svoxb_render_options& o) {
@@ -335,59 +337,90 @@ struct QueueScratch {
     int32_t* table = nullptr;
     int32_t* bricks = nullptr;
     int level = 0;
+    bool owned = false;
     cudaStream_t stream = nullptr;
-    int build(const svoxb_tree* t, float thresh, int softplus, int max_level, cudaStream_t s) {
-        stream = s;
-        const int64_t n = t->M * 8;
-        level = auto_top_level(t->M, max_level);
-        const int64_t cells = level > 0 ? ((int64_t)1 << (3 * level)) : 0;
+
+    // annotated | table | brick counter (8 words) | brick roots | bricks
+    struct Layout {
+        int64_t n, cells, cap;
+        int level;
+        size_t head, words;
+    };
+    static Layout layout(const svoxb_tree* t, int max_level) {
+        Layout l{};
+        l.n = t->M * 8;
+        l.level = auto_top_level(t->M, max_level);
+        l.cells = l.level > 0 ? ((int64_t)1 << (3 * l.level)) : 0;
         // bricks: one per table cell that holds a node, while the budget lasts
-        int64_t cap = 0;
-        if (level > 0 && g_tuning.render_bricks && t->M < kBrickMaxNodes &&
-            level + kBrickLevels < kCoordBits) {
-            cap = cells < t->M ? cells : t->M;
-            if (cap > kMaxBricks) cap = kMaxBricks;
+        l.cap = 0;
+        if (l.level > 0 && g_tuning.render_bricks && t->M < kBrickMaxNodes &&
+            l.level + kBrickLevels < kCoordBits) {
+            l.cap = l.cells < t->M ? l.cells : t->M;
+            if (l.cap > kMaxBricks) l.cap = kMaxBricks;
         }
-        // annotated | table | brick counter (8 words) | brick roots | bricks
-        const size_t head = (size_t)(n + cells) + 8 + (size_t)((cap + 7) & ~(int64_t)7);
-        int st = keep_pool_cached();
-        if (st) return st;
-        SVOXB_CUDA(cudaMallocAsync((void**)&annotated,
-                                   head * sizeof(int32_t) +
-                                       (size_t)cap * kBrickWords * sizeof(int32_t), s));
-        table = annotated + n;
-        annotate_sigma_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(
-            t->child, t->data, t->K, n, thresh, softplus, annotated);
+        l.head = (size_t)(l.n + l.cells) + 8 + (size_t)((l.cap + 7) & ~(int64_t)7);
+        l.words = l.head + (size_t)l.cap * kBrickWords;
+        return l;
+    }
+    static int default_level() {
+        const int m = g_tuning.render_top_level >= 0 ? g_tuning.render_top_level : 6;
+        return m > 7 ? 7 : m;
+    }
+    void adopt(const Layout& l, int32_t* mem) {
+        annotated = mem;
+        table = mem + l.n;
+        bricks = l.cap > 0 ? mem + l.head : nullptr;
+        level = l.level;
+    }
+
+    // Fills `external` (layout(t, max_level).words int32) or a pool allocation of its own.
+    int build(const svoxb_tree* t, float thresh, int softplus, int max_level, cudaStream_t s,
+              int32_t* external = nullptr) {
+        stream = s;
+        const Layout l = layout(t, max_level);
+        int32_t* mem = external;
+        if (!mem) {
+            int st = keep_pool_cached();
+            if (st) return st;
+            SVOXB_CUDA(cudaMallocAsync((void**)&mem, l.words * sizeof(int32_t), s));
+            owned = true;
+        }
+        adopt(l, mem);
+        annotate_sigma_kernel<<<(unsigned)((l.n + 255) / 256), 256, 0, s>>>(
+            t->child, t->data, t->K, l.n, thresh, softplus, annotated);
         SVOXB_CUDA(cudaGetLastError());
         if (level > 0) {
-            build_leaf_table_kernel<<<(unsigned)((cells + 255) / 256), 256, 0, s>>>(
+            build_leaf_table_kernel<<<(unsigned)((l.cells + 255) / 256), 256, 0, s>>>(
                 annotated, t->M, level, table);
             SVOXB_CUDA(cudaGetLastError());
         }
-        if (cap > 0) {
-            int32_t* counter = table + cells;
+        if (l.cap > 0) {
+            int32_t* counter = table + l.cells;
             int32_t* roots = counter + 8;
-            bricks = annotated + head;
             SVOXB_CUDA(cudaMemsetAsync(counter, 0, sizeof(int32_t), s));
-            assign_bricks_kernel<<<(unsigned)((cells + 255) / 256), 256, 0, s>>>(
-                table, (int)cells, (int)cap, counter, roots);
-            fill_bricks_kernel<<<(unsigned)cap, kBrickCells, 0, s>>>(annotated, t->M, level,
-                                                                     (int)cap, counter, roots, bricks);
+            assign_bricks_kernel<<<(unsigned)((l.cells + 255) / 256), 256, 0, s>>>(
+                table, (int)l.cells, (int)l.cap, counter, roots);
+            fill_bricks_kernel<<<(unsigned)l.cap, kBrickCells, 0, s>>>(
+                annotated, t->M, level, (int)l.cap, counter, roots, bricks);
             SVOXB_CUDA(cudaGetLastError());
         }
         return SVOXB_OK;
     }
-    ~QueueScratch() { if (annotated) cudaFreeAsync(annotated, stream); }
+    ~QueueScratch() { if (owned && annotated) cudaFreeAsync(annotated, stream); }
 };
 
 template <int BD, class Source>
 static int launch_queue(const RenderCall& c, const Source& src) {
     constexpr int K = 3 * BD + 1;
     QueueScratch scratch;
-    const int max_level = g_tuning.render_top_level >= 0 ? g_tuning.render_top_level : 6;
-    int st = scratch.build(c.tree, c.backward ? 0.f : c.opt.sigma_thresh, c.opt.density_softplus,
-                           max_level > 7 ? 7 : max_level, c.stream);
-    if (st) return st;
+    if (c.prepared != nullptr && !c.backward) {
+        scratch.adopt(QueueScratch::layout(c.tree, QueueScratch::default_level()), c.prepared);
+    } else {
+        const int st = scratch.build(c.tree, c.backward ? 0.f : c.opt.sigma_thresh,
+                                     c.opt.density_softplus, QueueScratch::default_level(),
+                                     c.stream);
+        if (st) return st;
+    }
     TreeArgs tr = tree_args(c.tree);
     tr.child = scratch.annotated;
     const TopTable top{scratch.table, scratch.level, scratch.bricks};
@@ -567,6 +600,62 @@ int svoxb_volume_render_image(const svoxb_tree* tree, const svoxb_camera* cam,
     RenderCall c{tree, *opt, (int64_t)cam->width * cam->height};
     c.out = out;
     c.stream = (cudaStream_t)stream;
+    return render_dispatch(c, PixelRays{cam->c2w, cam->fx, cam->fy, cam->width, cam->height});
+}
+
+// Whether the queue kernels take this tree and these options (the prepared scratch is theirs).
+static int queue_eligible(const svoxb_tree* t, const svoxb_render_options* o) {
+    int st = validate_tree(t);
+    if (st) return st;
+    if ((st = validate_options(t, *o))) return st;
+    if (o->format != SVOXB_FORMAT_SH || t->K != 3 * o->basis_dim + 1 || t->N != 2)
+        return SVOXB_ERR_FORMAT;
+    if (t->K % 4 == 0 && (uintptr_t)t->data % 16 != 0) return SVOXB_ERR_FORMAT;
+    if (t->M >= (1LL << 28)) return SVOXB_ERR_TOO_LARGE;
+    if (g_tuning.render_algo != 2) return SVOXB_ERR_OPTION;
+    return SVOXB_OK;
+}
+
+int64_t svoxb_render_scratch_words(const svoxb_tree* tree) {
+    if (!tree || tree->M < 1 || tree->N != 2) return 0;
+    return (int64_t)QueueScratch::layout(tree, QueueScratch::default_level()).words;
+}
+
+int svoxb_render_scratch_build(const svoxb_tree* tree, const svoxb_render_options* opt,
+                               int32_t* scratch, void* stream) {
+    if (!tree || !opt || !scratch) return SVOXB_ERR_NULL;
+    int st = queue_eligible(tree, opt);
+    if (st) return st;
+    QueueScratch q;
+    return q.build(tree, opt->sigma_thresh, opt->density_softplus, QueueScratch::default_level(),
+                   (cudaStream_t)stream, scratch);
+}
+
+int svoxb_volume_render_prepared(const svoxb_tree* tree, const svoxb_rays* rays,
+                                 const svoxb_render_options* opt, const int32_t* scratch,
+                                 float* out, void* stream) {
+    if (!tree || !rays || !opt || !scratch) return SVOXB_ERR_NULL;
+    if (rays->Q > 0 && (!rays->origins || !rays->dirs || !rays->vdirs)) return SVOXB_ERR_NULL;
+    int st = queue_eligible(tree, opt);
+    if (st) return st;
+    RenderCall c{tree, *opt, rays->Q};
+    c.out = out;
+    c.stream = (cudaStream_t)stream;
+    c.prepared = const_cast<int32_t*>(scratch);
+    return render_dispatch(c, RayBatch{rays->origins, rays->dirs, rays->vdirs});
+}
+
+int svoxb_volume_render_image_prepared(const svoxb_tree* tree, const svoxb_camera* cam,
+                                       const svoxb_render_options* opt, const int32_t* scratch,
+                                       float* out, void* stream) {
+    if (!tree || !cam || !opt || !cam->c2w || !scratch) return SVOXB_ERR_NULL;
+    if (cam->width < 0 || cam->height < 0) return SVOXB_ERR_SHAPE;
+    int st = queue_eligible(tree, opt);
+    if (st) return st;
+    RenderCall c{tree, *opt, (int64_t)cam->width * cam->height};
+    c.out = out;
+    c.stream = (cudaStream_t)stream;
+    c.prepared = const_cast<int32_t*>(scratch);
     return render_dispatch(c, PixelRays{cam->c2w, cam->fx, cam->fy, cam->width, cam->height});
 }
 

@@ -75,21 +75,25 @@ class _VolumeRenderFunction(autograd.Function):
     the version of ``data`` so that the backward kernel can march once."""
 
     @staticmethod
-    def forward(ctx, data, tree, rays, opt):
+    def forward(ctx, data, tree, rays, opt, prepared=None, train=None):
         ctx.tree, ctx.rays, ctx.opt = tree, rays, opt
         ctx.log = None
-        if data.requires_grad and USE_ITEM_LOG and _C.log_eligible(tree, opt):
+        # `train`: whether a backward can follow (the caller knows the grad mode; in here it
+        # is always off, and requires_grad / needs_input_grad ignore torch.no_grad())
+        if train is None:
+            train = data.requires_grad
+        if train and USE_ITEM_LOG and _C.log_eligible(tree, opt):
             # training step: record the contributing samples for the backward pass
             out, ctx.log = _C.volume_render_logged(tree, rays, opt)
         else:
-            out = _C.volume_render(tree, rays, opt)
+            out = _C.volume_render(tree, rays, opt, prepared=prepared)
         ctx.fwd = (out, data._version) if _single_march_ok(opt) else None
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
         if not ctx.needs_input_grad[0]:
-            return None, None, None, None
+            return None, None, None, None, None, None
         fwd = None
         if ctx.fwd is not None and ctx.fwd[1] == ctx.tree.data._version:
             fwd = ctx.fwd[0]
@@ -98,29 +102,31 @@ class _VolumeRenderFunction(autograd.Function):
             grad = _replay(ctx.tree, ctx.rays, ctx.opt, grad_out, fwd, ctx.log, False)
             ctx.log = None
             if grad is not None:
-                return grad, None, None, None
+                return grad, None, None, None, None, None
         return _C.volume_render_backward(ctx.tree, ctx.rays, ctx.opt, grad_out,
-                                         fwd), None, None, None
+                                         fwd), None, None, None, None, None
 
 
 class _VolumeRenderImageFunction(autograd.Function):
     """svox/renderer.py:74-89."""
 
     @staticmethod
-    def forward(ctx, data, tree, cam, opt):
+    def forward(ctx, data, tree, cam, opt, prepared=None, train=None):
         ctx.tree, ctx.cam, ctx.opt = tree, cam, opt
         ctx.log = None
-        if data.requires_grad and USE_ITEM_LOG and _C.log_eligible(tree, opt):
+        if train is None:
+            train = data.requires_grad
+        if train and USE_ITEM_LOG and _C.log_eligible(tree, opt):
             out, ctx.log = _C.volume_render_logged(tree, cam, opt, image=True)
         else:
-            out = _C.volume_render_image(tree, cam, opt)
+            out = _C.volume_render_image(tree, cam, opt, prepared=prepared)
         ctx.fwd = (out, data._version) if _single_march_ok(opt) else None
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
         if not ctx.needs_input_grad[0]:
-            return None, None, None, None
+            return None, None, None, None, None, None
         fwd = None
         if ctx.fwd is not None and ctx.fwd[1] == ctx.tree.data._version:
             fwd = ctx.fwd[0]
@@ -129,9 +135,21 @@ class _VolumeRenderImageFunction(autograd.Function):
             grad = _replay(ctx.tree, ctx.cam, ctx.opt, grad_out, fwd, ctx.log, True)
             ctx.log = None
             if grad is not None:
-                return grad, None, None, None
+                return grad, None, None, None, None, None
         return _C.volume_render_image_backward(ctx.tree, ctx.cam, ctx.opt, grad_out,
-                                               fwd), None, None, None
+                                               fwd), None, None, None, None, None
+
+
+class _FrozenTree:
+    def __init__(self, renderer):
+        self.renderer = renderer
+
+    def __enter__(self):
+        self.renderer._frozen = {}
+        return self.renderer
+
+    def __exit__(self, *exc):
+        self.renderer._frozen = None
 
 
 class VolumeRenderer(nn.Module):
@@ -154,6 +172,27 @@ class VolumeRenderer(nn.Module):
             ddim = tree.data_dim
             self._data_format = DataFormat("") if ddim == 4 else DataFormat(f"SH{(ddim - 1) // 3}")
         self.tree._weight_accum = None
+        self._frozen = None     # inside frozen_tree(): {(sigma_thresh, softplus): index tensor}
+
+    def frozen_tree(self):
+        """``with renderer.frozen_tree(): ...`` -- a promise that the tree (structure and
+        data) is not modified inside the block.  Forward renders in the block then build the
+        render index of the tree (annotated child array, leaf table, bricks) once instead of
+        on every call, which is what many views of one scene want.  No counterpart in the
+        reference; outside the block nothing is kept between calls, because ``tree.data`` can
+        be changed through ``.data`` without any version counter noticing."""
+        return _FrozenTree(self)
+
+    def _training(self):
+        return self.tree.data.requires_grad and torch.is_grad_enabled()
+
+    def _prepared(self, opt):
+        if self._frozen is None or self._training():
+            return None
+        key = (float(opt.sigma_thresh), bool(opt.density_softplus))
+        if key not in self._frozen:
+            self._frozen[key] = _C.render_scratch(self.tree._spec(), opt)
+        return self._frozen[key]
 
     @property
     def data_format(self):
@@ -168,8 +207,10 @@ class VolumeRenderer(nn.Module):
     def forward(self, rays: Rays, cuda=True, fast=False):
         """Render ``(B, 3)`` rays -> ``(B, rgb_dim)``.  Differentiable w.r.t. tree.data."""
         self._require_cuda(cuda)
+        opt = self._get_options(fast)
         return _VolumeRenderFunction.apply(self.tree.data, self.tree._spec(),
-                                           _rays_spec_from_rays(rays), self._get_options(fast))
+                                           _rays_spec_from_rays(rays), opt, self._prepared(opt),
+                                           self._training())
 
     def render_persp(self, c2w, width=800, height=800, fx=1111.111, fy=None, cuda=True,
                      fast=False):
@@ -178,9 +219,11 @@ class VolumeRenderer(nn.Module):
         if fy is None:
             fy = fx
         c2w = c2w.to(dtype=self.tree.data.dtype, device=self.tree.data.device).contiguous()
+        opt = self._get_options(fast)
         return _VolumeRenderImageFunction.apply(
             self.tree.data, self.tree._spec(),
-            _make_camera_spec(c2w, width, height, fx, fy), self._get_options(fast))
+            _make_camera_spec(c2w, width, height, fx, fy), opt, self._prepared(opt),
+            self._training())
 
     def se_grad(self, rays: Rays, colors):
         """Rendered colour, gradient and Gauss-Newton diagonal of the total squared error

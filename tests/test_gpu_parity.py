@@ -232,6 +232,39 @@ def test_replay_in_parts_equals_replay_in_one_go(name, image, cuda_device):
         case["tree"].to("cpu")
 
 
+@pytest.mark.parametrize("name", ["shell_sh9_rays", "shell_sh16_image", "opt_fast", "aniso_image",
+                                  "rgba_rays"])
+def test_frozen_tree_renders_are_identical(name, cuda_device):
+    # Inside renderer.frozen_tree() the render index is built once and reused; the renders
+    # are bit-identical to the ones that rebuild it per call (RGBA has no index: plain path).
+    case = CASES[name]()
+    tree = case["tree"].to(cuda_device)
+    try:
+        r = P._renderer(tree, case)
+
+        def render():
+            with torch.no_grad():
+                if case["kind"] == "rays":
+                    return r(svox.Rays(*[t.to(cuda_device) for t in case["rays"]]),
+                             fast=case["fast"])
+                cam = case["camera"]
+                return r.render_persp(cam["c2w"].to(cuda_device), width=cam["width"],
+                                      height=cam["height"], fx=cam["fx"], fy=cam["fy"],
+                                      fast=case["fast"])
+
+        plain = render()
+        with r.frozen_tree():
+            a = render()
+            b = render()
+            if name != "rgba_rays":
+                assert len(r._frozen) == 1 and next(iter(r._frozen.values())) is not None
+        assert r._frozen is None
+        assert torch.equal(a, plain) and torch.equal(b, plain)
+        csrc.check_device_status()
+    finally:
+        case["tree"].to("cpu")
+
+
 def test_item_log_overflow_falls_back(cuda_device):
     # A log that is too small must not be replayed: the backward marches instead.
     case = CASES["shell_sh9_rays"]()
