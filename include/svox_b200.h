@@ -146,8 +146,8 @@ int svoxb_volume_render_image_backward(const svoxb_tree* tree, const svoxb_camer
  * plain entry points rebuild it on every call because data may have changed.
  * Here the caller keeps it: svoxb_render_scratch_words int32 words of device
  * memory, filled once by svoxb_render_scratch_build and passed to any number
- * of svoxb_volume_render[_image]_prepared calls -- valid until the tree, those
- * two options or svoxb_tune change.  Octrees with SH colour in three channels
+ * of svoxb_volume_render[_image]_prepared calls -- valid until the tree or those
+ * two options change.  Octrees with SH colour in three channels
  * only (else SVOXB_ERR_FORMAT: use the plain entry points). */
 int64_t svoxb_render_scratch_words(const svoxb_tree* tree);
 int svoxb_render_scratch_build(const svoxb_tree* tree, const svoxb_render_options* opt,
@@ -297,20 +297,6 @@ const char* svoxb_strerror(int status);
 /* Text of the last CUDA runtime error seen by this library on the calling
  * thread (empty string if none). */
 const char* svoxb_last_cuda_error(void);
-
-/* Experiment hook (no counterpart in the reference).  Keys:
- *   0  threads per block of the render kernels (0 = automatic: 640)
- *   1  cap on the level of the render leaf table (-1 = automatic: 6)
- *   2  cap on the level of the query jump table (-1 = automatic: 7)
- *   3  render algorithm (2 = item queue, the default; 0 = warp-cooperative;
- *      1 = one thread per ray)
- *   5  MB of gradient one bin of the replay backward spans (default 16)
- *   6  L2 hint bits of the replay scatter (1 = packets evict-first,
- *      2 = gradient evict-last; default 3)
- *   7  bricks below the render leaf table (1 = on, the default; 0 = off)
- *   8  lanes of a warp that must be idle before new rays are loaded (default 4)
- * Unknown keys return SVOXB_ERR_OPTION. */
-int svoxb_tune(int key, int value);
 
 /* Library version, "major.minor.patch". */
 const char* svoxb_version(void);

@@ -7,6 +7,9 @@ generation) and never by the product path.  Nothing is copied from the
 reference tree; if the tree is absent this is a no-op and the prebuilt
 library (if any) is used as is.
 
+The reference checkout is looked for at ``$SVOX_REFERENCE_ROOT``, else in a
+directory ``reference`` beside this repository.
+
 Usage: python oracle/build_ref.py [reference_root]
 """
 import os
@@ -24,8 +27,14 @@ def built_path():
     return None
 
 
-def build(ref_root="/root/reference", verbose=False):
-    csrc = os.path.join(ref_root, "svox", "csrc")
+def reference_root():
+    """Where the reference checkout lies (it need not exist)."""
+    return os.environ.get("SVOX_REFERENCE_ROOT") or os.path.join(
+        os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build(ref_root=None, verbose=False):
+    csrc = os.path.join(ref_root or reference_root(), "svox", "csrc")
     if not os.path.isdir(csrc):
         return built_path()
     os.makedirs(OUT, exist_ok=True)
@@ -57,5 +66,5 @@ def load_module():
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else reference_root()
     print(build(root, verbose=True))

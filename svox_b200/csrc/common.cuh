@@ -142,16 +142,14 @@ struct TopScratch {
     ~TopScratch() { if (cells) cudaFreeAsync(cells, stream); }
 };
 
-// Tuning knobs (svoxb_tune).
+constexpr int kRefillBatch = 4;  // queue kernels: lanes that must be idle before rays are loaded
+constexpr int kReplayHints = 3;  // replay scatter: 1 = packets evict-first, 2 = gradient evict-last
+
+// The two switches the tests flip to show that an index or a bin size changes no result
+// (svoxb_test_knob).
 struct Tuning {
-    int render_block = 0;     // 0 = automatic
-    int render_top_level = -1;  // -1 = automatic
-    int query_top_level = -1;
-    int render_algo = 2;        // 2 = item queue, 0 = warp-cooperative, 1 = one thread per ray
-    int replay_bin_mb = 16;     // gradient bytes one replay bin spans
-    int refill_batch = 4;       // queue kernels: lanes that must be idle before rays are loaded
-    int render_bricks = 1;      // queue kernels: bricks below the leaf table
-    int replay_flags = 3;       // replay scatter: 1 = packets evict-first, 2 = gradient evict-last
+    int replay_bin_mb = 16;  // gradient bytes one replay bin spans
+    int render_bricks = 1;   // queue kernels: bricks below the leaf table
 };
 extern Tuning g_tuning;
 

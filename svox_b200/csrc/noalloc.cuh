@@ -59,12 +59,9 @@ static int launch_noalloc(const RenderCall& c, const RayBatch& src, int32_t* scr
         SVOXB_CUDA(cudaGetLastError());
     }
     const TopTable top{table, level};
-    const size_t top_bytes = 0;
     TreeArgs tr = tree_args(t);
     tr.child = annotated;
-    if constexpr (BD <= 9) return launch_queue_block<BD, 640>(c, src, tr, top, top_bytes);
-    else if constexpr (BD <= 16) return launch_queue_block<BD, 512>(c, src, tr, top, top_bytes);
-    else return launch_queue_block<BD, 256>(c, src, tr, top, top_bytes);
+    return launch_queue_fitted<BD>(c, src, tr, top);
 }
 
 }  // namespace svoxb

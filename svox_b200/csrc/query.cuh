@@ -134,8 +134,7 @@ static int launch_query(int mode, const svoxb_tree* tree, const float* indices, 
     if (!indices) return SVOXB_ERR_NULL;
     if ((Q + kQueryBlock - 1) / kQueryBlock > 0x7fffffffLL) return SVOXB_ERR_TOO_LARGE;
     TopScratch top;
-    const int max_level = g_tuning.query_top_level >= 0 ? g_tuning.query_top_level : 7;
-    int st = top.build(tree, max_level > 7 ? 7 : max_level, stream);
+    int st = top.build(tree, 7, stream);
     if (st) return st;
     const TopTable tt{top.cells, top.level};
     const unsigned grid = (unsigned)((Q + kQueryBlock - 1) / kQueryBlock);

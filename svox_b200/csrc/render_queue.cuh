@@ -36,25 +36,31 @@
 #pragma once
 
 #include "render.cuh"
-#include "render_coop.cuh"
 
 namespace svoxb {
 
-#ifdef SVOXB_PROFILE
-__device__ unsigned long long g_prof[16];
-// Per-warp cycle accounting of the loop phases (debug builds only).
-#define PROF_T0() unsigned long long prof_acc[16] = {0}; long long prof_t = clock64()
-#define PROF_ADD(i) do { long long n_ = clock64(); prof_acc[i] += (unsigned long long)(n_ - prof_t); prof_t = n_; } while (0)
-#define PROF_CNT(i, v) do { prof_acc[i] += (unsigned long long)(v); } while (0)
-#define PROF_END() do { if (lane == 0) { for (int i_ = 0; i_ < 16; ++i_) atomicAdd(&g_prof[i_], prof_acc[i_]); } } while (0)
-#else
-#define PROF_T0()
-#define PROF_ADD(i)
-#define PROF_CNT(i, v)
-#define PROF_END()
-#endif
-
+constexpr int kModeForward = 0;
+constexpr int kModeBackward = 1;
 constexpr int kModeForwardLogged = 2;  // forward that also records its items for the backward
+
+// Mark in the annotated child array: a leaf that passes the density test but
+// whose density cannot ride in the entry itself.
+constexpr int32_t kOccupied = INT32_MIN;
+
+// How the lanes of a warp move K-float records between global memory and the
+// per-item staging rows in shared memory.
+template <int K>
+struct RecordShape {
+    static constexpr bool VEC = (K % 4 == 0);            // 16-byte words possible
+    static constexpr int WORDS = VEC ? K / 4 : K;         // words per record
+    static constexpr int GROUP = WORDS <= 1 ? 1 : WORDS <= 2 ? 2 : WORDS <= 4 ? 4
+                                 : WORDS <= 8 ? 8 : WORDS <= 16 ? 16 : 32;  // lanes per item
+    static constexpr int IPP = 32 / GROUP;                // items per pass
+    static constexpr int WPL = (WORDS + GROUP - 1) / GROUP;  // words per lane per item
+    // staging row stride in floats: 16-byte rows for vector access, odd
+    // otherwise (both conflict-free for the owner's reads)
+    static constexpr int STRIDE = VEC ? K : (K | 1);
+};
 
 // Item log: what a logged forward leaves behind so that the backward pass can
 // replay the contributing samples without marching again and without reading
@@ -256,7 +262,7 @@ template <int K, int MODE>
 struct alignas(16) WarpQueue {
     static constexpr bool BWD = MODE == kModeBackward;
     static constexpr bool LOG = MODE == kModeForwardLogged;
-    using Shape = CoopShape<K>;
+    using Shape = RecordShape<K>;
     static constexpr int CAP = 96;  // a batch in flight (32) + items being collected (< 64)
     static constexpr int BD = (K - 1) / 3;
     static constexpr int RAYW = (BD + (BWD ? 3 : 0)) | 1;  // odd stride: no bank conflicts
@@ -289,7 +295,7 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
     constexpr bool BWD = MODE == kModeBackward;
     constexpr bool LOG = MODE == kModeForwardLogged;
     using WQ = WarpQueue<K, MODE>;
-    using Shape = CoopShape<K>;
+    using Shape = RecordShape<K>;
     static_assert(Shape::STRIDE >= 3, "result words live in the staging row");
     extern __shared__ __align__(16) unsigned char s_raw[];
     __shared__ unsigned s_next;
@@ -614,7 +620,6 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
         }
     };
 
-    PROF_T0();
     for (;;) {
         bool force = false;
         // ---- lanes that are not marching: finish, refill, termination ---------------------
@@ -694,8 +699,6 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                 force = true;
             }
         }
-        PROF_ADD(0);
-        PROF_CNT(8, 1);
 
         // ---- G step: every lane consumes the entry it requested one iteration ago -----------
         // An inner node moves the cursor one level down; a leaf is sampled and the cursor
@@ -830,7 +833,6 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
             }
             if (go) request_entry();
         }
-        PROF_ADD(1);
 
         // ---- push items --------------------------------------------------------------
         const unsigned pushed = __ballot_sync(0xffffffffu, item);
@@ -850,7 +852,6 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
         }
         qn += __popc(pushed);
         const int collected = qn - (inflight ? 32 : 0);
-        PROF_ADD(2);
         if (collected < 32 && !(force && qn > 0)) continue;
         __syncwarp();
 
@@ -858,12 +859,8 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
         if (inflight) {
             cp_async_wait_all();
             __syncwarp();
-            PROF_ADD(3);
-            PROF_CNT(10, 1);
-            PROF_CNT(11, 32);
             evaluate(32);
             inflight = false;
-            PROF_ADD(4);
         }
         if (force) {
             // a lane waits for its items (or nobody marches any more): flush everything now
@@ -872,17 +869,12 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                 request(nb);
                 cp_async_wait_all();
                 __syncwarp();
-                PROF_ADD(5);
-                PROF_CNT(12, 1);
-                PROF_CNT(13, nb);
                 evaluate(nb);
-                PROF_ADD(6);
             }
         } else if (qn >= 32) {
             request(32);
             asm volatile("cp.async.commit_group;" ::: "memory");
             inflight = true;
-            PROF_ADD(7);
         }
     }
     if (LOG) {
@@ -893,7 +885,6 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
         for (int i = threadIdx.x; i < kMaxBins; i += BLOCK)
             if (s_hist[i] != 0) atomicAdd(log + kLogHeads + i, s_hist[i]);
     }
-    PROF_END();
 }
 
 }  // namespace svoxb

@@ -214,7 +214,7 @@ __device__ __forceinline__ int4 ld_stream16(const int4* a, uint64_t pol) {
 
 template <int K>
 struct alignas(16) ScatterSmem {
-    using Shape = CoopShape<K>;
+    using Shape = RecordShape<K>;
     uint32_t slot[32];
     alignas(16) float rows[32 * Shape::STRIDE + 4];
 };
@@ -225,7 +225,7 @@ replay_scatter_kernel(int64_t n_slots, svoxb_render_options opt, float* __restri
                       const int32_t* __restrict__ log, ReplayBins b, int flags, int part,
                       int n_parts, int bin_begin, int bin_end) {
     constexpr int K = 3 * BD + 1;
-    using Shape = CoopShape<K>;
+    using Shape = RecordShape<K>;
     using SM = ScatterSmem<K>;
     extern __shared__ __align__(16) unsigned char s_raw[];
     const int lane = threadIdx.x & 31;

@@ -5,7 +5,6 @@
 #include "host.cuh"
 #include "query.cuh"
 #include "render.cuh"
-#include "render_coop.cuh"
 #include "render_queue.cuh"
 #include "render_replay.cuh"
 #include <new>
@@ -96,57 +95,6 @@ static int launch_sh(const RenderCall& c, const Source& src, const TopTable& top
     return SVOXB_OK;
 }
 
-// Scratch copy of the child array with the density test folded into the leaf
-// entries (render_coop.cuh); lives until the stream reaches the free.
-struct AnnotScratch {
-    int32_t* child = nullptr;
-    cudaStream_t stream = nullptr;
-    int build(const svoxb_tree* t, float thresh, int softplus, cudaStream_t s) {
-        stream = s;
-        const int64_t n = t->M * 8;
-        int st = keep_pool_cached();
-        if (st) return st;
-        SVOXB_CUDA(cudaMallocAsync((void**)&child, (size_t)n * sizeof(int32_t), s));
-        annotate_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(t->child, t->data, t->K, n,
-                                                                   thresh, softplus, child);
-        SVOXB_CUDA(cudaGetLastError());
-        return SVOXB_OK;
-    }
-    ~AnnotScratch() { if (child) cudaFreeAsync(child, stream); }
-};
-
-template <int BD, int BLOCK, class Source>
-static int launch_coop(const RenderCall& c, const Source& src, const TopTable& top, bool in_smem,
-                       size_t top_bytes) {
-    constexpr int K = 3 * BD + 1;
-    using Shape = CoopShape<K>;
-    AnnotScratch annot;
-    int st = annot.build(c.tree, c.backward ? 0.f : c.opt.sigma_thresh, c.opt.density_softplus,
-                         c.stream);
-    if (st) return st;
-    TreeArgs tr = tree_args(c.tree);
-    tr.child = annot.child;
-    const size_t smem = top_bytes + (size_t)(BLOCK / 32) * (Shape::STAGE_FLOATS * 4 + 32);
-    const int64_t n_gran = (c.Q + 31) / 32;
-    unsigned grid = 1;
-    if (!c.backward) {
-        auto k = render_coop_kernel<BD, BLOCK, kModeForward, Source>;
-        if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
-        k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, in_smem, (int)top_bytes, c.Q,
-                                          c.out, nullptr, nullptr, nullptr);
-    } else {
-        const bool single = c.fwd_out != nullptr && c.opt.sigma_thresh == 0.f &&
-                            c.opt.stop_thresh == 0.f;
-        auto k = render_coop_kernel<BD, BLOCK, kModeBackward, Source>;
-        if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
-        k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, in_smem, (int)top_bytes, c.Q,
-                                          nullptr, c.grad_out, single ? c.fwd_out : nullptr,
-                                          c.grad_data);
-    }
-    SVOXB_CUDA(cudaGetLastError());
-    return SVOXB_OK;
-}
-
 // Queue kernels (render_queue.cuh).  The block size is the largest whose
 // per-warp queues fit in shared memory next to the jump table.
 constexpr size_t kMaxSmem = 227 * 1024;
@@ -174,13 +122,13 @@ static int launch_queue_block(const RenderCall& c, const Source& src, const Tree
         if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
         k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, (int)top_bytes, c.Q, c.out,
                                           nullptr, nullptr, nullptr, c.log, c.log_capacity,
-                                          replay_bin_shift(c.tree->M, K), g_tuning.refill_batch);
+                                          replay_bin_shift(c.tree->M, K), kRefillBatch);
     } else if (!c.backward) {
         const size_t smem = top_bytes + (size_t)(BLOCK / 32) * sizeof(WarpQueue<K, kModeForward>);
         auto k = render_queue_kernel<BD, BLOCK, kModeForward, Source>;
         if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
         k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, (int)top_bytes, c.Q, c.out,
-                                          nullptr, nullptr, nullptr, nullptr, 0, 0, g_tuning.refill_batch);
+                                          nullptr, nullptr, nullptr, nullptr, 0, 0, kRefillBatch);
     } else {
         const size_t smem = top_bytes + (size_t)(BLOCK / 32) * sizeof(WarpQueue<K, kModeBackward>);
         const bool single = c.fwd_out != nullptr && c.opt.sigma_thresh == 0.f &&
@@ -189,10 +137,34 @@ static int launch_queue_block(const RenderCall& c, const Source& src, const Tree
         if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
         k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, (int)top_bytes, c.Q, nullptr,
                                           c.grad_out, single ? c.fwd_out : nullptr, c.grad_data,
-                                          nullptr, 0, 0, g_tuning.refill_batch);
+                                          nullptr, 0, 0, kRefillBatch);
     }
     SVOXB_CUDA(cudaGetLastError());
     return SVOXB_OK;
+}
+
+// Picks the block size: 640 threads where the record allows it (the kernel needs ~90
+// registers; at 768 threads it spilled inside the loop), fewer while the per-warp queues
+// do not fit in shared memory.
+template <int BD, class Source>
+static int launch_queue_fitted(const RenderCall& c, const Source& src, const TreeArgs& tr,
+                               const TopTable& top) {
+    constexpr int K = 3 * BD + 1;
+    const size_t top_bytes = 0;  // the leaf table stays in global memory
+    const size_t per_warp = c.backward ? sizeof(WarpQueue<K, kModeBackward>)
+                            : c.log    ? sizeof(WarpQueue<K, kModeForwardLogged>)
+                                       : sizeof(WarpQueue<K, kModeForward>);
+    int want = 640;
+    // static shared memory: the ticket counter, and the bin histogram of the logged forward
+    const size_t fixed = 64 + (c.log ? (size_t)kMaxBins * sizeof(int) : 0);
+    while (want > 256 && top_bytes + (size_t)(want / 32) * per_warp + fixed > kMaxSmem) want -= 128;
+    if constexpr (BD <= 9) {
+        if (want >= 640) return launch_queue_block<BD, 640>(c, src, tr, top, top_bytes);
+    }
+    if constexpr (BD <= 16) {
+        if (want >= 512) return launch_queue_block<BD, 512>(c, src, tr, top, top_bytes);
+    }
+    return launch_queue_block<BD, 256>(c, src, tr, top, top_bytes);
 }
 
 // Replay backward (render_replay.cuh): prefix, pack, bin, then the scatter in one
@@ -294,7 +266,7 @@ static int replay_scatter_block(const ReplayJob& job, int part, float* grad, int
         if ((int64_t)grid > most) grid = (unsigned)(most > 1 ? most : 1);
     }
     k<<<grid, BLOCK, smem, stream>>>(job.n_slots, job.opt, grad, job.log, job.bins,
-                                    g_tuning.replay_flags, part, job.n_parts, job.bin_begin,
+                                    kReplayHints, part, job.n_parts, job.bin_begin,
                                     job.bin_end);
     const cudaError_t e = cudaGetLastError();
     return e != cudaSuccess ? set_cuda_error(e) : SVOXB_OK;
@@ -363,8 +335,7 @@ struct QueueScratch {
         return l;
     }
     static int default_level() {
-        const int m = g_tuning.render_top_level >= 0 ? g_tuning.render_top_level : 6;
-        return m > 7 ? 7 : m;
+        return 6;
     }
     void adopt(const Layout& l, int32_t* mem) {
         annotated = mem;
@@ -411,7 +382,6 @@ struct QueueScratch {
 
 template <int BD, class Source>
 static int launch_queue(const RenderCall& c, const Source& src) {
-    constexpr int K = 3 * BD + 1;
     QueueScratch scratch;
     if (c.prepared != nullptr && !c.backward) {
         scratch.adopt(QueueScratch::layout(c.tree, QueueScratch::default_level()), c.prepared);
@@ -424,24 +394,7 @@ static int launch_queue(const RenderCall& c, const Source& src) {
     TreeArgs tr = tree_args(c.tree);
     tr.child = scratch.annotated;
     const TopTable top{scratch.table, scratch.level, scratch.bricks};
-    const size_t top_bytes = 0;  // the leaf table stays in global memory
-    const size_t per_warp = c.backward ? sizeof(WarpQueue<K, kModeBackward>)
-                            : c.log    ? sizeof(WarpQueue<K, kModeForwardLogged>)
-                                       : sizeof(WarpQueue<K, kModeForward>);
-    // 640 threads: the kernel needs ~90 registers; at 768 (80 registers) it spills in the loop
-    int want = g_tuning.render_block > 0 ? g_tuning.render_block : 640;
-    // static shared memory: the ticket counter, and the bin histogram of the logged forward
-    const size_t fixed = 64 + (c.log ? (size_t)kMaxBins * sizeof(int) : 0);
-    while (want > 256 && top_bytes + (size_t)(want / 32) * per_warp + fixed > kMaxSmem) want -= 128;
-    if constexpr (BD <= 9) {
-        if (want >= 1024) return launch_queue_block<BD, 1024>(c, src, tr, top, top_bytes);
-        if (want >= 768) return launch_queue_block<BD, 768>(c, src, tr, top, top_bytes);
-        if (want >= 640) return launch_queue_block<BD, 640>(c, src, tr, top, top_bytes);
-    }
-    if constexpr (BD <= 16) {
-        if (want >= 512) return launch_queue_block<BD, 512>(c, src, tr, top, top_bytes);
-    }
-    return launch_queue_block<BD, 256>(c, src, tr, top, top_bytes);
+    return launch_queue_fitted<BD>(c, src, tr, top);
 }
 
 template <int BLOCK, class Source>
@@ -476,19 +429,6 @@ static int dispatch_layout(const RenderCall& c, const Source& src, const TopTabl
     const bool aligned = ((uintptr_t)t->data % 16 == 0) &&
                          (!c.backward || (uintptr_t)c.grad_data % 16 == 0);
     const bool vec = aligned && (t->K % 4 == 0);
-    // Warp-cooperative kernels: octrees whose records allow the chosen word
-    // size (any K with 32-bit words; 16-byte aligned buffers for K % 4 == 0).
-    if (g_tuning.render_algo == 0 && t->weight_accum == nullptr && t->N == 2 &&
-        (aligned || t->K % 4 != 0) &&
-        t->M * 8 < 0xffffffffLL) {
-        switch (c.opt.basis_dim) {
-            case 1: return launch_coop<1, BLOCK>(c, src, top, in_smem, smem);
-            case 4: return launch_coop<4, BLOCK>(c, src, top, in_smem, smem);
-            case 9: return launch_coop<9, BLOCK>(c, src, top, in_smem, smem);
-            case 16: return launch_coop<16, BLOCK>(c, src, top, in_smem, smem);
-            case 25: return launch_coop<25, BLOCK>(c, src, top, in_smem, smem);
-        }
-    }
     switch (c.opt.basis_dim) {
         case 1:
             return vec ? launch_sh<1, true, BLOCK>(c, src, top, in_smem, smem)
@@ -524,7 +464,7 @@ static int render_dispatch(const RenderCall& c, const Source& src) {
         const bool sh3 = c.opt.format == SVOXB_FORMAT_SH && t->K == 3 * c.opt.basis_dim + 1;
         const bool aligned = ((uintptr_t)t->data % 16 == 0) &&
                              (!c.backward || (uintptr_t)c.grad_data % 16 == 0);
-        if (g_tuning.render_algo == 2 && sh3 && t->N == 2 && (aligned || t->K % 4 != 0) &&
+        if (sh3 && t->N == 2 && (aligned || t->K % 4 != 0) &&
             t->M < (1LL << 28)) {
             switch (c.opt.basis_dim) {
                 case 1: return launch_queue<1>(c, src);
@@ -537,16 +477,12 @@ static int render_dispatch(const RenderCall& c, const Source& src) {
     }
 
     TopScratch scratch;
-    const int max_level = g_tuning.render_top_level >= 0 ? g_tuning.render_top_level : 5;
-    if ((st = scratch.build(c.tree, max_level > 7 ? 7 : max_level, c.stream))) return st;
+    if ((st = scratch.build(c.tree, 5, c.stream))) return st;
     const TopTable top{scratch.cells, scratch.level};
     // The table is staged in shared memory up to level 5 (128 KB).
     const bool in_smem = scratch.level > 0 && scratch.level <= 5;
     const size_t smem = in_smem ? ((size_t)4 << (3 * scratch.level)) : 0;
-    int block = g_tuning.render_block;
-    if (block == 0) block = (smem > 64 * 1024) ? 1024 : 256;
-    if (block >= 1024) return dispatch_layout<1024>(c, src, top, in_smem, smem);
-    if (block >= 512) return dispatch_layout<512>(c, src, top, in_smem, smem);
+    if (smem > 64 * 1024) return dispatch_layout<1024>(c, src, top, in_smem, smem);
     return dispatch_layout<256>(c, src, top, in_smem, smem);
 }
 
@@ -612,7 +548,6 @@ static int queue_eligible(const svoxb_tree* t, const svoxb_render_options* o) {
         return SVOXB_ERR_FORMAT;
     if (t->K % 4 == 0 && (uintptr_t)t->data % 16 != 0) return SVOXB_ERR_FORMAT;
     if (t->M >= (1LL << 28)) return SVOXB_ERR_TOO_LARGE;
-    if (g_tuning.render_algo != 2) return SVOXB_ERR_OPTION;
     return SVOXB_OK;
 }
 
@@ -1027,30 +962,11 @@ const char* svoxb_last_cuda_error(void) { return t_cuda_error; }
 
 const char* svoxb_version(void) { return "0.1.0"; }
 
-#ifdef SVOXB_PROFILE
-int svoxb_prof_read(unsigned long long* out16, int clear) {
-    SVOXB_CUDA(cudaDeviceSynchronize());
-    SVOXB_CUDA(cudaMemcpyFromSymbol(out16, g_prof, 16 * sizeof(unsigned long long)));
-    if (clear) {
-        unsigned long long z[16] = {0};
-        SVOXB_CUDA(cudaMemcpyToSymbol(g_prof, z, sizeof z));
-    }
-    return 0;
-}
-#endif
-
-// Tuning hook for experiments: key 0 = render block size (256 | 1024, 0 auto),
-// 1 = render jump-table level cap (-1 auto), 2 = query jump-table level cap,
-// 3 = render algorithm (2 item queue, 0 warp-cooperative, 1 one thread per ray).
-int svoxb_tune(int key, int value) {
+// Test hook (include/svox_b200_testing.h): key 5 = MB of gradient one replay bin spans,
+// key 7 = bricks below the render leaf table on / off.
+int svoxb_test_knob(int key, int value) {
     switch (key) {
-        case 0: g_tuning.render_block = value; return SVOXB_OK;
-        case 1: g_tuning.render_top_level = value; return SVOXB_OK;
-        case 2: g_tuning.query_top_level = value; return SVOXB_OK;
-        case 3: g_tuning.render_algo = value; return SVOXB_OK;
-        case 6: g_tuning.replay_flags = value; return SVOXB_OK;
-        case 7: g_tuning.render_bricks = value; return SVOXB_OK;
-        case 8: g_tuning.refill_batch = value; return SVOXB_OK;
+        case 7: g_tuning.render_bricks = value != 0; return SVOXB_OK;
         case 5:
             if (value < 1 || value > 1024) return SVOXB_ERR_OPTION;
             g_tuning.replay_bin_mb = value;

@@ -8,6 +8,8 @@ reference produced for them.  Each builder returns a dict:
     kind     "rays" | "image" | "query"
     rays     svox_b200.Rays            (kind == "rays")
     grad_out upstream gradient         (rays / image; None -> no backward)
+    mse_targets  instead of grad_out: colours (Q, 3); the loss is the mean squared error
+                 against them, so the upstream gradient is 2 (out - targets) / (3 Q)
     camera   dict(c2w, width, height, fx, fy)   (kind == "image")
     points   (Q, 3) world points, grad_out (Q, K)  (kind == "query")
     render   kwargs for VolumeRenderer(tree, **render)
@@ -36,13 +38,14 @@ def _small_shell(fmt, seed, init_refine=3, extra=3):
 
 
 def _base(tree, kind, **kw):
-    d = dict(tree=tree, kind=kind, render={}, attrs={}, fast=False, grad_out=None)
+    d = dict(tree=tree, kind=kind, render={}, attrs={}, fast=False, grad_out=None,
+             mse_targets=None)
     d.update(kw)
     return d
 
 
 def c1_rays():
-    """BASELINE config 1: 16^3-leaf SH4 tree, 4096 rays, backward of sum(rgb)."""
+    """Smoke configuration: 16^3-leaf SH4 tree, 4096 rays, backward of sum(rgb)."""
     tree, rays = W.config1()
     return _base(tree, "rays", rays=rays, grad_out=torch.ones(rays.origins.shape[0], 3))
 
@@ -56,7 +59,8 @@ def shell_sh9_rays():
 
 
 def c4_sample_rays():
-    """BASELINE config 4 (full tree), first 16384 rays of its 2^20, forward only."""
+    """The training-step benchmark scene (full 512^3 shell tree), first 16384 rays of its 2^20,
+    forward only."""
     tree, rays, _ = W.config4(Q=1 << 14)
     return _base(tree, "rays", rays=rays)
 
@@ -254,6 +258,17 @@ def deep_rays():
 
 # Cases without a reference fixture: checked against the oracle only.
 EXTRA_CASES = {f.__name__: f for f in [deep_rays]}
+
+def c4_full_rays():
+    """The training-step benchmark itself: the full 512^3 shell tree, all 2^20 rays, gradient
+    of the mean squared error against the seeded colour targets."""
+    tree, rays, targets = W.config4()
+    return _base(tree, "rays", rays=rays, mse_targets=targets)
+
+
+# Full-size cases: minutes of CPU work for the oracle, GPU tests only.
+FULL_CASES = {f.__name__: f for f in [c4_full_rays]}
+FULL_OUT_STRIDE = 16   # their fixtures keep the colours of every 16th ray
 
 # Cases whose fixtures are cheap enough to check on the CPU in the default test run.
 BIG = {"c4_sample_rays"}

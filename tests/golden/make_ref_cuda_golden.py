@@ -9,6 +9,13 @@ outputs as ``ref_cuda_<case>.npz``:
     ids            packed leaf ids (query cases)
     grad_*         digest of the gradient w.r.t. tree.data (see
                    tests/parity_util.grad_digest)
+    grad_val2      the same sampled elements from a SECOND run of the reference on the
+                   same inputs: its gradient is a sum of float atomics in whatever order
+                   the hardware took them, so two runs differ; the difference is the
+                   yardstick for "equal up to the order of the atomics"
+    spread_*       that run-to-run difference over the WHOLE gradient: largest
+                   |g1 - g2| / max|g1|, and largest |g1 - g2| / |g1| over elements
+                   with |g1| > 1e-6 max|g1|
 
 and, for WEIGHT_CASES, the reference's weight accumulator after one forward
 render as ``ref_cuda_weights_<case>.npz`` (non-zero entries only):
@@ -23,7 +30,11 @@ colours of tests/parity_util.se_grad_colors as ``ref_cuda_se_grad_<case>.npz``:
     grad_*         digest of the gradient
     hess_*         digest of the Gauss-Newton diagonal
 
+The full-size cases (FULL_CASES, "--full") keep the colours of every
+FULL_OUT_STRIDE-th ray only.
+
 Usage: python tests/golden/make_ref_cuda_golden.py [out_dir] [case ...]
+       python tests/golden/make_ref_cuda_golden.py [out_dir] --full
        python tests/golden/make_ref_cuda_golden.py [out_dir] --weights
        python tests/golden/make_ref_cuda_golden.py [out_dir] --se-grad
 """
@@ -36,7 +47,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(HERE))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 
-from golden.cases import CASES  # noqa: E402
+from golden.cases import CASES, FULL_CASES, FULL_OUT_STRIDE  # noqa: E402
 import parity_util as P  # noqa: E402
 
 
@@ -77,16 +88,27 @@ def main():
         return weights(out_dir)
     if "--se-grad" in sys.argv:
         return se_grad(out_dir)
-    names = sys.argv[2:] or list(CASES)
+    full = "--full" in sys.argv
+    table = FULL_CASES if full else CASES
+    names = [a for a in sys.argv[2:] if not a.startswith("--")] or list(table)
     for name in names:
-        case = CASES[name]()
+        case = table[name]()
         res = P.run_ref_cuda(case)
-        blob = {"out": res["out"]}
+        blob = {"out": res["out"][::FULL_OUT_STRIDE] if full else res["out"]}
         if res["ids"] is not None:
             blob["ids"] = res["ids"]
             blob["out"] = res["out"][:P.QUERY_ROWS_KEPT]
         if res["grad"] is not None:
             blob.update(P.grad_digest(res["grad"]))
+            g1 = res["grad"].reshape(-1)
+            g2 = P.run_ref_cuda(case)["grad"].reshape(-1)       # the same again
+            blob["grad_val2"] = g2[blob["grad_idx"]]
+            diff, top = np.abs(g1 - g2), np.abs(g1).max()
+            big = np.abs(g1) > 1e-6 * top
+            blob["spread_maxnorm"] = diff.max() / top
+            blob["spread_rel"] = (diff[big] / np.abs(g1[big])).max() if big.any() else 0.0
+            print(name, "run-to-run: max-norm %.3g, element-wise %.3g" %
+                  (blob["spread_maxnorm"], blob["spread_rel"]), flush=True)
         np.savez_compressed(os.path.join(out_dir, f"ref_cuda_{name}.npz"), **blob)
         print(name, "out", res["out"].shape, "grad", None if res["grad"] is None
               else res["grad"].shape, flush=True)

@@ -69,7 +69,9 @@ def _run_product(case, device, backward, single_march):
             out = r.render_persp(cam["c2w"].to(device), width=cam["width"], height=cam["height"],
                                  fx=cam["fx"], fy=cam["fy"], fast=case["fast"])
         res["out"] = out.detach().cpu().numpy()
-        if backward and case["grad_out"] is not None:
+        if backward and case["mse_targets"] is not None:
+            ((out - case["mse_targets"].to(device)) ** 2).mean().backward()
+        elif backward and case["grad_out"] is not None:
             if not single_march:
                 out.grad_fn.fwd = None  # force the reference's two-march backward
             out.backward(case["grad_out"].to(device))
@@ -91,6 +93,14 @@ def _oracle_options(case):
                        max_comp=po.max_comp, sigma_thresh=po.sigma_thresh,
                        stop_thresh=po.stop_thresh, density_softplus=po.density_softplus,
                        rgb_padding=po.rgb_padding)
+
+
+def _upstream(case, out):
+    """The gradient that reaches the render's output: given, or that of the MSE loss."""
+    if case["mse_targets"] is not None:
+        tg = case["mse_targets"].numpy()
+        return ((2.0 / out.size) * (out - tg)).astype(np.float32)
+    return None if case["grad_out"] is None else case["grad_out"].numpy()
 
 
 def run_oracle(case, backward=True, want_counts=False):
@@ -117,9 +127,10 @@ def run_oracle(case, backward=True, want_counts=False):
             res["out"], res["visits"], res["contrib"] = r
         else:
             res["out"] = r
-        if backward and case["grad_out"] is not None:
+        gout = _upstream(case, res["out"])
+        if backward and gout is not None:
             res["grad"], res["grad_abs"] = orc.volume_render_backward(
-                ot, o, d, v, opt, case["grad_out"].numpy(), want_abs=True)
+                ot, o, d, v, opt, gout, want_abs=True)
     else:
         cam = case["camera"]
         args = (cam["c2w"].numpy(), cam["fx"], cam["fy"], cam["width"], cam["height"], opt)
@@ -182,8 +193,11 @@ def run_ref_cuda(case, device="cuda:0", backward=True, weight_op=None):
             rs.origins, rs.dirs, rs.vdirs = [t.to(device).contiguous() for t in case["rays"]]
             out = ref.volume_render(spec, rs, opt)
             res["out"] = out.cpu().numpy()
-            if backward and case["grad_out"] is not None:
-                g = ref.volume_render_backward(spec, rs, opt, case["grad_out"].to(device))
+            gout = case["grad_out"]
+            if case["mse_targets"] is not None:
+                gout = (2.0 / out.numel()) * (out - case["mse_targets"].to(device))
+            if backward and gout is not None:
+                g = ref.volume_render_backward(spec, rs, opt, gout.to(device).contiguous())
                 res["grad"] = g.double().cpu().numpy()
         else:
             cam = case["camera"]

@@ -9,13 +9,21 @@ import pytest
 from svox_b200 import csrc
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-HEADER = os.path.join(ROOT, "include", "svox_b200.h")
+INCLUDE = os.path.join(ROOT, "include")
+HEADER = os.path.join(INCLUDE, "svox_b200.h")
+
+
+def _strip_comments(text):
+    return re.sub(r"/\*.*?\*/", "", text, flags=re.S)
 
 
 def _declared():
-    text = open(HEADER).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(svoxb_[a-z_0-9]+)\s*\(", text)))
+    names = set()
+    for fn in sorted(os.listdir(INCLUDE)):
+        if fn.endswith(".h"):
+            text = _strip_comments(open(os.path.join(INCLUDE, fn)).read())
+            names |= set(re.findall(r"\b(svoxb_[a-z_0-9]+)\s*\(", text))
+    return sorted(names)
 
 
 @pytest.fixture(scope="module")
@@ -67,4 +75,4 @@ def test_argument_errors_without_gpu(lib):
     o = opt._pack()
     # empty batch: nothing to do, no launch
     assert lib.svoxb_volume_render(C.byref(ok), C.byref(rays), C.byref(o), None, None) == 0
-    assert lib.svoxb_tune(99, 0) == 4
+    assert lib.svoxb_test_knob(99, 0) == 4

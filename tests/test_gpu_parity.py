@@ -107,17 +107,17 @@ def test_bricks_and_bin_size_do_not_change_results(name, cuda_device):
     orc = P.run_oracle(case)
     try:
         base = P.run_product(case, cuda_device)
-        assert lib.svoxb_tune(7, 0) == 0
+        assert lib.svoxb_test_knob(7, 0) == 0
         plain = P.run_product(case, cuda_device)
         assert np.array_equal(base["out"], plain["out"])
         assert P.grad_excess(base["grad"], plain["grad"], orc["grad_abs"], GRAD_TOL_REF) <= 2.5
-        assert lib.svoxb_tune(7, 1) == 0 and lib.svoxb_tune(5, 1) == 0
+        assert lib.svoxb_test_knob(7, 1) == 0 and lib.svoxb_test_knob(5, 1) == 0
         fine = P.run_product(case, cuda_device)
         assert np.array_equal(base["out"], fine["out"])
         assert P.grad_excess(base["grad"], fine["grad"], orc["grad_abs"], GRAD_TOL_REF) <= 2.5
     finally:
-        lib.svoxb_tune(7, 1)
-        lib.svoxb_tune(5, 16)
+        lib.svoxb_test_knob(7, 1)
+        lib.svoxb_test_knob(5, 16)
 
 
 @pytest.mark.parametrize("name", ["c1_rays", "shell_sh9_rays", "shell_sh16_image", "opt_fast",
@@ -440,7 +440,7 @@ def test_c_abi_direct_call(cuda_device):
 
 
 def test_full_size_properties_config2_slice(cuda_device):
-    """BASELINE config 2 at depth 7 (128^3 leaves) with 2^22 points: the
+    """The query benchmark one level coarser (128^3 leaves) with 2^22 points: the
     size-independent invariants of the query."""
     tree, pts = W.config2(Q=1 << 22, init_refine=6)
     tree = tree.to(cuda_device)
