@@ -168,15 +168,25 @@ int svoxb_volume_render_image_prepared(const svoxb_tree* tree, const svoxb_camer
  * words (one chunk = 32 samples).  The replay backward streams that log instead
  * of marching the rays and reading the leaf records again: it sorts the
  * samples by leaf range (scratch from the stream's memory pool, 32 bytes per
- * sample of `chunks_used` chunks; pass what svoxb_item_log_used reported, or 0
- * for capacity_chunks) and reduces the gradient range by range so that it
- * stays in L2.  If that scratch cannot be had it marches like
- * svoxb_volume_render_backward.  Only for octrees with SH colour in three channels,
- * sigma_thresh = stop_thresh = 0 and no density_softplus (else
- * SVOXB_ERR_FORMAT / SVOXB_ERR_OPTION).  If the log was too small
- * (svoxb_item_log_used reports more chunks than capacity_chunks) the log must
- * not be replayed: call svoxb_volume_render_backward instead.  `data` must
- * not change between the two calls. */
+ * sample) and reduces the gradient range by range so that it stays in L2.
+ * Only for octrees with SH colour in three channels, sigma_thresh =
+ * stop_thresh = 0 and no density_softplus (else SVOXB_ERR_FORMAT /
+ * SVOXB_ERR_OPTION).  `data` must not change between the two calls.
+ *
+ * A log that was too small must not be replayed.  `chunks_used` says who
+ * checks that:
+ *   0    nobody has read the count back.  The replay kernels read it on the
+ *        device and do nothing if the forward asked for more chunks than
+ *        `capacity_chunks`; a marching backward (as
+ *        svoxb_volume_render_backward) is enqueued behind them that does its
+ *        work only in that case.  No host synchronisation; the scratch is
+ *        sized for the whole log; the result is the gradient either way.
+ *   > 0  the caller read the count with svoxb_item_log_used (which
+ *        synchronises) and found it <= capacity_chunks: the scratch is sized
+ *        for that many chunks and no fallback is enqueued.  With a larger
+ *        count the caller must call svoxb_volume_render_backward instead.
+ * If the scratch cannot be had, the call marches like
+ * svoxb_volume_render_backward. */
 int64_t svoxb_item_log_words(int64_t capacity_chunks);
 int svoxb_volume_render_logged(const svoxb_tree* tree, const svoxb_rays* rays,
                                const svoxb_render_options* opt, float* out, int32_t* log,
@@ -201,6 +211,8 @@ int svoxb_volume_render_image_backward_replay(const svoxb_tree* tree, const svox
  * 1/2 sum (render - colour)^2, i.e. for every element of data the sum over rays
  * and channels of (d render / d element)^2.  Computed from the item log of a
  * logged forward like the replay backward (same restrictions, same scratch);
+ * chunks_used must be the count read with svoxb_item_log_used (there is no
+ * marching fallback for this result: 0 is refused with SVOXB_ERR_OPTION);
  * SVOXB_ERR_TOO_LARGE if the scratch cannot be had.  The first two results of
  * se_grad are the logged forward's output and the replay backward with
  * grad_output = render - colour. */
@@ -219,35 +231,38 @@ int svoxb_volume_render_image_hessdiag_replay(const svoxb_tree* tree, const svox
 /* The replay backward in steps, for callers that overlap the all-reduce of the
  * gradient with its computation (no counterpart in the reference).  _begin
  * sorts the logged samples by leaf range (arguments as for
- * svoxb_volume_render_backward_replay; SVOXB_ERR_TOO_LARGE if the scratch
- * cannot be had) and returns a job.  The leaf slots are cut into `n_parts`
- * (1..16) consecutive ranges (whole bins); svoxb_replay_part_range gives the slots
+ * svoxb_volume_render_backward_replay, chunks_used included;
+ * SVOXB_ERR_TOO_LARGE if the scratch cannot be had) and returns a job.
+ * grad_data_out is the gradient buffer, zeroed by the caller: with
+ * chunks_used = 0 the marching fallback for an overflowed log is enqueued here,
+ * BEFORE the parts, so that a part's rows are final after its scatter
+ * whichever of the two produced them -- every process of a data-parallel job
+ * can then issue the same collectives without agreeing on a route first.
+ * The leaf slots are cut into `n_parts` (1..16) consecutive ranges (whole
+ * bins, svoxb_replay_bin_shift); svoxb_replay_part_range gives the slots
  * [begin, end) of a part, i.e. rows [begin*K, end*K) of the flat gradient.
- * svoxb_replay_scatter adds the gradient of one part into grad_data_out (the
- * caller zeroes it first); with reserve_sms > 0 it leaves that many SMs free
- * for a collective kernel running beside it.  After a part's scatter the rows
- * of that part are final.  svoxb_replay_end releases the scratch on `stream`. */
+ * svoxb_replay_scatter adds the gradient of one part into grad_data_out; with
+ * reserve_sms > 0 it leaves that many SMs free for a collective kernel running
+ * beside it.  svoxb_replay_end releases the scratch on `stream`. */
 int svoxb_replay_begin(const svoxb_tree* tree, const svoxb_rays* rays,
                        const svoxb_render_options* opt, const float* grad_output,
                        const float* fwd_out, int32_t* log, int64_t capacity_chunks,
-                       int64_t chunks_used, int n_parts, void* stream, void** job);
+                       int64_t chunks_used, int n_parts, float* grad_data_out, void* stream,
+                       void** job);
 int svoxb_replay_image_begin(const svoxb_tree* tree, const svoxb_camera* cam,
                              const svoxb_render_options* opt, const float* grad_output,
                              const float* fwd_out, int32_t* log, int64_t capacity_chunks,
-                             int64_t chunks_used, int n_parts, void* stream, void** job);
+                             int64_t chunks_used, int n_parts, float* grad_data_out,
+                             void* stream, void** job);
 int svoxb_replay_part_range(const void* job, int part, int64_t* slot_begin, int64_t* slot_end);
-/* Optional, before the first scatter: let the parts tile only the bins
- * [bin_begin, bin_end) (bin = leaf slot >> svoxb_replay_bin_shift; the forward's
- * per-bin sample counts are words 32.. of the log).  Rows outside receive no
- * sample; a caller that knows them empty on every process need not reduce them. */
-int svoxb_replay_set_span(void* job, int bin_begin, int bin_end, void* stream);
 /* log2 of the leaf slots per bin for a tree of M nodes and K floats per record. */
 int svoxb_replay_bin_shift(int64_t M, int32_t K);
 int svoxb_replay_scatter(const void* job, int part, float* grad_data_out, int reserve_sms,
                          void* stream);
 int svoxb_replay_end(void* job, void* stream);
 
-/* Chunks the logged forward needed (synchronises `stream`). */
+/* Chunks the logged forward asked for (synchronises `stream`); more than the log's
+ * capacity means that it overflowed. */
 int svoxb_item_log_used(const int32_t* log, int64_t* chunks_used, void* stream);
 
 /* Forward ray render that allocates nothing (no counterpart in the

@@ -16,7 +16,8 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libsvox_b200.so")
+# SVOXB_LIBRARY: load another build of the library (e.g. one compiled with other flags)
+LIB_PATH = os.environ.get("SVOXB_LIBRARY") or os.path.join(_HERE, "libsvox_b200.so")
 
 FORMAT_RGBA, FORMAT_SH, FORMAT_SG, FORMAT_ASG = 0, 1, 2, 3
 ERR_TOO_LARGE = 8   # svoxb status: a size limit or the scratch allocation
@@ -57,6 +58,14 @@ class TreeSpec:
         self.offset = self.scaling = None
         self._weight_accum = None
         self._weight_accum_max = False
+        self._owner = None          # weak reference to the N3Tree this spec was packed from
+
+    def data_epoch(self):
+        """Counter of the owning tree's in-place edits of ``data`` that autograd's version
+        counter does not see (``tree[...] = v`` writes through ``data.data``); -1 without
+        an owner."""
+        tree = self._owner() if self._owner is not None else None
+        return tree._data_epoch if tree is not None else -1
 
 
 class RaysSpec:
@@ -341,11 +350,76 @@ def volume_render_image(tree, cam, opt, prepared=None):
 # ---------------------------------------------------------------------------
 # Logged forward / replay backward (training step without a second march)
 
-_items_per_ray = 48.0   # running estimate used to size the item log
-# Layout of the log's head (render_queue.cuh): word 2 = bin shift, word 3 = number of bins,
-# words LOG_HIST .. LOG_HIST + LOG_MAX_BINS = samples per bin of the last logged forward.
+# Layout of the log's head (render_queue.cuh): word 0 = chunks the forward asked for,
+# word 2 = bin shift, word 3 = number of bins, words LOG_HIST .. LOG_HIST + LOG_MAX_BINS =
+# samples per bin of the last logged forward.
 LOG_HIST, LOG_MAX_BINS = 32, 1024
 _LOG_SLACK_CHUNKS = 2 * 16384   # every warp of the forward takes log chunks 8 at a time
+_items_per_ray = 48.0           # running estimate used to size the item log
+_WATCH_SLOTS = 8
+
+
+class _LogWatch:
+    """Learns how large the item log has to be WITHOUT making the host wait for the device.
+
+    After a logged forward the number of chunks it asked for is copied to pinned host
+    memory, asynchronously; whenever the next log is sized, the counts that have arrived by
+    then adapt the per-ray estimate.  A log that was too small costs that one step a marching
+    backward (decided on the device, see ``volume_render_backward_replay``), never a wrong
+    gradient."""
+    slots = {}     # device -> [pinned int32 ring, next slot, pending [(slot, event, rays, cap)]]
+
+    @classmethod
+    def _state(cls, device):
+        st = cls.slots.get(device)
+        if st is None:
+            st = [torch.zeros(_WATCH_SLOTS, dtype=torch.int32).pin_memory(), 0, []]
+            cls.slots[device] = st
+        return st
+
+    @classmethod
+    def watch(cls, log, cap, n_rays):
+        st = cls._state(log.device)
+        pending = st[2]
+        if len(pending) >= _WATCH_SLOTS:           # nobody has polled for a while
+            cls.poll(log.device, wait=True)
+        slot = st[1]
+        st[1] = (slot + 1) % _WATCH_SLOTS
+        st[0][slot:slot + 1].copy_(log[:1], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        pending.append((slot, ev, n_rays, cap))
+
+    @classmethod
+    def poll(cls, device=None, wait=False):
+        """Fold the counts that have arrived into the estimate; ``wait`` blocks for all."""
+        global _items_per_ray
+        for dev, st in cls.slots.items():
+            if device is not None and dev != device:
+                continue
+            keep = []
+            for slot, ev, n_rays, cap in st[2]:
+                if wait:
+                    ev.synchronize()
+                elif not ev.query():
+                    keep.append((slot, ev, n_rays, cap))
+                    continue
+                used = int(st[0][slot])
+                cls.last_used, cls.last_cap = used, cap
+                if n_rays:
+                    # chunks are 32 items, partly filled ones included: keep 25 % head room
+                    need = max(8.0, 1.25 * 32.0 * used / n_rays)
+                    _items_per_ray = need if used > cap else max(need, 0.9 * _items_per_ray)
+            st[2] = keep
+        return _items_per_ray
+
+    last_used = last_cap = 0
+
+
+def log_estimate(wait=False):
+    """Current estimate of contributing samples per ray (what the next item log is sized by),
+    after folding in the counts of finished forwards; ``wait=True`` waits for all of them."""
+    return _LogWatch.poll(wait=wait)
 
 
 def log_eligible(tree, opt):
@@ -359,6 +433,7 @@ def log_eligible(tree, opt):
 def _log_alloc(n_rays, device):
     lib = library()
     lib.svoxb_item_log_words.restype = C.c_int64
+    _LogWatch.poll(device)
     cap = int(n_rays * _items_per_ray / 32) + _LOG_SLACK_CHUNKS
     words = lib.svoxb_item_log_words(C.c_int64(cap))
     return torch.empty(words, dtype=torch.int32, device=device), cap
@@ -387,13 +462,14 @@ def volume_render_logged(tree, rays_or_cam, opt, image=False):
         with _timed("volume_render"):
             st = fn(C.byref(ct), C.byref(cs), C.byref(co), C.c_void_p(out.data_ptr()),
                     C.c_void_p(log.data_ptr()), C.c_int64(cap), _stream())
-    if st:
-        _raise(st, "volume_render_logged")
+        if st:
+            _raise(st, "volume_render_logged")
+        _LogWatch.watch(log, cap, n)
     return out, (log, cap)
 
 
 def log_chunks_used(log):
-    """Chunks the logged forward needed (synchronises the current stream)."""
+    """Chunks the logged forward asked for (synchronises the current stream)."""
     used = C.c_int64(0)
     st = library().svoxb_item_log_used(C.c_void_p(log.data_ptr()), C.byref(used), _stream())
     if st:
@@ -401,34 +477,27 @@ def log_chunks_used(log):
     return used.value
 
 
-def _log_usage(log, cap, n_rays):
-    """Chunks used by the logged forward; adapts the per-ray estimate for the next log."""
-    global _items_per_ray
-    used = log_chunks_used(log)
-    _log_usage.last = used
-    if n_rays:
-        # chunks are 32 items, partly filled ones included: keep 25 % head room
-        need = max(8.0, 1.25 * 32.0 * used / n_rays)
-        _items_per_ray = need if used > cap else max(need, 0.9 * _items_per_ray)
-    return used
-
-
 def volume_render_backward_replay(tree, rays_or_cam, opt, grad_output, fwd_out, logpair,
-                                  image=False):
-    """Gradient w.r.t. data from the item log of ``volume_render_logged``; returns None if
-    the log overflowed (the caller then uses ``volume_render[_image]_backward``)."""
+                                  image=False, used=0, zeroed=None):
+    """Gradient w.r.t. data from the item log of ``volume_render_logged``.
+
+    ``used=0``: the host does not know whether the log was large enough and does not wait to
+    find out -- the kernels check on the device, and a marching backward enqueued behind them
+    takes over in that case.  ``used`` > 0: a count read with ``log_chunks_used`` that fits
+    the capacity (smaller scratch, no fallback enqueued).  ``zeroed``: a zero tensor like
+    ``data`` to add the gradient into (else one is made here)."""
     lib = library()
     log, cap = logpair
     dev = tree.data.device
     with torch.cuda.device(dev):
-        used = _log_usage(log, cap, fwd_out.numel() // 3)
-        if used > cap:
-            return None
         ct = _pack_tree(tree)
         co = opt._pack()
         _check_input(grad_output, "grad_output")
         _check_input(fwd_out, "fwd_out")
-        grad = torch.zeros_like(tree.data, memory_format=torch.contiguous_format)
+        if used > cap:
+            raise RuntimeError("the item log overflowed: it cannot be replayed")
+        grad = zeroed if zeroed is not None else \
+            torch.zeros_like(tree.data, memory_format=torch.contiguous_format)
         if image:
             cs = _pack_camera(rays_or_cam, dev)
             fn = lib.svoxb_volume_render_image_backward_replay
@@ -444,16 +513,17 @@ def volume_render_backward_replay(tree, rays_or_cam, opt, grad_output, fwd_out, 
     return grad
 
 
-def volume_render_hessdiag_replay(tree, rays_or_cam, opt, fwd_out, logpair, image=False):
+def volume_render_hessdiag_replay(tree, rays_or_cam, opt, fwd_out, logpair, used, image=False):
     """Gauss-Newton diagonal of the squared error from the item log (third result of the
-    reference's ``se_grad``); None if the log overflowed."""
+    reference's ``se_grad``).  ``used``: the count from ``log_chunks_used`` (there is no
+    marching fallback for this result, so the caller has to know that the log was large
+    enough)."""
     lib = library()
     log, cap = logpair
     dev = tree.data.device
+    if not 0 < used <= cap:
+        raise RuntimeError("the item log overflowed or its chunk count is not known")
     with torch.cuda.device(dev):
-        used = _log_usage(log, cap, fwd_out.numel() // 3)
-        if used > cap:
-            return None
         ct = _pack_tree(tree)
         co = opt._pack()
         _check_input(fwd_out, "fwd_out")
@@ -472,24 +542,30 @@ def volume_render_hessdiag_replay(tree, rays_or_cam, opt, fwd_out, logpair, imag
     return hess
 
 
+def replay_part_ranges(M, K, n_parts):
+    """Leaf-slot ranges [(begin, end)] of the ``n_parts`` parts of a replay backward for a tree
+    of ``M`` nodes with ``K`` floats per record (whole bins; the same on every process)."""
+    shift = library().svoxb_replay_bin_shift(C.c_int64(M), C.c_int32(K))
+    n_slots = M * 8
+    n_bins = ((n_slots - 1) >> shift) + 1
+    cut = [min(((p * n_bins) // n_parts) << shift, n_slots) for p in range(n_parts)] + [n_slots]
+    return list(zip(cut[:-1], cut[1:]))
+
+
 def volume_render_backward_replay_parts(tree, rays_or_cam, opt, grad_output, fwd_out, logpair,
-                                        n_parts, on_part, agree=None, reserve_sms=0,
-                                        image=False):
+                                        n_parts, on_part, reserve_sms=0, image=False,
+                                        zeroed=None):
     """The replay backward in ``n_parts`` consecutive leaf ranges.  After each part
     ``on_part(rows)`` is called with the flat view of the gradient rows that are final
-    (e.g. to start their all-reduce while the next part is computed).  ``agree(ok)``, if
-    given, is called once as ``agree(ok, log)`` with whether this process can replay and
-    the log (words ``LOG_HIST`` on hold the samples per bin) and returns False (some process
-    cannot: they must take the same route when ``on_part`` runs a collective), True, or
-    ``(bin_begin, bin_end)``: the parts then tile only those bins -- the rows outside
-    receive no sample from this process.
-    Returns None if the replay was not possible (nothing has been handed to ``on_part``)."""
+    (e.g. to start their all-reduce while the next part is computed).  The host never waits
+    for the device: whether the log was large enough is decided there, and the marching
+    fallback runs before the first part, so the rows handed on are final either way and every
+    process of a data-parallel job makes the same ``on_part`` calls."""
     lib = library()
     log, cap = logpair
     dev = tree.data.device
+    K = tree.data.shape[-1]
     with torch.cuda.device(dev):
-        ok = _log_usage(log, cap, fwd_out.numel() // 3) <= cap
-        used = _log_usage.last if ok else 0
         ct = _pack_tree(tree)
         co = opt._pack()
         _check_input(grad_output, "grad_output")
@@ -500,35 +576,30 @@ def volume_render_backward_replay_parts(tree, rays_or_cam, opt, grad_output, fwd
         else:
             cs = _pack_rays(rays_or_cam, dev)
             begin = lib.svoxb_replay_begin
+        grad = zeroed if zeroed is not None else \
+            torch.zeros_like(tree.data, memory_format=torch.contiguous_format)
+        flat = grad.view(-1)
+        ranges = replay_part_ranges(ct.M, K, n_parts)
         job = C.c_void_p(None)
         with _timed("volume_render_backward"):
-            if ok:
-                st = begin(C.byref(ct), C.byref(cs), C.byref(co),
-                           C.c_void_p(grad_output.data_ptr()), C.c_void_p(fwd_out.data_ptr()),
-                           C.c_void_p(log.data_ptr()), C.c_int64(cap), C.c_int64(used),
-                           C.c_int(n_parts), _stream(), C.byref(job))
-                if st and st != ERR_TOO_LARGE:
-                    _raise(st, "replay_begin")
-                ok = st == 0
-            span = None
-            if agree is not None:
-                verdict = agree(ok, log)
-                ok = verdict is not False and verdict is not None
-                if ok and verdict is not True:
-                    span = verdict
-            if not ok:
-                if job:
-                    lib.svoxb_replay_end(job, _stream())
-                return None
-            if span is not None:
-                st = lib.svoxb_replay_set_span(job, C.c_int(int(span[0])), C.c_int(int(span[1])),
-                                               _stream())
+            st = begin(C.byref(ct), C.byref(cs), C.byref(co),
+                       C.c_void_p(grad_output.data_ptr()), C.c_void_p(fwd_out.data_ptr()),
+                       C.c_void_p(log.data_ptr()), C.c_int64(cap), C.c_int64(0),
+                       C.c_int(n_parts), C.c_void_p(grad.data_ptr()), _stream(), C.byref(job))
+            if st == ERR_TOO_LARGE:
+                # no room for the sorted samples: march; the parts are then final at once
+                fn = lib.svoxb_volume_render_image_backward if image \
+                    else lib.svoxb_volume_render_backward
+                st = fn(C.byref(ct), C.byref(cs), C.byref(co),
+                        C.c_void_p(grad_output.data_ptr()), C.c_void_p(fwd_out.data_ptr()),
+                        C.c_void_p(grad.data_ptr()), C.c_int(0), _stream())
                 if st:
-                    lib.svoxb_replay_end(job, _stream())
-                    _raise(st, "replay_set_span")
-            grad = torch.zeros_like(tree.data, memory_format=torch.contiguous_format)
-            flat = grad.view(-1)
-            K = tree.data.shape[-1]
+                    _raise(st, "volume_render_backward")
+                for lo, hi in ranges:
+                    on_part(flat[lo * K:hi * K])
+                return grad
+            if st:
+                _raise(st, "replay_begin")
             try:
                 lo, hi = C.c_int64(0), C.c_int64(0)
                 for part in range(n_parts):
@@ -537,6 +608,7 @@ def volume_render_backward_replay_parts(tree, rays_or_cam, opt, grad_output, fwd
                     if st:
                         _raise(st, "replay_scatter")
                     lib.svoxb_replay_part_range(job, C.c_int(part), C.byref(lo), C.byref(hi))
+                    assert (lo.value, hi.value) == ranges[part]
                     on_part(flat[lo.value * K:hi.value * K])
             finally:
                 lib.svoxb_replay_end(job, _stream())

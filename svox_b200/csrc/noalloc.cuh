@@ -48,14 +48,15 @@ static int launch_noalloc(const RenderCall& c, const RayBatch& src, int32_t* scr
     const int64_t n = t->M * 8;
     // Both scratch regions are fully overwritten before they are read, so nothing
     // left over from an earlier call matters.
-    annotate_sigma_kernel<<<(unsigned)((n + 255) / 256), 256, 0, c.stream>>>(
-        t->child, t->data, t->K, n, c.opt.sigma_thresh, c.opt.density_softplus, annotated);
+    annotate_sigma_kernel<<<index_grid(n, 256, sm_count()), 256, 0, c.stream>>>(
+        t->child, t->data, t->K, n, c.opt.sigma_thresh, c.opt.density_softplus, annotated,
+        LogGate{});
     SVOXB_CUDA(cudaGetLastError());
     const int level = auto_top_level(t->M, kNoAllocTopLevel);
     if (level > 0) {
         const int cells = 1 << (3 * level);
-        build_leaf_table_kernel<<<(cells + 255) / 256, 256, 0, c.stream>>>(annotated, t->M, level,
-                                                                          table);
+        build_leaf_table_kernel<<<index_grid(cells, 256, sm_count()), 256, 0, c.stream>>>(annotated, t->M, level,
+                                                                          table, LogGate{});
         SVOXB_CUDA(cudaGetLastError());
     }
     const TopTable top{table, level};

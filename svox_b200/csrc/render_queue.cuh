@@ -83,6 +83,18 @@ constexpr int kLogRows = 12;
 constexpr int kLogChunkWords = kLogRows * 32;
 constexpr int kLogGrab = 8;  // chunks a warp takes per bump of the allocation counter
 
+// A launch that is a FALLBACK for an overflowed item log: its kernels do their work only if
+// the logged forward needed more chunks than the log holds (word 0 of the log counts the
+// chunks it asked for), so the host can enqueue replay and fallback without knowing which of
+// the two applies.  `log` null: unconditional.
+struct LogGate {
+    const int32_t* log = nullptr;
+    int64_t capacity = 0;
+    __device__ __forceinline__ bool closed() const {
+        return log != nullptr && (int64_t)__ldg(log) <= capacity;
+    }
+};
+
 constexpr int kCoordBits = 24;  // integer coordinates: floor(x * 2^24), exact for float x < 1
 
 // Bricks: every inner cell of the leaf table gets the 8x8x8 grid of the three
@@ -111,18 +123,28 @@ constexpr int kMaxBricks = 1 << 16;
 // (the reader then fetches the density from the record).
 __global__ void annotate_sigma_kernel(const int32_t* __restrict__ child,
                                       const float* __restrict__ data, int K, int64_t n_slots,
-                                      float thresh, int softplus, int32_t* __restrict__ out) {
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_slots) return;
-    int32_t c = child[i];
-    if (c == 0) {
-        const float raw = __ldg(data + i * K + (K - 1));
-        const float sigma = softplus ? softplus_m1(raw) : raw;
-        if (sigma > thresh)
-            c = (!softplus && raw >= 0.f) ? (int32_t)(0x80000000u | __float_as_uint(raw))
-                                          : kOccupied;
+                                      float thresh, int softplus, int32_t* __restrict__ out,
+                                      LogGate gate) {
+    if (gate.closed()) return;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_slots;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        int32_t c = child[i];
+        if (c == 0) {
+            const float raw = __ldg(data + i * K + (K - 1));
+            const float sigma = softplus ? softplus_m1(raw) : raw;
+            if (sigma > thresh)
+                c = (!softplus && raw >= 0.f) ? (int32_t)(0x80000000u | __float_as_uint(raw))
+                                              : kOccupied;
+        }
+        out[i] = c;
     }
-    out[i] = c;
+}
+
+// Grid of an index-building kernel over n items: enough blocks to fill the device, not one
+// per 256 items (a launch that finds its gate closed should cost next to nothing).
+inline unsigned index_grid(int64_t n, int block, int sms) {
+    const int64_t need = (n + block - 1) / block, most = (int64_t)sms * (2048 / block) * 2;
+    return (unsigned)(need < most ? (need > 0 ? need : 1) : most);
 }
 
 // L2 residency hints.  The annotated child array (tens of MB, re-read hundreds
@@ -176,85 +198,88 @@ __device__ __forceinline__ void red_add_v4_hint(float* addr, float a, float b, f
 constexpr int32_t kTabDescend = INT32_MIN;
 
 __global__ void build_leaf_table_kernel(const int32_t* __restrict__ annotated, int64_t M, int L,
-                                        int32_t* __restrict__ cells) {
-    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (1 << (3 * L))) return;
-    const int S = (1 << L) - 1;
-    const int iz = idx & S, iy = (idx >> L) & S, ix = idx >> (2 * L);
-    int64_t node = 0;
-    int32_t entry = 0;
-    for (int l = L - 1; l >= 0; --l) {
-        const int u = (ix >> l) & 1, v = (iy >> l) & 1, w = (iz >> l) & 1;
-        const int32_t e = annotated[node * 8 + (u * 4 + v * 2 + w)];
-        if (e <= 0) {
-            entry = (e == 0) ? -(L - l) : kTabDescend;
-            node = -1;
-            break;
+                                        int32_t* __restrict__ cells, LogGate gate) {
+    if (gate.closed()) return;
+    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < (1 << (3 * L));
+         idx += gridDim.x * blockDim.x) {
+        const int S = (1 << L) - 1;
+        const int iz = idx & S, iy = (idx >> L) & S, ix = idx >> (2 * L);
+        int64_t node = 0;
+        int32_t entry = 0;
+        for (int l = L - 1; l >= 0; --l) {
+            const int u = (ix >> l) & 1, v = (iy >> l) & 1, w = (iz >> l) & 1;
+            const int32_t e = annotated[node * 8 + (u * 4 + v * 2 + w)];
+            if (e <= 0) {
+                entry = (e == 0) ? -(L - l) : kTabDescend;
+                node = -1;
+                break;
+            }
+            node += e;
+            if (node >= M) { entry = kTabDescend; node = -1; break; }
         }
-        node += e;
-        if (node >= M) { entry = kTabDescend; node = -1; break; }
+        cells[idx] = node >= 0 ? (int32_t)node : entry;
     }
-    cells[idx] = node >= 0 ? (int32_t)node : entry;
 }
 
 // Gives every table cell that holds a node a brick while the budget lasts.
 __global__ void assign_bricks_kernel(int32_t* __restrict__ cells, int n_cells, int cap,
-                                     int32_t* __restrict__ counter, int32_t* __restrict__ roots) {
-    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= n_cells) return;
-    const int32_t e = cells[idx];
-    if (e <= 0) return;
-    const int id = atomicAdd(counter, 1);
-    if (id >= cap) return;
-    roots[id] = e;
-    cells[idx] = kBrickFlag + id;
+                                     int32_t* __restrict__ counter, int32_t* __restrict__ roots,
+                                     LogGate gate) {
+    if (gate.closed()) return;
+    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < n_cells;
+         idx += gridDim.x * blockDim.x) {
+        const int32_t e = cells[idx];
+        if (e <= 0) continue;
+        const int id = atomicAdd(counter, 1);
+        if (id >= cap) continue;
+        roots[id] = e;
+        cells[idx] = kBrickFlag + id;
+    }
 }
 
 // One block per brick, one thread per fine cell.
 __global__ void __launch_bounds__(kBrickCells)
 fill_bricks_kernel(const int32_t* __restrict__ annotated, int64_t M, int L, int cap,
                    const int32_t* __restrict__ counter, const int32_t* __restrict__ roots,
-                   int32_t* __restrict__ bricks) {
+                   int32_t* __restrict__ bricks, LogGate gate) {
+    if (gate.closed()) return;
     int n = *counter;
     if (n > cap) n = cap;
-    if ((int)blockIdx.x >= n) return;
     const int c = threadIdx.x;
     const int x = c >> 6, y = (c >> 3) & 7, z = c & 7;
-    int64_t node = roots[blockIdx.x];
-    int32_t cell_word = 0;
-    uint32_t group_word = 0;
-    bool done = false;
-    for (int l = 0; l < kBrickLevels && !done; ++l) {
-        const int sh = kBrickLevels - 1 - l;
-        const int cell = (((x >> sh) & 1) << 2) | (((y >> sh) & 1) << 1) | ((z >> sh) & 1);
-        const int32_t e = annotated[node * 8 + cell];
-        if (l == kBrickLevels - 1) {
-            // fine cell: leaf code or link, both relative to the group's node
-            cell_word = e;
-            if (e > 0 && node + e >= M) cell_word = (int32_t)(M - node);  // reported by the march
-            group_word = (2u << 28) | (uint32_t)node;
-            done = true;
-        } else if (e <= 0) {
-            cell_word = e;
-            group_word = ((uint32_t)l << 28) | (uint32_t)(node * 8 + cell);
-            done = true;
-        } else {
-            node += e;
-            if (node >= M) {  // corrupt link: reported by the march via an out-of-range link
-                cell_word = 1;
-                group_word = (2u << 28) | (uint32_t)(M - 1);
+    for (int b = blockIdx.x; b < n; b += gridDim.x) {
+        int64_t node = roots[b];
+        int32_t cell_word = 0;
+        uint32_t group_word = 0;
+        bool done = false;
+        for (int l = 0; l < kBrickLevels && !done; ++l) {
+            const int sh = kBrickLevels - 1 - l;
+            const int cell = (((x >> sh) & 1) << 2) | (((y >> sh) & 1) << 1) | ((z >> sh) & 1);
+            const int32_t e = annotated[node * 8 + cell];
+            if (l == kBrickLevels - 1) {
+                // fine cell: leaf code or link, both relative to the group's node
+                cell_word = e;
+                if (e > 0 && node + e >= M) cell_word = (int32_t)(M - node);  // reported by the march
+                group_word = (2u << 28) | (uint32_t)node;
                 done = true;
+            } else if (e <= 0) {
+                cell_word = e;
+                group_word = ((uint32_t)l << 28) | (uint32_t)(node * 8 + cell);
+                done = true;
+            } else {
+                node += e;
+                if (node >= M) {  // corrupt link: reported by the march via an out-of-range link
+                    cell_word = 1;
+                    group_word = (2u << 28) | (uint32_t)(M - 1);
+                    done = true;
+                }
             }
         }
+        int32_t* brick = bricks + (size_t)b * kBrickWords;
+        brick[c] = cell_word;
+        if (((x | y | z) & 1) == 0)
+            brick[kBrickCells + ((x >> 1) << 4 | (y >> 1) << 2 | (z >> 1))] = (int32_t)group_word;
     }
-    int32_t* brick = bricks + (size_t)blockIdx.x * kBrickWords;
-    brick[c] = cell_word;
-    if (((x | y | z) & 1) == 0)
-        brick[kBrickCells + ((x >> 1) << 4 | (y >> 1) << 2 | (z >> 1))] = (int32_t)group_word;
-}
-
-__device__ __forceinline__ void cp_async_wait_all() {
-    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
 }
 
 // Shared memory of one warp.
@@ -300,6 +325,8 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
     extern __shared__ __align__(16) unsigned char s_raw[];
     __shared__ unsigned s_next;
     __shared__ int s_hist[LOG ? kMaxBins : 1];  // logged forward: items per bin
+    // backward with a log: the marching fallback of a replay, needed only if the log overflowed
+    if (BWD && LogGate{log, log_capacity}.closed()) return;
     if (threadIdx.x == 0) s_next = 0;
     if (LOG) {
         for (int i = threadIdx.x; i < kMaxBins; i += BLOCK) s_hist[i] = 0;
@@ -309,10 +336,9 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
         }
     }
     const TopTable top = topg;  // leaf table in global memory (top_bytes is 0)
-    __syncthreads();
-
     const int lane = threadIdx.x & 31;
     WQ& q = *reinterpret_cast<WQ*>(s_raw + top_bytes + (size_t)(threadIdx.x >> 5) * sizeof(WQ));
+    __syncthreads();
     const float d_rgb_pad = 1 + 2 * opt.rgb_padding;
     const bool single = BWD && fwd_out != nullptr;
     const float bg = opt.background_brightness;
@@ -322,6 +348,7 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
     const int base = top.level;  // level of the jump table (0: none)
     const float big = (float)(1 << kCoordBits);
     const uint64_t pol_keep = l2_policy_keep(), pol_stream = l2_policy_stream();
+    const uint64_t pol_rec = pol_stream;
 
     // ---- per-lane state -------------------------------------------------------
     // A lane marches one ray (the CURRENT one) and may still have items queued for
@@ -600,7 +627,10 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
         mine_hi >>= 32;
     };
 
-    // Requests the records of the first nb queued items into the staging rows.
+    // Requests the records of the first nb queued items into the staging rows: groups of
+    // lanes copy a record each, 16 (or 4) bytes per lane, asynchronously.  (One bulk copy
+    // per record through the copy engine was measured instead: 13 % slower, the engine's
+    // rate of small requests then bounds the kernel.)
     auto request = [&](int nb) {
 #pragma unroll
         for (int p = 0; p < 32 / Shape::IPP; ++p) {
@@ -612,12 +642,19 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                 for (int w = 0; w < Shape::WPL; ++w) {
                     const int word = wj + w * Shape::GROUP;
                     if (word < Shape::WORDS) {
-                        if (Shape::VEC) cp_async16(row + 4 * word, rec + 4 * word, pol_stream);
-                        else cp_async4(row + word, rec + word, pol_stream);
+                        if (Shape::VEC) cp_async16(row + 4 * word, rec + 4 * word, pol_rec);
+                        else cp_async4(row + word, rec + word, pol_rec);
                     }
                 }
             }
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    // Waits until the records requested last have arrived.
+    auto wait_records = [&]() {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncwarp();
     };
 
     for (;;) {
@@ -857,8 +894,7 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
 
         // ---- S step -------------------------------------------------------------------
         if (inflight) {
-            cp_async_wait_all();
-            __syncwarp();
+            wait_records();
             evaluate(32);
             inflight = false;
         }
@@ -867,13 +903,11 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
             while (qn > 0) {
                 const int nb = qn < 32 ? qn : 32;
                 request(nb);
-                cp_async_wait_all();
-                __syncwarp();
+                wait_records();
                 evaluate(nb);
             }
         } else if (qn >= 32) {
             request(32);
-            asm volatile("cp.async.commit_group;" ::: "memory");
             inflight = true;
         }
     }

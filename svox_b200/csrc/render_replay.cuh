@@ -47,19 +47,19 @@ struct ReplayBins {
     const float4* rays;  // [3 per ray] {g0,g1,g2,out0} {out1,out2,v0,v1} {v2,-,-,-}
 };
 
-// First bin of part p when the bins [bin_begin, bin_end) are cut into n_parts ranges.
-__host__ __device__ inline int replay_part_first_bin(int p, int n_parts, int bin_begin,
-                                                     int bin_end) {
-    return bin_begin + (int)(((int64_t)p * (bin_end - bin_begin)) / n_parts);
+// First bin of part p when n_bins bins are cut into n_parts ranges.
+__host__ __device__ inline int replay_part_first_bin(int p, int n_parts, int n_bins) {
+    return (int)(((int64_t)p * n_bins) / n_parts);
 }
 
-// Work counters of the parts: part p starts at the first packet of its first bin.
-__global__ void replay_parts_kernel(ReplayBins b, int n_parts, int bin_begin, int bin_end);
-
-// One block: exclusive prefix of the forward's histogram.
-__global__ void replay_prefix_kernel(const int32_t* __restrict__ log, ReplayBins b, int n_parts) {
+// One block: exclusive prefix of the forward's histogram.  A log that overflowed (the forward
+// asked for more chunks than it holds) must not be replayed: all bins are then left empty, so
+// the bin pass and the scatter find nothing to do.
+__global__ void replay_prefix_kernel(const int32_t* __restrict__ log, ReplayBins b, int n_parts,
+                                     int64_t capacity_chunks) {
     __shared__ int s[kMaxBins];
     int n_bins = log[3];
+    if ((int64_t)log[0] > capacity_chunks) n_bins = 0;
     if (n_bins < 0) n_bins = 0;
     if (n_bins > kMaxBins) n_bins = kMaxBins;
     for (int i = threadIdx.x; i < kMaxBins; i += blockDim.x) {
@@ -75,17 +75,11 @@ __global__ void replay_prefix_kernel(const int32_t* __restrict__ log, ReplayBins
             run += s[i] > 0 ? s[i] : 0;
         }
         b.offset[kMaxBins] = (int)(run < b.capacity ? run : b.capacity);
-        // part p of the scatter covers bins [first_bin(p), first_bin(p + 1)) of all bins
-        // (replay_parts_kernel narrows that to a span of bins later, if asked)
+        // part p of the scatter covers bins [first_bin(p), first_bin(p + 1)): its work
+        // counter starts at the first packet of its first bin
         for (int p = 0; p < n_parts && p < kMaxParts; ++p)
-            b.work[p] = b.offset[replay_part_first_bin(p, n_parts, 0, n_bins)];
+            b.work[p] = b.offset[replay_part_first_bin(p, n_parts, n_bins)];
     }
-}
-
-__global__ void replay_parts_kernel(ReplayBins b, int n_parts, int bin_begin, int bin_end) {
-    const int p = threadIdx.x;
-    if (p < n_parts && p < kMaxParts)
-        b.work[p] = b.offset[replay_part_first_bin(p, n_parts, bin_begin, bin_end)];
 }
 
 // Per-ray inputs of the bin pass, packed so that one item needs three 16-byte
@@ -115,8 +109,15 @@ __global__ void replay_pack_rays_kernel(TreeArgs tr, Source src, svoxb_render_op
 template <int BLOCK, int CPW, int MINB, bool HESS>   // CPW: chunks per warp and block step
 __global__ void __launch_bounds__(BLOCK, MINB)
 replay_bin_kernel(svoxb_render_options opt, const int32_t* __restrict__ log, int64_t n_chunks,
-                  int64_t n_rays, ReplayBins b) {
+                  int64_t capacity_chunks, int64_t n_rays, ReplayBins b) {
     constexpr int WARPS = BLOCK / 32;
+    {
+        // the chunks the forward really wrote (n_chunks is the host's upper bound); none of
+        // them counts if the log overflowed
+        const int64_t used = log[0];
+        if (used > capacity_chunks) return;
+        if (used < n_chunks) n_chunks = used;
+    }
     __shared__ int s_cnt[kMaxBins];   // packets of this block step per bin, then their base
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float d_rgb_pad = 1 + 2 * opt.rgb_padding;
@@ -223,7 +224,7 @@ template <int BD, int BLOCK, bool HESS>
 __global__ void __launch_bounds__(BLOCK)
 replay_scatter_kernel(int64_t n_slots, svoxb_render_options opt, float* __restrict__ grad_data,
                       const int32_t* __restrict__ log, ReplayBins b, int flags, int part,
-                      int n_parts, int bin_begin, int bin_end) {
+                      int n_parts) {
     constexpr int K = 3 * BD + 1;
     using Shape = RecordShape<K>;
     using SM = ScatterSmem<K>;
@@ -231,13 +232,10 @@ replay_scatter_kernel(int64_t n_slots, svoxb_render_options opt, float* __restri
     const int lane = threadIdx.x & 31;
     SM& sm = *reinterpret_cast<SM*>(s_raw + (size_t)(threadIdx.x >> 5) * sizeof(SM));
     const int sub = lane / Shape::GROUP, wj = lane % Shape::GROUP;
-    // packets of this part: those of its bin range (bin_end < 0: all bins)
-    if (bin_end < 0) {
-        bin_begin = 0;
-        bin_end = log[3];
-    }
-    if (bin_end > kMaxBins) bin_end = kMaxBins;
-    const int64_t total = b.offset[replay_part_first_bin(part + 1, n_parts, bin_begin, bin_end)];
+    // packets of this part: those of its bin range
+    int n_bins = log[3];
+    if (n_bins > kMaxBins) n_bins = kMaxBins;
+    const int64_t total = b.offset[replay_part_first_bin(part + 1, n_parts, n_bins)];
     const int shift = log[2];
     const uint64_t pol_keep = l2_policy_keep(), pol_stream = l2_policy_stream();
     // Blocks take units of kScatterUnit packets in bin order from one counter, so the

@@ -28,6 +28,8 @@ struct RenderCall {
     int64_t log_capacity = 0;
     // forward with a scratch built earlier by svoxb_render_scratch_build (else per call)
     int32_t* prepared = nullptr;
+    // marching backward as the fallback of a replay: does its work only if this log overflowed
+    LogGate gate{};
 };
 
 static int out_dim_of(const svoxb_tree* t, const svoxb_render_options& o) {
@@ -137,7 +139,8 @@ static int launch_queue_block(const RenderCall& c, const Source& src, const Tree
         if ((st = persistent_grid(k, BLOCK, smem, n_gran, &grid))) return st;
         k<<<grid, BLOCK, smem, c.stream>>>(tr, src, c.opt, top, (int)top_bytes, c.Q, nullptr,
                                           c.grad_out, single ? c.fwd_out : nullptr, c.grad_data,
-                                          nullptr, 0, 0, kRefillBatch);
+                                          const_cast<int32_t*>(c.gate.log), c.gate.capacity, 0,
+                                          kRefillBatch);
     }
     SVOXB_CUDA(cudaGetLastError());
     return SVOXB_OK;
@@ -154,11 +157,18 @@ static int launch_queue_fitted(const RenderCall& c, const Source& src, const Tre
     const size_t per_warp = c.backward ? sizeof(WarpQueue<K, kModeBackward>)
                             : c.log    ? sizeof(WarpQueue<K, kModeForwardLogged>)
                                        : sizeof(WarpQueue<K, kModeForward>);
+#ifdef SVOXB_EXP_BLOCK768
+    int want = 768;
+#else
     int want = 640;
+#endif
     // static shared memory: the ticket counter, and the bin histogram of the logged forward
     const size_t fixed = 64 + (c.log ? (size_t)kMaxBins * sizeof(int) : 0);
     while (want > 256 && top_bytes + (size_t)(want / 32) * per_warp + fixed > kMaxSmem) want -= 128;
     if constexpr (BD <= 9) {
+#ifdef SVOXB_EXP_BLOCK768
+        if (want >= 768) return launch_queue_block<BD, 768>(c, src, tr, top, top_bytes);
+#endif
         if (want >= 640) return launch_queue_block<BD, 640>(c, src, tr, top, top_bytes);
     }
     if constexpr (BD <= 16) {
@@ -177,7 +187,6 @@ struct ReplayJob {
     int64_t n_slots = 0, n_rays = 0, chunks = 0;
     int K = 0, basis_dim = 0, n_parts = 1, shift = 0, n_bins = 1;
     bool hess = false;   // Gauss-Newton diagonal instead of the gradient
-    int bin_begin = 0, bin_end = -1;  // bins the parts tile (-1: all)
 };
 
 // Prefix + pack + bin.  SVOXB_ERR_TOO_LARGE when the packet buffer cannot be had
@@ -225,14 +234,15 @@ static int replay_begin(const RenderCall& c, const Source& src, int64_t chunks, 
     job->shift = replay_bin_shift(c.tree->M, c.tree->K);
     job->n_bins = (int)(((job->n_slots - 1) >> job->shift) + 1);
 
-    replay_prefix_kernel<<<1, 256, 0, c.stream>>>(c.log, b, n_parts);
+    replay_prefix_kernel<<<1, 256, 0, c.stream>>>(c.log, b, n_parts, c.log_capacity);
     if (chunks > 0) {
         replay_pack_rays_kernel<<<(unsigned)((c.Q + 255) / 256), 256, 0, c.stream>>>(
             tree_args(c.tree), src, c.opt, c.grad_out, c.fwd_out, c.Q, rays);
         unsigned grid = 1;
         auto run_bin = [&](auto k, int block) {
             int s2 = persistent_grid(k, block, 0, chunks, &grid);
-            if (s2 == SVOXB_OK) k<<<grid, block, 0, c.stream>>>(c.opt, c.log, chunks, c.Q, b);
+            if (s2 == SVOXB_OK)
+                k<<<grid, block, 0, c.stream>>>(c.opt, c.log, chunks, c.log_capacity, c.Q, b);
             return s2;
         };
         st = hess ? run_bin(replay_bin_kernel<128, 2, 12, true>, 128)
@@ -266,8 +276,7 @@ static int replay_scatter_block(const ReplayJob& job, int part, float* grad, int
         if ((int64_t)grid > most) grid = (unsigned)(most > 1 ? most : 1);
     }
     k<<<grid, BLOCK, smem, stream>>>(job.n_slots, job.opt, grad, job.log, job.bins,
-                                    kReplayHints, part, job.n_parts, job.bin_begin,
-                                    job.bin_end);
+                                    kReplayHints, part, job.n_parts);
     const cudaError_t e = cudaGetLastError();
     return e != cudaSuccess ? set_cuda_error(e) : SVOXB_OK;
 }
@@ -346,7 +355,7 @@ struct QueueScratch {
 
     // Fills `external` (layout(t, max_level).words int32) or a pool allocation of its own.
     int build(const svoxb_tree* t, float thresh, int softplus, int max_level, cudaStream_t s,
-              int32_t* external = nullptr) {
+              int32_t* external = nullptr, LogGate gate = LogGate{}) {
         stream = s;
         const Layout l = layout(t, max_level);
         int32_t* mem = external;
@@ -357,22 +366,23 @@ struct QueueScratch {
             owned = true;
         }
         adopt(l, mem);
-        annotate_sigma_kernel<<<(unsigned)((l.n + 255) / 256), 256, 0, s>>>(
-            t->child, t->data, t->K, l.n, thresh, softplus, annotated);
+        const int sms = sm_count();
+        annotate_sigma_kernel<<<index_grid(l.n, 256, sms), 256, 0, s>>>(
+            t->child, t->data, t->K, l.n, thresh, softplus, annotated, gate);
         SVOXB_CUDA(cudaGetLastError());
         if (level > 0) {
-            build_leaf_table_kernel<<<(unsigned)((l.cells + 255) / 256), 256, 0, s>>>(
-                annotated, t->M, level, table);
+            build_leaf_table_kernel<<<index_grid(l.cells, 256, sms), 256, 0, s>>>(
+                annotated, t->M, level, table, gate);
             SVOXB_CUDA(cudaGetLastError());
         }
         if (l.cap > 0) {
             int32_t* counter = table + l.cells;
             int32_t* roots = counter + 8;
             SVOXB_CUDA(cudaMemsetAsync(counter, 0, sizeof(int32_t), s));
-            assign_bricks_kernel<<<(unsigned)((l.cells + 255) / 256), 256, 0, s>>>(
-                table, (int)l.cells, (int)l.cap, counter, roots);
-            fill_bricks_kernel<<<(unsigned)l.cap, kBrickCells, 0, s>>>(
-                annotated, t->M, level, (int)l.cap, counter, roots, bricks);
+            assign_bricks_kernel<<<index_grid(l.cells, 256, sms), 256, 0, s>>>(
+                table, (int)l.cells, (int)l.cap, counter, roots, gate);
+            fill_bricks_kernel<<<index_grid(l.cap * kBrickCells, kBrickCells, sms), kBrickCells, 0, s>>>(
+                annotated, t->M, level, (int)l.cap, counter, roots, bricks, gate);
             SVOXB_CUDA(cudaGetLastError());
         }
         return SVOXB_OK;
@@ -388,7 +398,7 @@ static int launch_queue(const RenderCall& c, const Source& src) {
     } else {
         const int st = scratch.build(c.tree, c.backward ? 0.f : c.opt.sigma_thresh,
                                      c.opt.density_softplus, QueueScratch::default_level(),
-                                     c.stream);
+                                     c.stream, nullptr, c.gate);
         if (st) return st;
     }
     TreeArgs tr = tree_args(c.tree);
@@ -698,18 +708,26 @@ static int replay_backward(const svoxb_tree* tree, const Source& src, int64_t Q,
     c.stream = (cudaStream_t)stream;
     c.log = log;
     c.log_capacity = capacity_chunks;
-    if (chunks_used <= 0 || chunks_used > capacity_chunks) chunks_used = capacity_chunks;
+    // chunks_used > 0: the caller has read the count (svoxb_item_log_used) and vouches that
+    // the log did not overflow.  Otherwise the count stays on the device: the scratch is sized
+    // for the whole log, the kernels read the count themselves, and a marching backward is
+    // enqueued behind them that does its work only if the log overflowed.
+    const bool known = chunks_used > 0 && chunks_used <= capacity_chunks;
+    if (hess && !known) return SVOXB_ERR_OPTION;
     ReplayJob job;
-    st = replay_begin(c, src, chunks_used, 1, &job, hess);
+    st = replay_begin(c, src, known ? chunks_used : capacity_chunks, 1, &job, hess);
     if (st == SVOXB_OK) {
         st = replay_scatter(job, 0, grad_data_out, 0, c.stream);
         replay_end(&job, c.stream);
     }
-    if (st == SVOXB_ERR_TOO_LARGE && !hess) {
-        // no room for the packets: march instead (same result, the log is not used)
-        c.log = nullptr;
-        c.log_capacity = 0;
-        return render_dispatch(c, src);
+    if (hess) return st;
+    RenderCall march = c;
+    march.log = nullptr;
+    march.log_capacity = 0;
+    if (st == SVOXB_ERR_TOO_LARGE) return render_dispatch(march, src);  // no room for packets
+    if (st == SVOXB_OK && !known) {
+        march.gate = LogGate{log, capacity_chunks};
+        st = render_dispatch(march, src);
     }
     return st;
 }
@@ -798,14 +816,15 @@ template <class Source>
 static int replay_begin_checked(const svoxb_tree* tree, const Source& src, int64_t Q,
                                 const svoxb_render_options* opt, const float* grad_output,
                                 const float* fwd_out, int32_t* log, int64_t capacity_chunks,
-                                int64_t chunks_used, int n_parts, void* stream, void** job_out) {
+                                int64_t chunks_used, int n_parts, float* grad_data_out,
+                                void* stream, void** job_out) {
     if (!job_out) return SVOXB_ERR_NULL;
     *job_out = nullptr;
     int st = validate_tree(tree);
     if (st) return st;
     if ((st = validate_options(tree, *opt))) return st;
-    if (!log || (Q > 0 && (!grad_output || !fwd_out))) return SVOXB_ERR_NULL;
-    if ((st = log_eligible(tree, opt, nullptr))) return st;
+    if (!log || !grad_data_out || (Q > 0 && (!grad_output || !fwd_out))) return SVOXB_ERR_NULL;
+    if ((st = log_eligible(tree, opt, grad_data_out))) return st;
     RenderCall c{tree, *opt, Q};
     c.backward = true;
     c.grad_out = grad_output;
@@ -813,11 +832,24 @@ static int replay_begin_checked(const svoxb_tree* tree, const Source& src, int64
     c.stream = (cudaStream_t)stream;
     c.log = log;
     c.log_capacity = capacity_chunks;
-    if (chunks_used <= 0 || chunks_used > capacity_chunks) chunks_used = capacity_chunks;
+    const bool known = chunks_used > 0 && chunks_used <= capacity_chunks;
+    if (!known) chunks_used = capacity_chunks;
     if (Q == 0) chunks_used = 0;
     ReplayJob* job = new (std::nothrow) ReplayJob;
     if (!job) return SVOXB_ERR_TOO_LARGE;
     st = replay_begin(c, src, chunks_used, n_parts, job);
+    if (st == SVOXB_OK && !known && Q > 0) {
+        // the fallback for an overflowed log goes BEFORE the parts: if it runs, it produces the
+        // whole gradient and the parts add nothing, so every part's rows are final when the
+        // caller hands them on, whichever of the two happened
+        RenderCall march = c;
+        march.grad_data = grad_data_out;
+        march.log = nullptr;
+        march.log_capacity = 0;
+        march.gate = LogGate{log, capacity_chunks};
+        st = render_dispatch(march, src);
+        if (st != SVOXB_OK) replay_end(job, c.stream);
+    }
     if (st != SVOXB_OK) {
         delete job;
         return st;
@@ -831,24 +863,26 @@ extern "C" {
 int svoxb_replay_begin(const svoxb_tree* tree, const svoxb_rays* rays,
                        const svoxb_render_options* opt, const float* grad_output,
                        const float* fwd_out, int32_t* log, int64_t capacity_chunks,
-                       int64_t chunks_used, int n_parts, void* stream, void** job) {
+                       int64_t chunks_used, int n_parts, float* grad_data_out, void* stream,
+                       void** job) {
     if (!tree || !rays || !opt) return SVOXB_ERR_NULL;
     if (rays->Q > 0 && (!rays->origins || !rays->dirs || !rays->vdirs)) return SVOXB_ERR_NULL;
     return replay_begin_checked(tree, RayBatch{rays->origins, rays->dirs, rays->vdirs}, rays->Q,
                                 opt, grad_output, fwd_out, log, capacity_chunks, chunks_used,
-                                n_parts, stream, job);
+                                n_parts, grad_data_out, stream, job);
 }
 
 int svoxb_replay_image_begin(const svoxb_tree* tree, const svoxb_camera* cam,
                              const svoxb_render_options* opt, const float* grad_output,
                              const float* fwd_out, int32_t* log, int64_t capacity_chunks,
-                             int64_t chunks_used, int n_parts, void* stream, void** job) {
+                             int64_t chunks_used, int n_parts, float* grad_data_out,
+                             void* stream, void** job) {
     if (!tree || !cam || !opt || !cam->c2w) return SVOXB_ERR_NULL;
     if (cam->width < 0 || cam->height < 0) return SVOXB_ERR_SHAPE;
     return replay_begin_checked(tree,
                                 PixelRays{cam->c2w, cam->fx, cam->fy, cam->width, cam->height},
                                 (int64_t)cam->width * cam->height, opt, grad_output, fwd_out, log,
-                                capacity_chunks, chunks_used, n_parts, stream, job);
+                                capacity_chunks, chunks_used, n_parts, grad_data_out, stream, job);
 }
 
 int svoxb_replay_bin_shift(int64_t M, int32_t K) {
@@ -856,25 +890,12 @@ int svoxb_replay_bin_shift(int64_t M, int32_t K) {
     return replay_bin_shift(M, K);
 }
 
-int svoxb_replay_set_span(void* job, int bin_begin, int bin_end, void* stream) {
-    if (!job) return SVOXB_ERR_NULL;
-    ReplayJob* j = static_cast<ReplayJob*>(job);
-    if (bin_begin < 0 || bin_end < bin_begin || bin_end > j->n_bins) return SVOXB_ERR_OPTION;
-    j->bin_begin = bin_begin;
-    j->bin_end = bin_end;
-    replay_parts_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(j->bins, j->n_parts, bin_begin,
-                                                           bin_end);
-    const cudaError_t e = cudaGetLastError();
-    return e != cudaSuccess ? set_cuda_error(e) : SVOXB_OK;
-}
-
 int svoxb_replay_part_range(const void* job, int part, int64_t* slot_begin, int64_t* slot_end) {
     if (!job || !slot_begin || !slot_end) return SVOXB_ERR_NULL;
     const ReplayJob* j = static_cast<const ReplayJob*>(job);
     if (part < 0 || part >= j->n_parts) return SVOXB_ERR_OPTION;
-    const int b0 = j->bin_begin, b1 = j->bin_end < 0 ? j->n_bins : j->bin_end;
-    const int64_t lo = (int64_t)replay_part_first_bin(part, j->n_parts, b0, b1) << j->shift;
-    int64_t hi = (int64_t)replay_part_first_bin(part + 1, j->n_parts, b0, b1) << j->shift;
+    const int64_t lo = (int64_t)replay_part_first_bin(part, j->n_parts, j->n_bins) << j->shift;
+    int64_t hi = (int64_t)replay_part_first_bin(part + 1, j->n_parts, j->n_bins) << j->shift;
     if (hi > j->n_slots) hi = j->n_slots;
     *slot_begin = lo < j->n_slots ? lo : j->n_slots;
     *slot_end = hi;

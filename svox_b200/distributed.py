@@ -43,7 +43,8 @@ class _Overlap:
     """State of the overlapped gradient all-reduce (see ``overlap_grad_allreduce``)."""
     group = None
     works = []
-    reduced = False     # the gradient of the last backward left the renderer already summed
+    reduced = 0       # backward passes since the last allreduce_grad whose gradient left the
+    backwards = 0     # renderer already summed / all of them that went through the hook
 
     @classmethod
     def on_part(cls, rows):
@@ -53,44 +54,25 @@ class _Overlap:
                                          async_op=True))
 
     @classmethod
-    def agree(cls, ok, log):
-        # Every rank must take the same route (the parts run one collective each), and only
-        # the leaf ranges that received samples on SOME rank need reducing: sum the ranks'
-        # "cannot replay" flags and their per-bin sample counts in one small all-reduce.
-        from .csrc import LOG_HIST, LOG_MAX_BINS
-        vec = torch.empty(1 + LOG_MAX_BINS, dtype=torch.int64, device=log.device)
-        vec[0] = 0 if ok else 1
-        vec[1:] = log[LOG_HIST:LOG_HIST + LOG_MAX_BINS]
-        dist.all_reduce(vec, op=dist.ReduceOp.SUM, group=cls.group)
-        host = vec.cpu()
-        n_bins = int(log[3].item())
-        if int(host[0]) != 0:
-            return False
-        used = torch.nonzero(host[1:1 + n_bins]).flatten()
-        if used.numel() == 0:
-            return (0, 0)
-        return (int(used[0]), int(used[-1]) + 1)
-
-    @classmethod
     def on_done(cls):
         for w in cls.works:
             w.wait()            # the current stream waits for the collective's stream
         cls.works = []
-        cls.reduced = True
+        cls.reduced += 1
 
 
 def overlap_grad_allreduce(n_parts=8, group=None, reserve_sms=16):
-    """Overlap the all-reduce of ``data.grad`` with its computation, and reduce only the
-    leaf ranges that received samples on some rank (the rest of the gradient is zero
-    everywhere).  ``n_parts=1`` keeps the second saving without the overlap.
+    """Overlap the all-reduce of ``data.grad`` with its computation.
 
     The replay backward of the renderer produces the gradient leaf range by leaf range;
     with this switched on, the rows of a finished range are all-reduced (asynchronously, on
     the backend's stream) while the next range is computed, and ``reserve_sms`` SMs are left
     to the collective's kernel.  ``allreduce_grad`` then finds the gradient already summed
-    and does nothing.  Steps whose backward cannot take that route on some rank (log overflow, options
-    the replay does not cover) still get the plain all-reduce; the ranks agree on the route
-    with a one-word all-reduce per step.  ``n_parts=0`` switches it off.
+    and does nothing.  The ranges depend on the tree's size alone and the host never looks
+    at device results on this route (an item log that turns out too small is handled on the
+    device), so every rank issues the same collectives in the same order.  Backward passes
+    that do not replay (thresholds on, ``data`` edited since the forward) leave their
+    gradient to ``allreduce_grad``.  ``n_parts=0`` switches it off.
     Every rank must make the same call.
     """
     from . import render
@@ -100,8 +82,8 @@ def overlap_grad_allreduce(n_parts=8, group=None, reserve_sms=16):
         return
     _Overlap.group = group
     _Overlap.works = []
-    _Overlap.reduced = False
-    render.GRAD_PARTS = (int(n_parts), _Overlap.on_part, _Overlap.on_done, _Overlap.agree,
+    _Overlap.reduced = 0
+    render.GRAD_PARTS = (int(n_parts), _Overlap.on_part, _Overlap.on_done,
                          int(reserve_sms) if n_parts > 1 else 0)   # one part: nothing overlaps
 
 
@@ -109,12 +91,21 @@ def allreduce_grad(tree, group=None, async_op=False):
     """Sum ``tree.data.grad`` over all ranks (the one collective of a training step).
 
     A rank whose rays all missed the tree has no gradient yet: it contributes zeros.
+    With ``overlap_grad_allreduce`` on, a step with ONE backward pass arrives here already
+    summed.  A step that accumulated several backward passes into ``data.grad`` cannot be
+    told apart element by element, so that combination is refused: switch the overlap off
+    when accumulating gradients.
     """
     if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
         return None
-    if _Overlap.reduced:        # summed range by range inside the backward pass
-        _Overlap.reduced = False
+    reduced, _Overlap.reduced = _Overlap.reduced, 0
+    if reduced == 1:            # summed range by range inside the backward pass
         return None
+    if reduced > 1:
+        raise RuntimeError(
+            "allreduce_grad: several backward passes were reduced inside the backward and "
+            "accumulated into data.grad; call allreduce_grad after each backward, or switch "
+            "overlap_grad_allreduce off when accumulating gradients")
     if tree.data.grad is None:
         tree.data.grad = torch.zeros_like(tree.data)
     return dist.all_reduce(tree.data.grad, op=dist.ReduceOp.SUM, group=group, async_op=async_op)

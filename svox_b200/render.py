@@ -22,24 +22,55 @@ __all__ = ["VolumeRenderer", "NDCConfig", "Rays", "_VolumeRenderFunction",
 # samples so that the backward replays them instead of marching again (costs
 # memory: about 40 bytes per contributing sample until the backward has run).
 USE_ITEM_LOG = True
+# Tests: make the backward ignore what the forward kept and march twice like the reference.
+FORCE_TWO_MARCHES = False
 
 # Set by ``svox_b200.distributed.overlap_grad_allreduce``: (n_parts, on_part, on_done,
-# agree, reserve_sms).  The replay backward then produces the gradient in n_parts consecutive
+# reserve_sms).  The replay backward then produces the gradient in n_parts consecutive
 # leaf ranges and hands each finished range to on_part (which starts its all-reduce).
 GRAD_PARTS = None
 
 
-def _replay(tree, src, opt, grad_out, fwd, log, image):
-    """Replay backward, in parts when a gradient hook is installed; None -> caller marches."""
+_side_streams = {}
+
+
+def _zeroed_beside(like):
+    """A zero tensor shaped like ``like`` whose fill runs on a side stream; -> (tensor, event
+    after which it is zero)."""
+    dev = like.device
+    side = _side_streams.get(dev)
+    if side is None:
+        side = _side_streams[dev] = torch.cuda.Stream(device=dev)
+    buf = torch.empty_like(like, memory_format=torch.contiguous_format)
+    side.wait_stream(torch.cuda.current_stream(dev))     # the memory's previous users are done
+    with torch.cuda.stream(side):
+        buf.zero_()
+        done = torch.cuda.Event()
+        done.record(side)
+    return buf, done
+
+
+def _claim(ctx):
+    """The gradient buffer cleared during the forward, once the current stream may use it."""
+    if ctx.grad_buffer is None:
+        return None
+    buf, done = ctx.grad_buffer
+    ctx.grad_buffer = None
+    torch.cuda.current_stream(buf.device).wait_event(done)
+    return buf
+
+
+def _replay(tree, src, opt, grad_out, fwd, log, image, zeroed=None):
+    """Replay backward, in parts when a gradient hook is installed."""
     if GRAD_PARTS is not None:
-        n_parts, on_part, on_done, agree, reserve = GRAD_PARTS
+        n_parts, on_part, on_done, reserve = GRAD_PARTS
         grad = _C.volume_render_backward_replay_parts(tree, src, opt, grad_out, fwd, log, n_parts,
-                                                      on_part, agree=agree, reserve_sms=reserve,
-                                                      image=image)
-        if grad is not None:
-            on_done()
+                                                      on_part, reserve_sms=reserve, image=image,
+                                                      zeroed=zeroed)
+        on_done()
         return grad
-    return _C.volume_render_backward_replay(tree, src, opt, grad_out, fwd, log, image=image)
+    return _C.volume_render_backward_replay(tree, src, opt, grad_out, fwd, log, image=image,
+                                            zeroed=zeroed)
 
 NDCConfig = namedtuple("NDCConfig", ["width", "height", "focal"])
 Rays = namedtuple("Rays", ["origins", "dirs", "viewdirs"])
@@ -70,41 +101,74 @@ def _single_march_ok(opt):
     return opt.sigma_thresh == 0.0 and opt.stop_thresh == 0.0
 
 
+def _forward(ctx, data, tree, src, opt, prepared, train, image):
+    """Common forward of the two autograd Functions.
+
+    What the backward needs is kept with ``save_for_backward`` (freed with the graph, and an
+    in-place edit of the returned render raises instead of silently corrupting the gradient):
+    the render itself, whose dot product with the upstream gradient replaces the reference's
+    first march, and the item log of a training step.
+    """
+    ctx.tree, ctx.src, ctx.opt, ctx.image = tree, src, opt, image
+    ctx.log_capacity = None
+    # `train`: whether a backward can follow (the caller knows the grad mode; in here it
+    # is always off, and requires_grad / needs_input_grad ignore torch.no_grad())
+    if train is None:
+        train = data.requires_grad
+    log = None
+    ctx.grad_buffer = None
+    if train and USE_ITEM_LOG and _C.log_eligible(tree, opt):
+        # training step: record the contributing samples for the backward pass, and clear the
+        # gradient buffer the backward will add into on a second stream meanwhile (the march
+        # leaves a third of the memory bandwidth unused)
+        ctx.grad_buffer = _zeroed_beside(tree.data)
+        out, (log, ctx.log_capacity) = _C.volume_render_logged(tree, src, opt, image=image)
+    elif image:
+        out = _C.volume_render_image(tree, src, opt, prepared=prepared)
+    else:
+        out = _C.volume_render(tree, src, opt, prepared=prepared)
+    ctx.data_state = (data._version, tree.data_epoch())
+    ctx.keeps_out = train and _single_march_ok(opt)
+    if ctx.keeps_out:
+        ctx.save_for_backward(*((out,) if log is None else (out, log)))
+    return out
+
+
+def _backward(ctx, grad_out):
+    """Common backward: replay of the item log, else one march with the saved render, else
+    (``data`` was edited since the forward, or thresholds are on) the reference's two marches,
+    which recompute everything from the current ``data`` as the reference does."""
+    none = (None,) * 5
+    if not ctx.needs_input_grad[0]:
+        return (None,) + none
+    fwd = log = None
+    if ctx.keeps_out and not FORCE_TWO_MARCHES:
+        saved = ctx.saved_tensors
+        unchanged = ctx.data_state == (ctx.tree.data._version, ctx.tree.data_epoch())
+        if unchanged:
+            fwd = saved[0]
+            if len(saved) > 1:
+                log = (saved[1], ctx.log_capacity)
+    grad_out = grad_out.contiguous()
+    if fwd is not None and log is not None:
+        return (_replay(ctx.tree, ctx.src, ctx.opt, grad_out, fwd, log, ctx.image,
+                        _claim(ctx)),) + none
+    ctx.grad_buffer = None
+    if ctx.image:
+        return (_C.volume_render_image_backward(ctx.tree, ctx.src, ctx.opt, grad_out, fwd),) + none
+    return (_C.volume_render_backward(ctx.tree, ctx.src, ctx.opt, grad_out, fwd),) + none
+
+
 class _VolumeRenderFunction(autograd.Function):
-    """svox/renderer.py:57-72.  Additionally remembers the forward output and
-    the version of ``data`` so that the backward kernel can march once."""
+    """svox/renderer.py:57-72."""
 
     @staticmethod
     def forward(ctx, data, tree, rays, opt, prepared=None, train=None):
-        ctx.tree, ctx.rays, ctx.opt = tree, rays, opt
-        ctx.log = None
-        # `train`: whether a backward can follow (the caller knows the grad mode; in here it
-        # is always off, and requires_grad / needs_input_grad ignore torch.no_grad())
-        if train is None:
-            train = data.requires_grad
-        if train and USE_ITEM_LOG and _C.log_eligible(tree, opt):
-            # training step: record the contributing samples for the backward pass
-            out, ctx.log = _C.volume_render_logged(tree, rays, opt)
-        else:
-            out = _C.volume_render(tree, rays, opt, prepared=prepared)
-        ctx.fwd = (out, data._version) if _single_march_ok(opt) else None
-        return out
+        return _forward(ctx, data, tree, rays, opt, prepared, train, False)
 
     @staticmethod
     def backward(ctx, grad_out):
-        if not ctx.needs_input_grad[0]:
-            return None, None, None, None, None, None
-        fwd = None
-        if ctx.fwd is not None and ctx.fwd[1] == ctx.tree.data._version:
-            fwd = ctx.fwd[0]
-        grad_out = grad_out.contiguous()
-        if fwd is not None and ctx.log is not None:
-            grad = _replay(ctx.tree, ctx.rays, ctx.opt, grad_out, fwd, ctx.log, False)
-            ctx.log = None
-            if grad is not None:
-                return grad, None, None, None, None, None
-        return _C.volume_render_backward(ctx.tree, ctx.rays, ctx.opt, grad_out,
-                                         fwd), None, None, None, None, None
+        return _backward(ctx, grad_out)
 
 
 class _VolumeRenderImageFunction(autograd.Function):
@@ -112,32 +176,11 @@ class _VolumeRenderImageFunction(autograd.Function):
 
     @staticmethod
     def forward(ctx, data, tree, cam, opt, prepared=None, train=None):
-        ctx.tree, ctx.cam, ctx.opt = tree, cam, opt
-        ctx.log = None
-        if train is None:
-            train = data.requires_grad
-        if train and USE_ITEM_LOG and _C.log_eligible(tree, opt):
-            out, ctx.log = _C.volume_render_logged(tree, cam, opt, image=True)
-        else:
-            out = _C.volume_render_image(tree, cam, opt, prepared=prepared)
-        ctx.fwd = (out, data._version) if _single_march_ok(opt) else None
-        return out
+        return _forward(ctx, data, tree, cam, opt, prepared, train, True)
 
     @staticmethod
     def backward(ctx, grad_out):
-        if not ctx.needs_input_grad[0]:
-            return None, None, None, None, None, None
-        fwd = None
-        if ctx.fwd is not None and ctx.fwd[1] == ctx.tree.data._version:
-            fwd = ctx.fwd[0]
-        grad_out = grad_out.contiguous()
-        if fwd is not None and ctx.log is not None:
-            grad = _replay(ctx.tree, ctx.cam, ctx.opt, grad_out, fwd, ctx.log, True)
-            ctx.log = None
-            if grad is not None:
-                return grad, None, None, None, None, None
-        return _C.volume_render_image_backward(ctx.tree, ctx.cam, ctx.opt, grad_out,
-                                               fwd), None, None, None, None, None
+        return _backward(ctx, grad_out)
 
 
 class _FrozenTree:
@@ -257,14 +300,16 @@ class VolumeRenderer(nn.Module):
             colors = colors.to(device=self.tree.data.device, dtype=self.tree.data.dtype)
             for _ in range(4):      # a log that was too small is enlarged and the render redone
                 out, log = _C.volume_render_logged(tree, src, opt, image=image)
+                used = _C.log_chunks_used(log[0])
+                _C.log_estimate(wait=True)
+                if used > log[1]:
+                    continue
                 resid = (out - colors.reshape(out.shape)).contiguous()
                 grad = _C.volume_render_backward_replay(tree, src, opt, resid, out, log,
+                                                        image=image, used=max(used, 1))
+                hess = _C.volume_render_hessdiag_replay(tree, src, opt, out, log, max(used, 1),
                                                         image=image)
-                if grad is None:
-                    continue
-                hess = _C.volume_render_hessdiag_replay(tree, src, opt, out, log, image=image)
-                if hess is not None:
-                    return out, grad, hess
+                return out, grad, hess
         raise RuntimeError("se_grad: the item log kept overflowing")
 
     @staticmethod

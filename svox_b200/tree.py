@@ -17,6 +17,7 @@ native library; there is no CPU implementation of the query in this
 package (a CPU tree raises).
 """
 import math
+import weakref
 from warnings import warn
 
 import numpy as np
@@ -93,6 +94,7 @@ class N3Tree(nn.Module):
             self.extra_data = None
 
         self._ver = 0
+        self._data_epoch = 0     # bumped by every write that goes through ``data.data``
         self._invalidate()
         self._lock_tree_structure = False
         self._weight_accum = None
@@ -373,12 +375,14 @@ class N3Tree(nn.Module):
 
     def _invalidate(self):
         self._ver += 1
+        self._data_epoch += 1
         self._last_all_leaves = None
         self._last_frontier = None
 
     def _spec(self, world=True):
         """Pack the tensors for the native library (svox/svox.py:1084-1103)."""
         spec = _C.TreeSpec()
+        spec._owner = weakref.ref(self)
         spec.data = self.data
         spec.child = self.child
         spec.parent_depth = self.parent_depth

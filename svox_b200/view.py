@@ -94,6 +94,9 @@ class N3TreeView:
         if isinstance(value, N3TreeView):
             value = value.values_nograd
         data = self.tree.data.data
+        # autograd's version counter does not see writes through ``.data``: count them, so
+        # that a backward whose forward ran before this edit recomputes from the new values
+        self.tree._data_epoch += 1
         if self._require_subindex():
             k4 = self._dev_key(4)
             tmp = data[k4]

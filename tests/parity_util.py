@@ -43,10 +43,12 @@ def run_product(case, device="cuda:0", backward=True, single_march=True, item_lo
     ``single_march``) instead of replaying the forward's item log."""
     from svox_b200 import render as _render
     _render.USE_ITEM_LOG = bool(item_log)
+    _render.FORCE_TWO_MARCHES = not single_march
     try:
         return _run_product(case, device, backward, single_march)
     finally:
         _render.USE_ITEM_LOG = True
+        _render.FORCE_TWO_MARCHES = False
 
 
 def _run_product(case, device, backward, single_march):
@@ -72,8 +74,6 @@ def _run_product(case, device, backward, single_march):
         if backward and case["mse_targets"] is not None:
             ((out - case["mse_targets"].to(device)) ** 2).mean().backward()
         elif backward and case["grad_out"] is not None:
-            if not single_march:
-                out.grad_fn.fwd = None  # force the reference's two-march backward
             out.backward(case["grad_out"].to(device))
     if tree.data.grad is not None:
         res["grad"] = tree.data.grad.double().cpu().numpy()

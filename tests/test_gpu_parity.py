@@ -189,21 +189,16 @@ def test_replay_in_parts_equals_replay_in_one_go(name, image, cuda_device):
             src = svox.render._rays_spec_from_rays(
                 svox.Rays(*[t.to(cuda_device) for t in case["rays"]]))
         gout = case["grad_out"].to(cuda_device).contiguous()
-        for _ in range(3):
-            out, log = csrc.volume_render_logged(spec, src, opt, image=image)
-            whole = csrc.volume_render_backward_replay(spec, src, opt, gout, out, log, image=image)
-            if whole is not None:
-                break
-        assert whole is not None
+        out, log = csrc.volume_render_logged(spec, src, opt, image=image)
+        whole = csrc.volume_render_backward_replay(spec, src, opt, gout, out, log, image=image)
         seen = []
 
         def on_part(rows):
             seen.append((rows.data_ptr(), rows.numel(), float(rows.abs().sum())))
 
         parts = csrc.volume_render_backward_replay_parts(spec, src, opt, gout, out, log, 5,
-                                                         on_part, agree=lambda ok, log: ok,
-                                                         reserve_sms=8, image=image)
-        assert parts is not None and len(seen) == 5
+                                                         on_part, reserve_sms=8, image=image)
+        assert len(seen) == 5
         filled = [x for x in seen if x[1] > 0]             # an empty view has no address
         assert filled[0][0] == parts.data_ptr()
         for (p0, n0, _), (p1, _, _) in zip(filled, filled[1:]):
@@ -212,21 +207,11 @@ def test_replay_in_parts_equals_replay_in_one_go(name, image, cuda_device):
         assert any(a > 0 for _, _, a in seen)
         scale = whole.abs().max().item()
         assert (parts - whole).abs().max().item() <= 1e-5 * scale
-
-        # the same over the span of bins that hold samples only (what a multi-GPU caller
-        # reduces): the rows outside stay zero, as they are in the one-shot gradient
-        def used_span(ok, log_words):
-            n_bins = int(log_words[3].item())
-            hist = log_words[csrc.LOG_HIST:csrc.LOG_HIST + n_bins].cpu()
-            used = torch.nonzero(hist).flatten()
-            return (int(used[0]), int(used[-1]) + 1)
-
-        del seen[:]
-        span = csrc.volume_render_backward_replay_parts(spec, src, opt, gout, out, log, 3,
-                                                        on_part, agree=used_span, image=image)
-        assert span is not None and len(seen) == 3
-        assert sum(n for _, n, _ in seen) <= parts.numel()
-        assert (span - whole).abs().max().item() <= 1e-5 * scale
+        # the ranges are a function of the tree's size alone (every process of a
+        # data-parallel job cuts the gradient at the same rows)
+        K = tree.data_dim
+        want = csrc.replay_part_ranges(tree.child.shape[0], K, 5)
+        assert [n for _, n, _ in seen] == [(hi - lo) * K for lo, hi in want]
         csrc.check_device_status()
     finally:
         case["tree"].to("cpu")
@@ -266,22 +251,73 @@ def test_frozen_tree_renders_are_identical(name, cuda_device):
 
 
 def test_item_log_overflow_falls_back(cuda_device):
-    # A log that is too small must not be replayed: the backward marches instead.
+    # A log that is too small must not be replayed.  Nobody on the host knows at the time: the
+    # replay kernels see it on the device and do nothing, and the marching backward enqueued
+    # behind them does the work.  Both the one-shot replay and the replay in parts.
     case = CASES["shell_sh9_rays"]()
-    old = csrc._items_per_ray
+    orc = P.run_oracle(case)
+    marched = P.run_product(case, cuda_device, item_log=False)
+    old, slack = csrc._items_per_ray, csrc._LOG_SLACK_CHUNKS
     try:
+        csrc.log_estimate(wait=True)
         csrc._items_per_ray = 0.0
-        slack = csrc._LOG_SLACK_CHUNKS
         csrc._LOG_SLACK_CHUNKS = 64                       # far fewer chunks than needed
         a = P.run_product(case, cuda_device)
-        csrc._LOG_SLACK_CHUNKS = slack
-        assert csrc._items_per_ray > 1.0                # the estimate was raised for next time
-        b = P.run_product(case, cuda_device, item_log=False)
-        orc = P.run_oracle(case)
-        assert P.grad_excess(a["grad"], b["grad"], orc["grad_abs"], GRAD_TOL_REF) <= 2.5
+        assert csrc.log_estimate(wait=True) > 1.0       # the estimate was raised for next time
+        assert csrc._LogWatch.last_used > csrc._LogWatch.last_cap
+        assert P.grad_excess(a["grad"], marched["grad"], orc["grad_abs"], GRAD_TOL_REF) <= 2.5
+
+        csrc._items_per_ray = 0.0
+        tree = case["tree"].to(cuda_device)
+        r = P._renderer(tree, case)
+        opt, spec = r._get_options(False), tree._spec()
+        src = svox.render._rays_spec_from_rays(svox.Rays(*[t.to(cuda_device) for t in case["rays"]]))
+        gout = case["grad_out"].to(cuda_device).contiguous()
+        out, log = csrc.volume_render_logged(spec, src, opt)
+        assert csrc.log_chunks_used(log[0]) > log[1]      # it did overflow
+        rows = []
+        parts = csrc.volume_render_backward_replay_parts(spec, src, opt, gout, out, log, 4,
+                                                         lambda x: rows.append(x.numel()))
+        assert len(rows) == 4 and sum(rows) == parts.numel()
+        assert P.grad_excess(parts.double().cpu().numpy(), marched["grad"], orc["grad_abs"],
+                             GRAD_TOL_REF) <= 2.5
+        csrc.check_device_status()
     finally:
+        csrc.log_estimate(wait=True)
         csrc._items_per_ray = old
         csrc._LOG_SLACK_CHUNKS = slack
+        case["tree"].to("cpu")
+
+
+def test_edits_between_forward_and_backward(cuda_device):
+    # The reference's backward recomputes everything from the current `data`
+    # (svox/renderer.py:66-72 keeps only the spec objects).  Here the forward's result and
+    # item log are reused, so an edit in between must be noticed: a write through the tree's
+    # own setters makes the backward march again from the new values, and an in-place edit of
+    # the returned render (which the saved copy would silently disagree with) raises.
+    case = CASES["shell_sh9_rays"]()
+    tree = case["tree"].to(cuda_device)
+    try:
+        r = P._renderer(tree, case)
+        rays = svox.Rays(*[t.to(cuda_device) for t in case["rays"]])
+        gout = case["grad_out"].to(cuda_device)
+        tree.zero_grad(set_to_none=True)
+        out = r(rays)
+        with torch.no_grad():
+            tree[torch.arange(0, tree.n_leaves, 3), -1:] = 7.5    # every third leaf's density
+        out.backward(gout)
+        got = tree.data.grad.clone()
+        tree.zero_grad(set_to_none=True)
+        r(rays).backward(gout)                            # forward and backward on the new data
+        want = tree.data.grad
+        assert (got - want).abs().max().item() <= 1e-5 * want.abs().max().item()
+        out = r(rays)
+        out.clamp_(0.0, 0.5)
+        with pytest.raises(RuntimeError):
+            out.backward(gout)
+        csrc.check_device_status()
+    finally:
+        case["tree"].to("cpu")
 
 
 def test_toy_example_known_answer(cuda_device):
