@@ -462,11 +462,14 @@ def run_train(a):
 
     if world > 1:
         set_variant("allreduce_after_backward")
+        csrc.reserve_sms(a.overlap_reserve)      # the collective runs beside every kernel now
         for i in range(warm):
             step_pipelined(i)
         drain()
         ms = H.timed(step_pipelined, a.steps, finish=drain)
-        variants["allreduce_under_next_step"] = {"ms_per_step": ms, "value": Q / ms / 1e3}
+        csrc.reserve_sms(0)
+        variants["allreduce_under_next_step"] = {"ms_per_step": ms, "value": Q / ms / 1e3,
+                                                 "reserved_sms": a.overlap_reserve}
 
     # ---- correctness of the multi-GPU step (outside the timed region) ----------------------
     check = None

@@ -169,9 +169,8 @@ int svoxb_volume_render_image_prepared(const svoxb_tree* tree, const svoxb_camer
  * of marching the rays and reading the leaf records again: it sorts the
  * samples by leaf range (scratch from the stream's memory pool, 32 bytes per
  * sample) and reduces the gradient range by range so that it stays in L2.
- * Only for octrees with SH colour in three channels, sigma_thresh =
- * stop_thresh = 0 and no density_softplus (else SVOXB_ERR_FORMAT /
- * SVOXB_ERR_OPTION).  `data` must not change between the two calls.
+ * Only for octrees with SH colour in three channels and sigma_thresh =
+ * stop_thresh = 0 (else SVOXB_ERR_FORMAT / SVOXB_ERR_OPTION).  `data` must not change between the two calls.
  *
  * A log that was too small must not be replayed.  `chunks_used` says who
  * checks that:
@@ -279,7 +278,9 @@ int svoxb_item_log_used(const int32_t* log, int64_t* chunks_used, void* stream);
  * anything is launched.
  *
  * The first call on a device looks up the array's device address
- * (cudaGetSymbolAddress); make that first call outside any stream capture.
+ * (cudaGetSymbolAddress); make that first call outside any stream capture,
+ * and from one host thread (the look-up is cached without a lock; threads
+ * racing on a device's first call would all store the same address).
  * All calls share the one array.  Each call overwrites the parts it reads, so
  * nothing has to be cleared between calls, but two calls whose kernels
  * overlap on the GPU (different streams, no ordering between them) race on
@@ -312,6 +313,13 @@ const char* svoxb_strerror(int status);
 /* Text of the last CUDA runtime error seen by this library on the calling
  * thread (empty string if none). */
 const char* svoxb_last_cuda_error(void);
+
+/* Leave `n` multiprocessors without a block in the library's persistent kernels (the
+ * march, the passes of the replay backward), for kernels of the caller that run beside
+ * them on another stream -- typically a collective that reduces the previous step's
+ * gradient while this step computes (no counterpart in the reference).  Process-wide,
+ * takes effect at the next launch; returns the previous value; n < 0 only queries. */
+int svoxb_reserve_sms(int n);
 
 /* Library version, "major.minor.patch". */
 const char* svoxb_version(void);

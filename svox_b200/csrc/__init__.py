@@ -427,7 +427,7 @@ def log_eligible(tree, opt):
     return (opt.format == FORMAT_SH and tree.data.shape[1] == 2
             and tree.data.shape[4] == 3 * opt.basis_dim + 1
             and opt.sigma_thresh == 0.0 and opt.stop_thresh == 0.0
-            and not opt.density_softplus and tree.data.dtype == torch.float32)
+            and tree.data.dtype == torch.float32)
 
 
 def _log_alloc(n_rays, device):
@@ -694,6 +694,12 @@ def check_device_status():
     st = device_status(clear=True)
     if st:
         _raise(st, "device_status")
+
+
+def reserve_sms(n):
+    """Leave ``n`` multiprocessors to other kernels (a collective on another stream) in the
+    library's persistent kernels; returns the previous setting (``n < 0``: query only)."""
+    return int(library().svoxb_reserve_sms(C.c_int(int(n))))
 
 
 def version():

@@ -21,6 +21,13 @@ __device__ int g_status = 0;  // the library is a single translation unit
 
 __device__ __forceinline__ void report(int code) { atomicMax(&g_status, code); }
 
+// 16-byte vector reduction into global memory (addr 16-byte aligned).
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b),
+                 "f"(c), "f"(d)
+                 : "memory");
+}
+
 constexpr int kMaxDescent = 40;  // levels; far beyond any float-resolvable depth
 
 // clamp_coord of the reference (svox/csrc/include/common.cuh:36-41): the bound
@@ -152,5 +159,6 @@ struct Tuning {
     int render_bricks = 1;   // queue kernels: bricks below the leaf table
 };
 extern Tuning g_tuning;
+extern int g_reserved_sms;
 
 }  // namespace svoxb

@@ -10,6 +10,7 @@
 namespace svoxb {
 
 Tuning g_tuning;
+int g_reserved_sms = 0;  // multiprocessors the persistent grids leave without a block
 
 static thread_local char t_cuda_error[256] = "";
 

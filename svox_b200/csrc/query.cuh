@@ -89,6 +89,44 @@ query_kernel(TreeArgs tr, TopTable top, const float* __restrict__ pts, int64_t Q
     if (wb >= Q) return;
     const int K = (MODE == 0) ? tr.K : Kg;
     const int nvalid = (int)((Q - wb) < 32 ? (Q - wb) : 32);
+    if (MODE == 1) {
+        // Backward: add row p of the upstream gradient into the record of point p's leaf.  A
+        // record is K floats at 4-byte alignment, so each is cut into at most 3 single floats
+        // up to the next 16-byte boundary, whole 16-byte words (one vector reduction each,
+        // a quarter of the requests of scalar atomics) and at most 3 single floats behind
+        // them.  Lanes take these pieces of the warp's 32 records round robin.
+        const int per_point = 6 + (K >> 2);        // 3 head + K/4 word + 3 tail places
+        const bool vec_ok = (reinterpret_cast<uintptr_t>(grad_data) & 15) == 0;
+        const int n_units = nvalid * per_point;
+        for (int base = 0; base < n_units; base += 32) {       // warp-uniform trip count
+            const int u = base + lane;
+            const int p = u < n_units ? u / per_point : 0, j = u - p * per_point;
+            const int64_t s = __shfl_sync(0xffffffffu, slot, p);
+            if (u >= n_units || s < 0) continue;
+            const int64_t first = s * K;                       // destination, in floats
+            int head = vec_ok ? (int)((4 - (first & 3)) & 3) : 0;
+            if (head > K) head = K;
+            const int words = vec_ok ? (K - head) >> 2 : 0;
+            const float* __restrict__ src = grad_out + (wb + p) * K;
+            if (j < 3) {
+                if (j < head && j < K) atomicAdd(grad_data + first + j, __ldg(src + j));
+            } else if (j < 3 + (K >> 2)) {
+                const int w = j - 3;
+                if (w < words) {
+                    const int e = head + 4 * w;
+                    red_add_v4(grad_data + first + e, __ldg(src + e), __ldg(src + e + 1),
+                               __ldg(src + e + 2), __ldg(src + e + 3));
+                } else if (!vec_ok) {                           // unaligned buffer: scalars
+                    for (int e = 4 * w; e < 4 * w + 4 && e < K; ++e)
+                        atomicAdd(grad_data + first + e, __ldg(src + e));
+                }
+            } else {
+                const int e = (vec_ok ? head + 4 * words : 4 * (K >> 2)) + (j - 3 - (K >> 2));
+                if (e < K) atomicAdd(grad_data + first + e, __ldg(src + e));
+            }
+        }
+        return;
+    }
     const int total = nvalid * K;
     int p = 0, e = lane;  // element j = p*K + e of the warp's (nvalid, K) block
     while (e >= K) { e -= K; ++p; }
@@ -106,24 +144,15 @@ query_kernel(TreeArgs tr, TopTable top, const float* __restrict__ pts, int64_t Q
             dst[u] = -1;
             v[u] = 0.f;
             if (j < total && s >= 0) {
-                if (MODE == 0) {
-                    v[u] = __ldg(tr.data + s * K + e);
-                    dst[u] = wb * K + j;
-                } else {
-                    v[u] = __ldg(grad_out + wb * K + j);
-                    dst[u] = s * K + e;
-                }
+                v[u] = __ldg(tr.data + s * K + e);
+                dst[u] = wb * K + j;
             }
             e += 32;
             while (e >= K) { e -= K; ++p; }
         }
 #pragma unroll
-        for (int u = 0; u < kBatch; ++u) {
-            if (dst[u] >= 0) {
-                if (MODE == 0) values_out[dst[u]] = v[u];
-                else atomicAdd(grad_data + dst[u], v[u]);
-            }
-        }
+        for (int u = 0; u < kBatch; ++u)
+            if (dst[u] >= 0) values_out[dst[u]] = v[u];
     }
 }
 

@@ -266,12 +266,6 @@ __device__ __forceinline__ void load_record(const float* __restrict__ rec, float
     }
 }
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b),
-                 "f"(c), "f"(d)
-                 : "memory");
-}
-
 template <int K, bool VEC>
 __device__ __forceinline__ void scatter_record(float* __restrict__ g, const float* __restrict__ v) {
     if (VEC) {

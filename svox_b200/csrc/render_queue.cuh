@@ -69,9 +69,9 @@ struct RecordShape {
 //   [kLogHeads + b]        items whose leaf slot falls into bin b (= slot >> shift)
 //   chunk c at kLogChunks + c * kLogChunkWords: 12 rows of 32 words,
 //     row 0: word 0 = items in the chunk
-//     rows 1-11, one word per item: slot, ray, weight, T after, delta_t*delta_scale,
-//     sigmoid of the three channels, colour sums of the ray up to and including
-//     the item (three channels)
+//     rows 1-11, one word per item: slot, ray, weight, T after, delta_t*delta_scale
+//     (times the derivative of the density's softplus, if that is on), sigmoid of the
+//     three channels, colour sums of the ray up to and including the item (three channels)
 // With the partial colour sums every item is self-contained: the reference's
 // running `accum` after item k (svox/csrc/rt_kernel.cu:462-471) equals
 // <grad_out, out> - <grad_out, partial sums>, so the backward can take the
@@ -348,7 +348,14 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
     const int base = top.level;  // level of the jump table (0: none)
     const float big = (float)(1 << kCoordBits);
     const uint64_t pol_keep = l2_policy_keep(), pol_stream = l2_policy_stream();
+#if defined(SVOXB_EXP_RECORDS_NORMAL)
+    uint64_t pol_rec;
+    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pol_rec));
+#elif defined(SVOXB_EXP_RECORDS_LAST)
+    const uint64_t pol_rec = pol_keep;
+#else
     const uint64_t pol_rec = pol_stream;
+#endif
 
     // ---- per-lane state -------------------------------------------------------
     // A lane marches one ray (the CURRENT one) and may still have items queued for
@@ -820,13 +827,21 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                                                                 ((iz >> b) & 1));
                     float sigma = (e == kOccupied) ? __ldg(tr.data + (size_t)slot * K + (K - 1))
                                                    : __uint_as_float((uint32_t)e & 0x7fffffffu);
-                    if (opt.density_softplus) sigma = softplus_m1(sigma);
+                    dd = delta_t * r.delta_scale;
+                    if (opt.density_softplus) {
+                        // the log's step length carries d softplus / d raw density, the one
+                        // factor the replayed density gradient needs from the raw value
+                        // (svox/csrc/rt_kernel.cu:469-470)
+                        if (LOG) dd *= sigmoid_ref(sigma - 1);
+                        sigma = softplus_m1(sigma);
+                    }
                     const float att = BWD ? expf(-delta_t * sigma * r.delta_scale)
                                           : expf(-delta_t * r.delta_scale * sigma);
                     weight = light * (1.f - att);
                     light *= att;
-                    dd = delta_t * r.delta_scale;
+#ifndef SVOXB_EXP_NO_S
                     item = true;
+#endif
                     if (!BWD && light <= opt.stop_thresh) {
                         stopped = true;
                         done = true;

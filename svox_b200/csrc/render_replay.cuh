@@ -109,7 +109,8 @@ __global__ void replay_pack_rays_kernel(TreeArgs tr, Source src, svoxb_render_op
 template <int BLOCK, int CPW, int MINB, bool HESS>   // CPW: chunks per warp and block step
 __global__ void __launch_bounds__(BLOCK, MINB)
 replay_bin_kernel(svoxb_render_options opt, const int32_t* __restrict__ log, int64_t n_chunks,
-                  int64_t capacity_chunks, int64_t n_rays, ReplayBins b) {
+                  int64_t capacity_chunks, int64_t n_rays, ReplayBins b,
+                  const float* __restrict__ data, int K) {
     constexpr int WARPS = BLOCK / 32;
     {
         // the chunks the forward really wrote (n_chunks is the host's upper bound); none of
@@ -160,6 +161,14 @@ replay_bin_kernel(svoxb_render_options opt, const int32_t* __restrict__ log, int
                 const float gg[3] = {ra.x, ra.y, ra.z}, oo[3] = {ra.w, rb.x, rb.y};
                 vd[j][0] = rb.z; vd[j][1] = rb.w; vd[j][2] = rc.x;
                 float total_color = 0.f, accum = 0.f;
+                // Gauss-Newton diagonal with a softplus density: the reference adds, per
+                // channel, (d out / d raw)^2 + (d out / d density) * softplus'' with its own
+                // formula for the second term (svox/csrc/rt_kernel.cu:683-693); the logged
+                // step length already holds the factor softplus' = s
+                float one_minus_s = 0.f;
+                if (HESS && opt.density_softplus)
+                    one_minus_s = 1.f - sigmoid_ref(__ldg(data + (int64_t)(uint32_t)slot[j] * K +
+                                                         (K - 1)) - 1);
 #pragma unroll
                 for (int chn = 0; chn < 3; ++chn) {
                     const float sg = __int_as_float(ch[32 * (6 + chn) + lane]);
@@ -174,7 +183,7 @@ replay_bin_kernel(svoxb_render_options opt, const int32_t* __restrict__ log, int
                         f[j][chn] = wk * sg * (1.0 - sg) * d_rgb_pad;
                         const float ds = dd * ((sg * d_rgb_pad - opt.rgb_padding) * T -
                                                (oo[chn] - part));
-                        total_color += ds * ds;
+                        total_color += ds * ds + ds * one_minus_s;
                     }
                 }
                 gs[j] = HESS ? total_color : dd * (total_color * T - accum);

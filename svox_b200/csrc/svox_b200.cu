@@ -63,7 +63,9 @@ static int persistent_grid(Kernel kernel, int block, size_t smem, int64_t n_gran
     int per_sm = 0;
     SVOXB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, block, smem));
     if (per_sm < 1) per_sm = 1;
-    int64_t g = (int64_t)sm_count() * per_sm;
+    int sms = sm_count() - g_reserved_sms;     // see svoxb_reserve_sms
+    if (sms < 1) sms = 1;
+    int64_t g = (int64_t)sms * per_sm;
     const int64_t need = (n_gran * 32 + block - 1) / block;  // blocks that can get a granule each
     if (g > need) g = need;
     if (g < 1) g = 1;
@@ -242,7 +244,8 @@ static int replay_begin(const RenderCall& c, const Source& src, int64_t chunks, 
         auto run_bin = [&](auto k, int block) {
             int s2 = persistent_grid(k, block, 0, chunks, &grid);
             if (s2 == SVOXB_OK)
-                k<<<grid, block, 0, c.stream>>>(c.opt, c.log, chunks, c.log_capacity, c.Q, b);
+                k<<<grid, block, 0, c.stream>>>(c.opt, c.log, chunks, c.log_capacity, c.Q, b,
+                                                c.tree->data, c.tree->K);
             return s2;
         };
         st = hess ? run_bin(replay_bin_kernel<128, 2, 12, true>, 128)
@@ -650,8 +653,7 @@ int svoxb_volume_render_image_backward(const svoxb_tree* tree, const svoxb_camer
 static int log_eligible(const svoxb_tree* t, const svoxb_render_options* o, const float* grad) {
     if (o->format != SVOXB_FORMAT_SH || t->K != 3 * o->basis_dim + 1 || t->N != 2)
         return SVOXB_ERR_FORMAT;
-    if (o->sigma_thresh != 0.f || o->stop_thresh != 0.f || o->density_softplus)
-        return SVOXB_ERR_OPTION;
+    if (o->sigma_thresh != 0.f || o->stop_thresh != 0.f) return SVOXB_ERR_OPTION;
     if (t->M >= (1LL << 28)) return SVOXB_ERR_TOO_LARGE;
     if (t->K % 4 == 0 && ((uintptr_t)t->data % 16 != 0 || (uintptr_t)grad % 16 != 0))
         return SVOXB_ERR_FORMAT;
@@ -980,6 +982,12 @@ const char* svoxb_strerror(int status) {
 }
 
 const char* svoxb_last_cuda_error(void) { return t_cuda_error; }
+
+int svoxb_reserve_sms(int n) {
+    const int before = g_reserved_sms;
+    if (n >= 0) g_reserved_sms = n;
+    return before;
+}
 
 const char* svoxb_version(void) { return "0.1.0"; }
 

@@ -273,8 +273,9 @@ class VolumeRenderer(nn.Module):
         ``1/2 sum_r (C_hat(r) - C(r))^2`` (svox/renderer.py:324-349).
 
         -> ``colors (B, 3), grad (shape of tree.data), diag_hessian (shape of tree.data)``.
-        The diagonal is the squared norm of the Jacobian's columns, as in the reference.
-        Octrees with SH colour, without density_softplus (the route through the item log).
+        The diagonal is the squared norm of the Jacobian's columns, as in the reference
+        (with ``density_softplus`` plus the reference's own second-order term for the density).
+        Octrees with SH colour in three channels (the route through the item log).
         """
         self._require_cuda(True)
         return self._se_grad(_rays_spec_from_rays(rays), colors, False)
@@ -294,8 +295,7 @@ class VolumeRenderer(nn.Module):
         tree = self.tree._spec()
         if not _C.log_eligible(tree, opt):
             raise NotImplementedError(
-                "se_grad needs an octree (N = 2) with SH colour, zero thresholds and no "
-                "density_softplus")
+                "se_grad needs an octree (N = 2) with SH colour in three channels")
         with torch.no_grad():
             colors = colors.to(device=self.tree.data.device, dtype=self.tree.data.dtype)
             for _ in range(4):      # a log that was too small is enlarged and the render redone

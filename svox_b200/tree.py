@@ -256,69 +256,162 @@ class N3Tree(nn.Module):
         """
         return WeightAccumulator(self, op)
 
+    # The checkpoint is a flat npz whose keys, dtypes and meanings are the reference's file
+    # format (svox/svox.py:835-865, 899-938): (key, how to read it off a tree, how to put it
+    # back).  ``data`` is stored as float16; ``invradius3`` replaced a scalar ``invradius`` in
+    # older files; ``n_free``, ``data_format`` and ``extra_data`` may be absent.
+    _NPZ_FIELDS = (
+        ("data_dim", lambda t: t.data_dim, lambda t, v, dev: setattr(t, "data_dim", int(v))),
+        ("child", lambda t: t.child.cpu(),
+         lambda t, v, dev: setattr(t, "child", torch.from_numpy(v).to(dev))),
+        ("parent_depth", lambda t: t.parent_depth.cpu(),
+         lambda t, v, dev: setattr(t, "parent_depth", torch.from_numpy(v).to(dev))),
+        ("n_internal", lambda t: t._n_internal.cpu().item(),
+         lambda t, v, dev: t._n_internal.fill_(v.item())),
+        ("n_free", lambda t: t._n_free.cpu().item(), lambda t, v, dev: t._n_free.fill_(v.item())),
+        ("invradius3", lambda t: t.invradius.cpu(),
+         lambda t, v, dev: setattr(t, "invradius",
+                                   torch.from_numpy(v.astype(np.float32)).to(dev))),
+        ("offset", lambda t: t.offset.cpu(),
+         lambda t, v, dev: setattr(t, "offset", torch.from_numpy(v.astype(np.float32)).to(dev))),
+        ("depth_limit", lambda t: t.depth_limit,
+         lambda t, v, dev: setattr(t, "depth_limit", int(v))),
+        ("geom_resize_fact", lambda t: t.geom_resize_fact,
+         lambda t, v, dev: setattr(t, "geom_resize_fact", float(v))),
+        ("data", lambda t: t.data.data.half().cpu().numpy(), None),     # handled by load()
+        ("data_format", lambda t: None if t.data_format is None else repr(t.data_format),
+         lambda t, v, dev: setattr(t, "data_format", DataFormat(v.item()))),
+        ("extra_data", lambda t: None if t.extra_data is None else t.extra_data.cpu(),
+         lambda t, v, dev: setattr(t, "extra_data", torch.from_numpy(v).to(dev))),
+    )
+
     def save(self, path, shrink=True, compress=True):
+        """Write the tree as an npz in the reference's checkpoint format (``data`` as fp16)."""
         if shrink:
             self.shrink_to_fit()
-        out = {
-            "data_dim": self.data_dim,
-            "child": self.child.cpu(),
-            "parent_depth": self.parent_depth.cpu(),
-            "n_internal": self._n_internal.cpu().item(),
-            "n_free": self._n_free.cpu().item(),
-            "invradius3": self.invradius.cpu(),
-            "offset": self.offset.cpu(),
-            "depth_limit": self.depth_limit,
-            "geom_resize_fact": self.geom_resize_fact,
-            "data": self.data.data.half().cpu().numpy(),
-        }
-        if self.data_format is not None:
-            out["data_format"] = repr(self.data_format)
-        if self.extra_data is not None:
-            out["extra_data"] = self.extra_data.cpu()
-        (np.savez_compressed if compress else np.savez)(path, **out)
+        blob = {}
+        for key, read, _ in self._NPZ_FIELDS:
+            value = read(self)
+            if value is not None:
+                blob[key] = value
+        (np.savez_compressed if compress else np.savez)(path, **blob)
 
     @classmethod
     def load(cls, path, device="cpu", dtype=torch.float32, map_location=None):
+        """Read a checkpoint written by this package or by the reference."""
         if map_location is not None:
             warn("map_location has been renamed to device and may be removed")
             device = map_location
         assert dtype in (torch.float32, torch.float64), "Unsupported dtype"
         z = np.load(path)
         tree = cls(dtype=dtype, device=device)
-        tree.data_dim = int(z["data_dim"])
-        tree.child = torch.from_numpy(z["child"]).to(device)
-        tree.N = tree.child.shape[-1]
-        tree.parent_depth = torch.from_numpy(z["parent_depth"]).to(device)
-        tree._n_internal.fill_(z["n_internal"].item())
-        if "invradius3" in z.files:
-            tree.invradius = torch.from_numpy(z["invradius3"].astype(np.float32)).to(device)
-        else:
+        tree.data_format = tree.extra_data = None
+        tree._n_free.zero_()
+        for key, _, write in cls._NPZ_FIELDS:
+            if write is not None and key in z.files:
+                write(tree, z[key], device)
+        if "invradius3" not in z.files:                  # files older than per-axis radii
             tree.invradius.fill_(z["invradius"].item())
-        tree.offset = torch.from_numpy(z["offset"].astype(np.float32)).to(device)
-        tree.depth_limit = int(z["depth_limit"])
-        tree.geom_resize_fact = float(z["geom_resize_fact"])
+        tree.N = tree.child.shape[-1]
         tree.data = nn.Parameter(torch.from_numpy(z["data"].astype(np.float32)).to(
             device=device, dtype=dtype))
-        tree._n_free.fill_(z["n_free"].item() if "n_free" in z.files else 0)
-        tree.data_format = DataFormat(z["data_format"].item()) if "data_format" in z.files \
-            else None
-        tree.extra_data = torch.from_numpy(z["extra_data"]).to(device) \
-            if "extra_data" in z.files else None
         tree._invalidate()
         return tree
 
-    def shrink_to_fit(self):
-        """Drop unused capacity (no merged nodes to defragment in this package)."""
+    # ------------------------------------------------------------------
+    # Coarsening: frontier nodes (all of whose cells are leaves), merging them back into
+    # their parents, and compaction (svox/svox.py:436-580, 620-632, 745-788).
+    @property
+    def _frontier(self):
+        """Ids of the live nodes all of whose cells are leaves, ascending."""
+        if self._last_frontier is None:
+            n = self.n_internal
+            only_leaves = (self.child[:n] == 0).flatten(1).all(dim=1)
+            alive = self.parent_depth[:n, 0] != -1
+            self._last_frontier = torch.nonzero(only_leaves & alive).flatten()
+        return self._last_frontier
+
+    @property
+    def n_frontier(self):
+        return self._frontier.shape[0]
+
+    @property
+    def frontier_depth(self):
+        return self.parent_depth[self._frontier, 1]
+
+    def reduce_frontier(self, op=torch.mean, dim=None, grad=False):
+        """``op`` over the N^3 leaf records of every frontier node: ``op(x, dim=1)`` with ``x``
+        of shape ``(n_frontier, N^3, data_dim)`` (or the selected channels ``dim``)."""
+        src = self.data if grad else self.data.data
+        x = src[self._frontier].reshape(-1, self.N ** 3, self.data_dim)
+        return op(x if dim is None else x[..., dim], dim=1)
+
+    def max_frontier(self, dim=None, grad=False):
+        return self.reduce_frontier(lambda x, dim: torch.max(x, dim=dim)[0], dim=dim, grad=grad)
+
+    def diam_frontier(self, dim=None, grad=False, scale=1.0):
+        """Largest pairwise distance between the leaf records of every frontier node."""
+        def diameter(x, dim):
+            if x.ndim == 2:
+                x = x[:, :, None]
+            pair = torch.cdist(x * scale, x * scale)          # (B, N^3, N^3)
+            return pair.flatten(1).max(dim=1)[0]
+        return self.reduce_frontier(diameter, dim=dim, grad=grad)
+
+    def merge(self, frontier_sel=None, op=torch.mean):
+        """Turn the selected frontier nodes back into leaves of their parents, whose record
+        becomes ``op`` over the children's.  The freed nodes stay in the arrays (marked with
+        -1) until ``shrink_to_fit``.  Returns False if nothing was selected."""
         if self._lock_tree_structure:
             raise RuntimeError("Tree locked")
-        if self._n_free.item() != 0:
-            raise NotImplementedError("defragmenting merged nodes is not part of this package")
-        new_cap = self.n_internal
+        if self.n_internal - self._n_free.item() <= 1:
+            raise RuntimeError("Cannot merge root node")
+        nodes = self._frontier if frontier_sel is None else self._frontier[frontier_sel]
+        nodes = nodes.reshape(-1)
+        if nodes.numel() == 0:
+            return False
+        with torch.no_grad():
+            merged = op(self.data.data[nodes].reshape(-1, self.N ** 3, self.data_dim), dim=1)
+            if isinstance(merged, tuple):                 # torch.max / torch.min return pairs
+                merged = merged[0]
+            parent_slot = self.parent_depth[nodes, 0].long()
+            self.data.data.view(-1, self.data_dim)[parent_slot] = merged
+            self.child.view(-1)[parent_slot] = 0
+            self.parent_depth[nodes] = -1
+            self.child[nodes] = -1
+            self._n_free += nodes.shape[0]
+        self._invalidate()
+        return True
+
+    def shrink_to_fit(self):
+        """Drop unused capacity and the nodes freed by ``merge``: the surviving nodes move up
+        in order, links and parent slots are renumbered.  Re-creates the ``data`` parameter
+        (an optimizer holding the old one must be rebuilt)."""
+        if self._lock_tree_structure:
+            raise RuntimeError("Tree locked")
+        n_int, n_free = self.n_internal, int(self._n_free.item())
+        new_cap = n_int - n_free
         if new_cap >= self.capacity:
             return False
-        self.data = nn.Parameter(self.data.data[:new_cap].clone())
-        self.child = self.child[:new_cap].clone()
-        self.parent_depth = self.parent_depth[:new_cap].clone()
+        with torch.no_grad():
+            if n_free == 0:
+                keep = slice(0, new_cap)
+            else:
+                n3 = self.N ** 3
+                dead = self.parent_depth[:n_int, 0] == -1
+                new_id = torch.cumsum(~dead, dim=0) - 1          # id of a survivor after the move
+                keep = torch.nonzero(~dead).flatten()
+                # every survivor but the root: its parent's link and its own parent slot
+                kids = keep[keep != 0]
+                pslot = self.parent_depth[kids, 0].long()
+                pnode = torch.div(pslot, n3, rounding_mode="floor")
+                self.child.view(-1)[pslot] = (new_id[kids] - new_id[pnode]).to(torch.int32)
+                self.parent_depth[kids, 0] = (new_id[pnode] * n3 + pslot % n3).to(torch.int32)
+                self._n_internal.fill_(new_cap)
+                self._n_free.zero_()
+            self.data = nn.Parameter(self.data.data[keep].clone())
+            self.child = self.child[keep].clone()
+            self.parent_depth = self.parent_depth[keep].clone()
         self._invalidate()
         return True
 

@@ -266,9 +266,40 @@ def c4_full_rays():
     return _base(tree, "rays", rays=rays, mse_targets=targets)
 
 
-# Full-size cases: minutes of CPU work for the oracle, GPU tests only.
-FULL_CASES = {f.__name__: f for f in [c4_full_rays]}
-FULL_OUT_STRIDE = 16   # their fixtures keep the colours of every 16th ray
+def c2_full_query():
+    """The query benchmark itself: uniform tree of 256^3 leaves, SH16 (3.76 GB of data, byte
+    offsets beyond 2^31), 2^24 uniform points, N(0,1) upstream gradient."""
+    tree, pts = W.config2()
+    gout = torch.randn(pts.shape[0], tree.data_dim, generator=_g(121))
+    return _base(tree, "query", points=pts, grad_out=gout)
+
+
+def _full_view(cfg, width, height, focal, **kw):
+    tree, cams = cfg(n_views=1)
+    return _base(tree, "image", camera=dict(c2w=cams[0], width=width, height=height, fx=focal,
+                                            fy=focal), **kw)
+
+
+def c3_full_image():
+    """First view of the sparse-shell forward benchmark: 512^3 shell, SH16, 800x800,
+    stop_thresh 1e-2."""
+    return _full_view(W.config3, 800, 800, 1111.0, attrs=dict(stop_thresh=1e-2))
+
+
+def c5_full_image():
+    """First view of the large multi-view benchmark: three shells refined to 1024^3, SH16
+    (12 GB of data, element offsets beyond 2^31), 1920x1080, step 5e-4, fast=True."""
+    return _full_view(W.config5, 1920, 1080, 1600.0, render=dict(step_size=5e-4), fast=True)
+
+
+# Full-size cases: minutes of CPU work for the oracle, GPU tests only.  Their fixtures keep a
+# strided sample of the outputs: the colours of every FULL_OUT_STRIDE-th ray, every
+# FULL_PIXEL_STRIDE-th pixel (row-major), the leaf ids of every FULL_ID_STRIDE-th point.
+FULL_CASES = {f.__name__: f for f in [c4_full_rays, c2_full_query, c3_full_image,
+                                      c5_full_image]}
+FULL_OUT_STRIDE = 16
+FULL_PIXEL_STRIDE = 97
+FULL_ID_STRIDE = 4096
 
 # Cases whose fixtures are cheap enough to check on the CPU in the default test run.
 BIG = {"c4_sample_rays"}

@@ -30,8 +30,8 @@ colours of tests/parity_util.se_grad_colors as ``ref_cuda_se_grad_<case>.npz``:
     grad_*         digest of the gradient
     hess_*         digest of the Gauss-Newton diagonal
 
-The full-size cases (FULL_CASES, "--full") keep the colours of every
-FULL_OUT_STRIDE-th ray only.
+The full-size cases (FULL_CASES, "--full") keep a strided sample of the outputs
+(see tests/golden/cases.py).
 
 Usage: python tests/golden/make_ref_cuda_golden.py [out_dir] [case ...]
        python tests/golden/make_ref_cuda_golden.py [out_dir] --full
@@ -47,7 +47,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(HERE))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 
-from golden.cases import CASES, FULL_CASES, FULL_OUT_STRIDE  # noqa: E402
+from golden.cases import (CASES, FULL_CASES, FULL_ID_STRIDE, FULL_OUT_STRIDE,  # noqa: E402
+                          FULL_PIXEL_STRIDE)
 import parity_util as P  # noqa: E402
 
 
@@ -66,7 +67,8 @@ def weights(out_dir):
         print(name, "weights: non-zero", idx.size, "of", s.size, flush=True)
 
 
-SE_GRAD_CASES = ["c1_rays", "shell_sh9_rays", "shell_sh16_image", "opt_comp_range"]
+SE_GRAD_CASES = ["c1_rays", "shell_sh9_rays", "shell_sh16_image", "opt_comp_range",
+                 "opt_softplus_pad_bg"]
 
 
 def se_grad(out_dir):
@@ -94,9 +96,13 @@ def main():
     for name in names:
         case = table[name]()
         res = P.run_ref_cuda(case)
-        blob = {"out": res["out"][::FULL_OUT_STRIDE] if full else res["out"]}
+        blob = {"out": res["out"]}
+        if full and case["kind"] == "rays":
+            blob["out"] = res["out"][::FULL_OUT_STRIDE]
+        elif full and case["kind"] == "image":
+            blob["out"] = res["out"].reshape(-1, res["out"].shape[-1])[::FULL_PIXEL_STRIDE]
         if res["ids"] is not None:
-            blob["ids"] = res["ids"]
+            blob["ids"] = res["ids"][::FULL_ID_STRIDE] if full else res["ids"]
             blob["out"] = res["out"][:P.QUERY_ROWS_KEPT]
         if res["grad"] is not None:
             blob.update(P.grad_digest(res["grad"]))

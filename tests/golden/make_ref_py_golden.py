@@ -4,11 +4,21 @@ Imports the unmodified reference package from a checkout (first argument, or
 the default below; it has no compiled extension there, so every call takes the
 pure-PyTorch path of svox/svox.py:224-268 and svox/renderer.py:205-282) and
 stores its outputs for the seeded cases it can express: zero thresholds,
-unit-cube world box, SH / RGBA colour.  Trees are built with the reference's
-own N3Tree from the same seeds and checked to be structurally identical to
-the ones tests/golden/cases.py builds.
+unit-cube world box, SH / RGBA colour.  For these the tensors of the trees
+that tests/golden/cases.py builds are copied into the reference's N3Tree class
+(so both sides render the same bits).
 
     ref_py_<case>.npz: out, [ids], [grad_* digest]
+
+With ``--structure`` it instead builds trees with the REFERENCE's own
+constructor, ``refine`` and view selection, and writes them with the
+reference's own ``N3Tree.save``:
+
+    ref_py_saved_tree_<name>.npz   (the reference's checkpoint format, as written by it)
+
+tests/test_tree_structure.py loads those files with svox_b200.N3Tree.load,
+rebuilds the same trees with svox_b200 from the same recipe (RECIPES below)
+and compares node numbering and file contents.
 
 Work-arounds that leave the reference untouched: inputs are cloned (the CPU
 path normalises ``dirs`` and clamps points in place), and the background is
@@ -16,6 +26,7 @@ passed as an object whose ``__rmul__`` broadcasts per ray (the CPU path adds
 a (B,) vector to a (B,3) tensor, svox/renderer.py:281).
 
 Usage: python tests/golden/make_ref_py_golden.py [reference_root] [case ...]
+       python tests/golden/make_ref_py_golden.py [reference_root] --structure
 """
 import os
 import sys
@@ -44,12 +55,73 @@ class _Background:
         return t[:, None] * self.v
 
 
+# Recipes of the structure fixtures.  Either library follows them with its own N3Tree:
+# constructor, then for every (lo, hi, repeats): refine `repeats` times the leaves whose
+# centre lies at distance [lo, hi] from the centre of the cube, then seeded values.
+RECIPES = {
+    "octree": dict(ctor=dict(N=2, data_format="SH4", init_refine=2),
+                   refines=[(0.25, 0.40, 2), (0.30, 0.33, 1)], seed=201),
+    "n3": dict(ctor=dict(N=3, data_format="RGBA", init_refine=1, radius=[0.5, 1.0, 2.0],
+                         center=[0.0, 0.5, -1.0]),
+               refines=[(0.0, 0.30, 1)], seed=202),
+}
+
+
+def build_recipe(lib, recipe):
+    """``lib``: the reference package or svox_b200 (same API)."""
+    tree = lib.N3Tree(**recipe["ctor"])
+    for lo, hi, repeats in recipe["refines"]:
+        view = tree[:]
+        centre = view.corners_local + 0.5 * view.lengths_local[:, None]
+        dist = (centre - 0.5).norm(dim=1)
+        tree[(dist >= lo) & (dist <= hi)].refine(repeats)
+    gen = torch.Generator().manual_seed(recipe["seed"])
+    with torch.no_grad():
+        tree.data.data.copy_(torch.randn(tree.data.shape, generator=gen))
+    return tree
+
+
+def coarsen(tree):
+    """The merge both libraries perform on a recipe tree: every second frontier node whose
+    largest last-channel value is below the median goes back into its parent (mean of the
+    children), then the arrays are compacted."""
+    top = tree.max_frontier(dim=-1)
+    pick = torch.zeros(tree.n_frontier, dtype=torch.bool)
+    pick[::2] = True
+    pick &= top <= top.median()
+    tree.merge(pick)
+    tree.shrink_to_fit()
+    return pick
+
+
+def structure(ref):
+    for name, recipe in RECIPES.items():
+        tree = build_recipe(ref, recipe)
+        tree.check_integrity()
+        path = os.path.join(HERE, f"ref_py_saved_tree_{name}.npz")
+        tree.save(path)                      # the reference's own writer
+        print(name, "nodes", tree.n_internal, "leaves", tree.n_leaves, "->", path, flush=True)
+        # frontier queries and a merge + compaction, all by the reference's own code
+        blob = dict(frontier=tree._frontier.numpy(), frontier_depth=tree.frontier_depth.numpy(),
+                    mean=tree.reduce_frontier().numpy(), top=tree.max_frontier(dim=-1).numpy(),
+                    diam=tree.diam_frontier().numpy())
+        blob["pick"] = coarsen(tree).numpy()
+        tree.check_integrity()
+        np.savez_compressed(os.path.join(HERE, f"ref_py_frontier_{name}.npz"), **blob)
+        tree.save(os.path.join(HERE, f"ref_py_saved_tree_{name}_merged.npz"), shrink=False)
+        print(name, "merged", int(blob["pick"].sum()), "of", blob["pick"].size,
+              "frontier nodes ->", tree.n_internal, "nodes", flush=True)
+
+
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 and os.path.isdir(sys.argv[1]) else "/root/reference"
+    from oracle.build_ref import reference_root
+    root = sys.argv[1] if len(sys.argv) > 1 and os.path.isdir(sys.argv[1]) else reference_root()
     names = [a for a in sys.argv[1:] if a in CASES] or PY_CASES
     sys.path.insert(0, root)
     warnings.filterwarnings("ignore")
     import svox as ref
+    if "--structure" in sys.argv:
+        return structure(ref)
 
     for name in names:
         case = CASES[name]()

@@ -231,21 +231,59 @@ def grad_digest(grad, n_sample=20000, seed=0):
 
 def grad_excess(grad, ref_grad, grad_abs, rel_tol=1e-4):
     """Worst |g - ref| in units of the tolerance rel_tol * sum|contributions|
-    (floored at 1e-4 of the largest gradient); <= 1 means within tolerance."""
+    (floored at 1e-4 of the largest gradient); <= 1 means within tolerance.  Used against the
+    CPU oracle, whose libm expf differs from CUDA's in the last bit."""
     g, r = np.asarray(grad, np.float64).reshape(-1), np.asarray(ref_grad, np.float64).reshape(-1)
     scale = np.maximum(np.asarray(grad_abs, np.float64).reshape(-1), 1e-4 * np.abs(r).max())
     return float((np.abs(g - r) / (rel_tol * scale)).max())
 
 
+# Gradient against the reference's CUDA extension.  Every gradient element is a sum of float
+# atomics, so the reference does not even reproduce itself: two runs of it on the same inputs
+# (fixtures: grad_val, grad_val2) differ by up to 2e-7 of an element's summed |contributions|,
+# and where the contributions cancel that is far more than 1e-4 of the element's VALUE (the
+# full-size training step: 6e-3 between the reference's own two runs).  So "within 1e-4
+# relative" is asserted in the two forms that a float sum can meet:
+#   * the whole gradient: max |g - ref| / max |ref| <= GRAD_MAXNORM_TOL (ten times tighter
+#     than 1e-4; observed < 1e-6);
+#   * every element: |g - ref| <= 1e-4 |ref| + GRAD_CANCEL_TOL * sum|contributions|.
+#     Observed: < 7e-6 of the summed magnitude (the kernels also take the running sum of the
+#     reference's second march from the forward's result, a few more roundings than a
+#     reordering of atomics), the reference against itself 3e-7.
+GRAD_MAXNORM_TOL = 1e-5
+GRAD_REL_TOL = 1e-4
+GRAD_CANCEL_TOL = 2e-5
+
+
+def grad_deviation(grad, ref_grad, grad_abs):
+    """-> (max-norm error, worst element in units of its allowance); both must be <= 1 after
+    dividing the first by GRAD_MAXNORM_TOL."""
+    g, r = np.asarray(grad, np.float64).reshape(-1), np.asarray(ref_grad, np.float64).reshape(-1)
+    top = np.abs(r).max()
+    if top == 0:
+        return float(np.abs(g).max()), 0.0
+    err = np.abs(g - r)
+    allow = GRAD_REL_TOL * np.abs(r) + GRAD_CANCEL_TOL * np.maximum(
+        np.asarray(grad_abs, np.float64).reshape(-1), 1e-4 * top)
+    return float(err.max() / top), float((err / allow).max())
+
+
+def assert_grad_matches_reference(grad, ref_grad, grad_abs, what="gradient"):
+    maxnorm, worst = grad_deviation(grad, ref_grad, grad_abs)
+    assert maxnorm <= GRAD_MAXNORM_TOL, f"{what}: max-norm error {maxnorm:.3g}"
+    assert worst <= 1.0, f"{what}: an element is off by {worst:.2f} x its allowance"
+    return maxnorm, worst
+
+
 def grad_error(grad, ref_grad):
-    """max |g - ref| / max |ref| and the worst element-wise relative error over
-    elements with |ref| > 1e-3 * max|ref|."""
+    """max |g - ref| / max |ref| and the worst element-wise relative error over elements with
+    |ref| > 1e-6 * max|ref| (reported, not asserted: see above)."""
     g, r = np.asarray(grad, np.float64).reshape(-1), np.asarray(ref_grad, np.float64).reshape(-1)
     scale = np.abs(r).max()
     if scale == 0:
         return float(np.abs(g).max()), 0.0
     err = np.abs(g - r)
-    big = np.abs(r) > 1e-3 * scale
+    big = np.abs(r) > 1e-6 * scale
     rel = float((err[big] / np.abs(r[big])).max()) if big.any() else 0.0
     return float(err.max() / scale), rel
 

@@ -3,8 +3,10 @@
 Compared against
 * the committed fixtures of the reference's CUDA extension (same seeded
   inputs): leaf ids and values bit-exact, colours within 1e-5 absolute
-  (the north-star tolerance; observed ~1e-6), gradients within 1e-4 of the
-  summed magnitude per element (float-atomics ordering);
+  (observed ~1e-6), gradients as parity_util.assert_grad_matches_reference
+  says (1e-5 of the largest element for the whole gradient; per element 1e-4
+  relative plus 2e-5 of the element's summed contributions, which is what
+  sums of float atomics can agree to);
 * the CPU oracle, on the same cases and on cases without fixtures;
 * size-independent properties at full benchmark size.
 """
@@ -23,7 +25,6 @@ from svox_b200 import workloads as W
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
 RGB_TOL = 1e-5
-GRAD_TOL_REF = 1e-4      # vs reference CUDA (shares CUDA's expf)
 GRAD_TOL_ORACLE = 1e-3   # vs CPU oracle (libm expf, amplified by cancellation)
 
 
@@ -53,10 +54,8 @@ def test_case_against_reference_fixture_and_oracle(name, cuda_device):
         assert P.grad_excess(mine["grad"], orc["grad"], orc["grad_abs"], GRAD_TOL_ORACLE) <= 1.0
         if z is not None and "grad_idx" in z.files:
             idx = z["grad_idx"]
-            worst = P.grad_excess(mine["grad"].reshape(-1)[idx], z["grad_val"],
-                                  orc["grad_abs"].reshape(-1)[idx], GRAD_TOL_REF)
-            # both sides are float-atomics sums in arbitrary order
-            assert worst <= 2.5, f"gradient off by {worst:.2f} x tolerance"
+            P.assert_grad_matches_reference(mine["grad"].reshape(-1)[idx], z["grad_val"],
+                                            orc["grad_abs"].reshape(-1)[idx], name)
 
 
 @pytest.mark.parametrize("name", ["c1_rays", "shell_sh9_rays", "opt_fast", "shell_sh16_image",
@@ -69,11 +68,12 @@ def test_two_march_backward_matches_single_march(name, cuda_device):
     b = P.run_product(case, cuda_device, single_march=False)["grad"]
     orc = P.run_oracle(case)
     assert P.grad_excess(b, orc["grad"], orc["grad_abs"], GRAD_TOL_ORACLE) <= 1.0
-    assert P.grad_excess(a, b, orc["grad_abs"], GRAD_TOL_REF) <= 2.5
+    P.assert_grad_matches_reference(a, b, orc["grad_abs"])
 
 
 @pytest.mark.parametrize("name", ["c1_rays", "shell_sh9_rays", "shell_sh16_image", "aniso_rays",
-                                  "aniso_image", "sh1_rays", "sh25_rays", "opt_comp_range"])
+                                  "aniso_image", "sh1_rays", "sh25_rays", "opt_comp_range",
+                                  "opt_softplus_pad_bg"])
 def test_replay_backward_matches_marching_backward(name, cuda_device):
     # With gradients enabled the forward logs its contributing samples and the
     # backward replays the log; the marching backward must give the same gradient.
@@ -83,7 +83,7 @@ def test_replay_backward_matches_marching_backward(name, cuda_device):
     assert np.array_equal(a["out"], b["out"])          # logging does not change the render
     orc = P.run_oracle(case)
     assert P.grad_excess(a["grad"], orc["grad"], orc["grad_abs"], GRAD_TOL_ORACLE) <= 1.0
-    assert P.grad_excess(a["grad"], b["grad"], orc["grad_abs"], GRAD_TOL_REF) <= 2.5
+    P.assert_grad_matches_reference(a["grad"], b["grad"], orc["grad_abs"])
 
 
 @pytest.mark.parametrize("name", list(EXTRA_CASES))
@@ -110,11 +110,11 @@ def test_bricks_and_bin_size_do_not_change_results(name, cuda_device):
         assert lib.svoxb_test_knob(7, 0) == 0
         plain = P.run_product(case, cuda_device)
         assert np.array_equal(base["out"], plain["out"])
-        assert P.grad_excess(base["grad"], plain["grad"], orc["grad_abs"], GRAD_TOL_REF) <= 2.5
+        P.assert_grad_matches_reference(base["grad"], plain["grad"], orc["grad_abs"])
         assert lib.svoxb_test_knob(7, 1) == 0 and lib.svoxb_test_knob(5, 1) == 0
         fine = P.run_product(case, cuda_device)
         assert np.array_equal(base["out"], fine["out"])
-        assert P.grad_excess(base["grad"], fine["grad"], orc["grad_abs"], GRAD_TOL_REF) <= 2.5
+        P.assert_grad_matches_reference(base["grad"], fine["grad"], orc["grad_abs"])
     finally:
         lib.svoxb_test_knob(7, 1)
         lib.svoxb_test_knob(5, 16)
@@ -146,7 +146,7 @@ def test_weight_accumulation_matches_oracle(name, op, cuda_device):
 
 
 @pytest.mark.parametrize("name", ["c1_rays", "shell_sh9_rays", "shell_sh16_image",
-                                  "opt_comp_range", "aniso_rays"])
+                                  "opt_comp_range", "aniso_rays", "opt_softplus_pad_bg"])
 def test_se_grad_matches_oracle_and_reference_fixture(name, cuda_device):
     # VolumeRenderer.se_grad / se_grad_persp (svox/renderer.py:324-385): colour, gradient and
     # Gauss-Newton diagonal of the squared error against seeded colours.
@@ -156,17 +156,24 @@ def test_se_grad_matches_oracle_and_reference_fixture(name, cuda_device):
     assert np.abs(mine["out"] - orc["out"]).max() <= RGB_TOL
     assert P.grad_excess(mine["grad"], orc["grad"], orc["grad_abs"], GRAD_TOL_ORACLE) <= 1.0
     hmax = np.abs(orc["hess"]).max()
-    assert np.all(np.abs(mine["hess"] - orc["hess"]) <= 1e-3 * orc["hess"] + 1e-4 * hmax)
+    # (with density_softplus the reference's diagonal has a signed term: entries can be negative)
+    herr = np.abs(mine["hess"] - orc["hess"]) / (1e-3 * np.abs(orc["hess"]) + 1e-4 * hmax)
+    assert herr.max() <= 1.0, f"Gauss-Newton diagonal off by {herr.max():.2f} x its allowance"
     path = os.path.join(GOLD, f"ref_cuda_se_grad_{name}.npz")
     if os.path.exists(path):
         z = np.load(path)
         assert np.abs(mine["out"] - z["out"]).max() <= RGB_TOL
         gi, hi = z["grad_idx"], z["hess_idx"]
-        worst = P.grad_excess(mine["grad"].reshape(-1)[gi], z["grad_val"],
-                              orc["grad_abs"].reshape(-1)[gi], GRAD_TOL_REF)
-        assert worst <= 2.5, f"gradient off by {worst:.2f} x tolerance"
+        # The reference's se_grad kernel adds the density gradient of every sample once per
+        # colour channel (three atomics of partial terms, svox/csrc/rt_kernel.cu:683-698);
+        # here the channels are summed before the one addition.  Same value, other roundings
+        # of terms that nearly cancel: 3e-4 of an element's summed |contributions| (observed
+        # up to 1e-4), where the plain backward is held to 2e-5.
+        assert P.grad_excess(mine["grad"].reshape(-1)[gi], z["grad_val"],
+                             orc["grad_abs"].reshape(-1)[gi], 3e-4) <= 1.0
         h, want = mine["hess"].reshape(-1)[hi], z["hess_val"]
-        assert np.all(np.abs(h - want) <= 1e-4 * want + 1e-5 * np.abs(want).max())
+        herr = np.abs(h - want) / (1e-4 * np.abs(want) + 1e-5 * np.abs(want).max())
+        assert herr.max() <= 1.0, f"diagonal vs reference off by {herr.max():.2f} x its allowance"
 
 
 @pytest.mark.parametrize("name,image", [("shell_sh9_rays", False), ("shell_sh16_image", True)])
@@ -265,7 +272,7 @@ def test_item_log_overflow_falls_back(cuda_device):
         a = P.run_product(case, cuda_device)
         assert csrc.log_estimate(wait=True) > 1.0       # the estimate was raised for next time
         assert csrc._LogWatch.last_used > csrc._LogWatch.last_cap
-        assert P.grad_excess(a["grad"], marched["grad"], orc["grad_abs"], GRAD_TOL_REF) <= 2.5
+        P.assert_grad_matches_reference(a["grad"], marched["grad"], orc["grad_abs"])
 
         csrc._items_per_ray = 0.0
         tree = case["tree"].to(cuda_device)
@@ -279,8 +286,8 @@ def test_item_log_overflow_falls_back(cuda_device):
         parts = csrc.volume_render_backward_replay_parts(spec, src, opt, gout, out, log, 4,
                                                          lambda x: rows.append(x.numel()))
         assert len(rows) == 4 and sum(rows) == parts.numel()
-        assert P.grad_excess(parts.double().cpu().numpy(), marched["grad"], orc["grad_abs"],
-                             GRAD_TOL_REF) <= 2.5
+        P.assert_grad_matches_reference(parts.double().cpu().numpy(), marched["grad"],
+                                        orc["grad_abs"])
         csrc.check_device_status()
     finally:
         csrc.log_estimate(wait=True)
@@ -424,7 +431,7 @@ def test_linearity_of_backward_in_upstream_gradient(cuda_device):
         case["grad_out"] = g * scale
         grads.append(P.run_product(case, cuda_device)["grad"])
     orc = P.run_oracle(case)
-    assert P.grad_excess(2.0 * grads[0], grads[1], orc["grad_abs"], GRAD_TOL_REF) <= 2.5
+    P.assert_grad_matches_reference(2.0 * grads[0], grads[1], orc["grad_abs"])
 
 
 def test_query_backward_is_a_histogram(cuda_device):
