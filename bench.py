@@ -53,11 +53,15 @@ METRICS = {
     "image3": "Mrays/s render_persp forward (SH deg 3, 512^3 shell, 800x800 views)",
     "image5": "Mrays/s render_persp forward (SH deg 3, three shells at 1024^3, 1920x1080 views)",
 }
-# DRAM bytes (read + write) per launch of the dominant kernels of the training step, from an
-# ncu capture of a 2^17-ray launch scaled by 8 to the 2^20-ray launch (traffic grows with the
-# rays).  Printed only together with `traffic_source`, which names the capture.
-NCU_TRAFFIC = None
-NCU_TRAFFIC_SOURCE = None
+# DRAM bytes (read + write) of one launch of the dominant kernel of the training step (the
+# logged forward march), from an ncu capture of a 2^17-ray launch (1.938 GB read + 0.353 GB
+# written) scaled by 8 to the 2^20-ray launch: its traffic grows with the rays.  The backward's
+# does not (the gradient is read and written once whatever the number of rays), so it has no
+# scaled figure.  Printed only together with `traffic_source`, which names the capture.
+NCU_TRAFFIC = {"forward": 8 * (1.938027e9 + 0.352580e9), "backward": None}
+NCU_TRAFFIC_SOURCE = ("ncu --set full of render_queue_kernel<9,640,ForwardLogged> at 2^17 rays "
+                      "x 8 (profiles/training_step_rays131072_ncu_full.md); valid for the "
+                      "kernel as of library version " + "0.2.0")
 
 
 def parse():
@@ -555,6 +559,8 @@ def run_train(a):
                       "the previous step computes (double-buffered)"}
 
     peak, peak_src = peaks()
+    # the captured traffic describes this workload on one GPU with the kernels of one version
+    traffic_ok = Q == 1 << 20 and world == 1 and csrc.version() in NCU_TRAFFIC_SOURCE
     line = {
         "metric": METRICS["train"], "value": Q / ms_step / 1e3, "unit": UNIT, "n_gpus": world,
         "steps": a.steps, "warmup": warm, "ms_per_step": ms_step,
@@ -572,9 +578,8 @@ def run_train(a):
         "roofline": {"bound": "hbm", "kernel": "render_queue_kernel, logged forward (volume_render)",
                      "achieved": fwd_bytes / world / ms_fwd / 1e6, "peak": peak, "unit": "GB/s",
                      "frac": fwd_bytes / world / ms_fwd / 1e6 / peak,
-                     "traffic": NCU_TRAFFIC["forward"] if NCU_TRAFFIC and Q == 1 << 20
-                     and world == 1 else None,
-                     "traffic_source": NCU_TRAFFIC_SOURCE if NCU_TRAFFIC else None,
+                     "traffic": NCU_TRAFFIC["forward"] if traffic_ok else None,
+                     "traffic_source": NCU_TRAFFIC_SOURCE if traffic_ok else None,
                      "peak_source": peak_src, "ms_per_launch": ms_fwd,
                      "algorithmic_bytes_per_launch": fwd_bytes / world},
         # The backward replays the forward's item log.  `model_frac` divides the bytes of the
@@ -590,18 +595,16 @@ def run_train(a):
                               "bytes_of_this_design_per_launch": replay_bytes / world,
                               "model_frac": bwd_bytes / world / ms_bwd / 1e6 / peak,
                               "algorithmic_bytes_per_launch": bwd_bytes / world,
-                              "traffic": NCU_TRAFFIC["backward"] if NCU_TRAFFIC and Q == 1 << 20
-                              and world == 1 else None,
-                              "traffic_source": NCU_TRAFFIC_SOURCE if NCU_TRAFFIC else None,
+                              "traffic": None,
                               "ms_per_launch": ms_bwd},
         "roofline_step": {"algorithmic_bytes": fwd_bytes + bwd_bytes,
                           "achieved": (fwd_bytes + bwd_bytes) / ms_step / 1e6,
                           "frac": (fwd_bytes + bwd_bytes) / ms_step / 1e6 / (peak * world)},
         "e2e": e2e,
-        # per step: forward = log head clear, annotate, leaf table, brick assign, brick fill,
-        # march; backward = prefix, ray pack, bin, scatter (one launch per part), and the five
-        # launches of the marching fallback, which return at once unless the log overflowed
-        "gpu_launches": (6 + 3 + (a.overlap_parts if best == "allreduce_inside_backward" else 1)
+        # per step: forward = annotate, leaf table, brick assign, brick fill, march; backward =
+        # prefix, ray pack, bin, scatter (one launch per part), and the five launches of the
+        # marching fallback, which return at once unless the log overflowed
+        "gpu_launches": (5 + 3 + (a.overlap_parts if best == "allreduce_inside_backward" else 1)
                          + 5) * a.steps,
         "clocks": clocks,
     }

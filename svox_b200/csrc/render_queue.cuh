@@ -115,7 +115,7 @@ constexpr int kBrickCells = 512;
 constexpr int kBrickWords = kBrickCells + 64;
 constexpr int32_t kBrickFlag = 1 << 30;
 constexpr int64_t kBrickMaxNodes = 1 << 25;  // slots must fit 28 bits
-constexpr int kMaxBricks = 1 << 16;
+constexpr int kMaxBricks = 1 << 17;
 
 // Annotated child entry: > 0 link; 0 leaf failing the density test; < 0 leaf
 // passing it, with the density's float bits in the low 31 bits when the
@@ -348,14 +348,9 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
     const int base = top.level;  // level of the jump table (0: none)
     const float big = (float)(1 << kCoordBits);
     const uint64_t pol_keep = l2_policy_keep(), pol_stream = l2_policy_stream();
-#if defined(SVOXB_EXP_RECORDS_NORMAL)
-    uint64_t pol_rec;
-    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pol_rec));
-#elif defined(SVOXB_EXP_RECORDS_LAST)
-    const uint64_t pol_rec = pol_keep;
-#else
+    // records stream through L2 (evict-first): measured 0.2 ms faster per launch than the
+    // default policy and than evict-last, which push the tree's index out of L2
     const uint64_t pol_rec = pol_stream;
-#endif
 
     // ---- per-lane state -------------------------------------------------------
     // A lane marches one ray (the CURRENT one) and may still have items queued for
@@ -839,9 +834,7 @@ render_queue_kernel(TreeArgs tr, Source src, svoxb_render_options opt, TopTable 
                                           : expf(-delta_t * r.delta_scale * sigma);
                     weight = light * (1.f - att);
                     light *= att;
-#ifndef SVOXB_EXP_NO_S
                     item = true;
-#endif
                     if (!BWD && light <= opt.stop_thresh) {
                         stopped = true;
                         done = true;

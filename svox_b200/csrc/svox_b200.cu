@@ -159,18 +159,11 @@ static int launch_queue_fitted(const RenderCall& c, const Source& src, const Tre
     const size_t per_warp = c.backward ? sizeof(WarpQueue<K, kModeBackward>)
                             : c.log    ? sizeof(WarpQueue<K, kModeForwardLogged>)
                                        : sizeof(WarpQueue<K, kModeForward>);
-#ifdef SVOXB_EXP_BLOCK768
-    int want = 768;
-#else
     int want = 640;
-#endif
     // static shared memory: the ticket counter, and the bin histogram of the logged forward
     const size_t fixed = 64 + (c.log ? (size_t)kMaxBins * sizeof(int) : 0);
     while (want > 256 && top_bytes + (size_t)(want / 32) * per_warp + fixed > kMaxSmem) want -= 128;
     if constexpr (BD <= 9) {
-#ifdef SVOXB_EXP_BLOCK768
-        if (want >= 768) return launch_queue_block<BD, 768>(c, src, tr, top, top_bytes);
-#endif
         if (want >= 640) return launch_queue_block<BD, 640>(c, src, tr, top, top_bytes);
     }
     if constexpr (BD <= 16) {
@@ -346,8 +339,11 @@ struct QueueScratch {
         l.words = l.head + (size_t)l.cap * kBrickWords;
         return l;
     }
-    static int default_level() {
-        return 6;
+    // Level of the leaf table: 6 (64^3 cells, 1 MB); 7 (128^3, 8 MB) for trees of several
+    // million nodes, whose leaves lie up to ten levels deep: the bricks below the table then
+    // still reach them in one step.
+    static int default_level(const svoxb_tree* t) {
+        return t->M >= (4LL << 20) ? 7 : 6;
     }
     void adopt(const Layout& l, int32_t* mem) {
         annotated = mem;
@@ -397,10 +393,10 @@ template <int BD, class Source>
 static int launch_queue(const RenderCall& c, const Source& src) {
     QueueScratch scratch;
     if (c.prepared != nullptr && !c.backward) {
-        scratch.adopt(QueueScratch::layout(c.tree, QueueScratch::default_level()), c.prepared);
+        scratch.adopt(QueueScratch::layout(c.tree, QueueScratch::default_level(c.tree)), c.prepared);
     } else {
         const int st = scratch.build(c.tree, c.backward ? 0.f : c.opt.sigma_thresh,
-                                     c.opt.density_softplus, QueueScratch::default_level(),
+                                     c.opt.density_softplus, QueueScratch::default_level(c.tree),
                                      c.stream, nullptr, c.gate);
         if (st) return st;
     }
@@ -566,7 +562,7 @@ static int queue_eligible(const svoxb_tree* t, const svoxb_render_options* o) {
 
 int64_t svoxb_render_scratch_words(const svoxb_tree* tree) {
     if (!tree || tree->M < 1 || tree->N != 2) return 0;
-    return (int64_t)QueueScratch::layout(tree, QueueScratch::default_level()).words;
+    return (int64_t)QueueScratch::layout(tree, QueueScratch::default_level(tree)).words;
 }
 
 int svoxb_render_scratch_build(const svoxb_tree* tree, const svoxb_render_options* opt,
@@ -575,7 +571,7 @@ int svoxb_render_scratch_build(const svoxb_tree* tree, const svoxb_render_option
     int st = queue_eligible(tree, opt);
     if (st) return st;
     QueueScratch q;
-    return q.build(tree, opt->sigma_thresh, opt->density_softplus, QueueScratch::default_level(),
+    return q.build(tree, opt->sigma_thresh, opt->density_softplus, QueueScratch::default_level(tree),
                    (cudaStream_t)stream, scratch);
 }
 
@@ -989,7 +985,7 @@ int svoxb_reserve_sms(int n) {
     return before;
 }
 
-const char* svoxb_version(void) { return "0.1.0"; }
+const char* svoxb_version(void) { return "0.2.0"; }
 
 // Test hook (include/svox_b200_testing.h): key 5 = MB of gradient one replay bin spans,
 // key 7 = bricks below the render leaf table on / off.
