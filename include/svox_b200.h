@@ -58,6 +58,14 @@ typedef struct {
     float* weight_accum;
     int32_t weight_accum_max;
     int32_t reserved_;
+    /* Lobe parameters of the Gaussian colour bases (TreeSpec::extra_data,
+     * svox/csrc/rt_kernel.cu:120-140), row-major (extra_rows, extra_cols); used
+     * only by SVOXB_FORMAT_SG (row i: sharpness, lobe axis xyz; extra_cols >= 4)
+     * and SVOXB_FORMAT_ASG (row i: two bandwidths, then the x, y and z axes of the
+     * lobe's frame; extra_cols >= 11), with extra_rows >= basis_dim.  Null otherwise. */
+    const float* extra_data;
+    int32_t extra_rows;
+    int32_t extra_cols;
 } svoxb_tree;
 
 /* Replaces RaysSpec (svox/csrc/include/data_spec.hpp:51-64): three (Q, 3)
@@ -147,8 +155,9 @@ int svoxb_volume_render_image_backward(const svoxb_tree* tree, const svoxb_camer
  * Here the caller keeps it: svoxb_render_scratch_words int32 words of device
  * memory, filled once by svoxb_render_scratch_build and passed to any number
  * of svoxb_volume_render[_image]_prepared calls -- valid until the tree or those
- * two options change.  Octrees with SH colour in three channels
- * only (else SVOXB_ERR_FORMAT: use the plain entry points). */
+ * two options change.  Octrees with three colour channels of 1, 4, 9, 16 or
+ * 25 basis functions (SH, SG or ASG) only (else SVOXB_ERR_FORMAT: use the
+ * plain entry points). */
 int64_t svoxb_render_scratch_words(const svoxb_tree* tree);
 int svoxb_render_scratch_build(const svoxb_tree* tree, const svoxb_render_options* opt,
                                int32_t* scratch, void* stream);
@@ -169,7 +178,8 @@ int svoxb_volume_render_image_prepared(const svoxb_tree* tree, const svoxb_camer
  * of marching the rays and reading the leaf records again: it sorts the
  * samples by leaf range (scratch from the stream's memory pool, 32 bytes per
  * sample) and reduces the gradient range by range so that it stays in L2.
- * Only for octrees with SH colour in three channels and sigma_thresh =
+ * Only for octrees with three colour channels of 1, 4, 9, 16 or 25 basis
+ * functions (SH, SG or ASG) and sigma_thresh =
  * stop_thresh = 0 (else SVOXB_ERR_FORMAT / SVOXB_ERR_OPTION).  `data` must not change between the two calls.
  *
  * A log that was too small must not be replayed.  `chunks_used` says who

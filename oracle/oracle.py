@@ -15,7 +15,8 @@ FORMAT_RGBA, FORMAT_SH, FORMAT_SG, FORMAT_ASG = 0, 1, 2, 3
 class OrcTree(C.Structure):
     _fields_ = [("data", C.c_void_p), ("child", C.c_void_p), ("M", C.c_int64),
                 ("N", C.c_int32), ("K", C.c_int32),
-                ("offset", C.c_float * 3), ("scaling", C.c_float * 3)]
+                ("offset", C.c_float * 3), ("scaling", C.c_float * 3),
+                ("extra", C.c_void_p), ("extra_cols", C.c_int32)]
 
 
 class OrcOptions(C.Structure):
@@ -82,7 +83,7 @@ def _ptr(a):
 class Tree:
     """Borrowed view of the tree arrays: data (M,N,N,N,K) f32, child (M,N,N,N) i32."""
 
-    def __init__(self, data, child, offset=(0, 0, 0), scaling=(1, 1, 1)):
+    def __init__(self, data, child, offset=(0, 0, 0), scaling=(1, 1, 1), extra=None):
         self.data = _f32(data)
         self.child = np.ascontiguousarray(child, dtype=np.int32)
         assert self.data.ndim == 5 and self.child.ndim == 4
@@ -90,8 +91,11 @@ class Tree:
         self.K = self.data.shape[-1]
         self.offset = [float(x) for x in np.asarray(offset, dtype=np.float32)]
         self.scaling = [float(x) for x in np.asarray(scaling, dtype=np.float32)]
+        # lobe parameters of the SG / ASG colour bases, (basis_dim, 4 or 11)
+        self.extra = _f32(extra) if extra is not None and np.size(extra) else None
         self.c = OrcTree(_ptr(self.data), _ptr(self.child), self.M, self.N, self.K,
-                         (C.c_float * 3)(*self.offset), (C.c_float * 3)(*self.scaling))
+                         (C.c_float * 3)(*self.offset), (C.c_float * 3)(*self.scaling),
+                         _ptr(self.extra), self.extra.shape[1] if self.extra is not None else 0)
 
     @classmethod
     def from_n3tree(cls, tree, world=True):
@@ -100,9 +104,12 @@ class Tree:
         del n  # the kernels see the full capacity, as the reference's do
         data = tree.data.detach().cpu().numpy()
         child = tree.child.cpu().numpy()
+        extra = getattr(tree, "extra_data", None)
+        extra = extra.cpu().numpy() if extra is not None else None
         if world:
-            return cls(data, child, tree.offset.cpu().numpy(), tree.invradius.cpu().numpy())
-        return cls(data, child)
+            return cls(data, child, tree.offset.cpu().numpy(), tree.invradius.cpu().numpy(),
+                       extra=extra)
+        return cls(data, child, extra=extra)
 
 
 def options(step_size=1e-3, background_brightness=1.0, format=FORMAT_SH, basis_dim=1,

@@ -36,6 +36,8 @@
 
 #define ORC_FORMAT_RGBA 0
 #define ORC_FORMAT_SH 1
+#define ORC_FORMAT_SG 2
+#define ORC_FORMAT_ASG 3
 
 typedef struct {
     const float* data;     /* (M, N, N, N, K) */
@@ -45,6 +47,8 @@ typedef struct {
     int32_t K;
     float offset[3];
     float scaling[3];
+    const float* extra;    /* (basis_dim, extra_cols): lobe parameters of SG / ASG, else NULL */
+    int32_t extra_cols;
 } OrcTree;
 
 /* Field for field svox/csrc/include/data_spec.hpp:107-126. */
@@ -258,6 +262,34 @@ static void sh_basis(int basis_dim, const float* dir, float* out) {
 
 void orc_sh_basis(int basis_dim, const float* dir, float* out) { sh_basis(basis_dim, dir, out); }
 
+/* u.v as nvcc contracts u0*v0 + u1*v1 + u2*v2 (svox/csrc/rt_kernel.cu:103-107) */
+static inline float dot3(const float* u, const float* v) {
+    return g_fc.sh_basis ? fmaf(u[2], v[2], fmaf(u[1], v[1], u[0] * v[0]))
+                         : u[0] * v[0] + u[1] * v[1] + u[2] * v[2];
+}
+
+/* svox/csrc/rt_kernel.cu:110-184 (maybe_precalc_basis): SH, or the spherical-Gaussian (SG) and
+ * anisotropic spherical-Gaussian (ASG) lobes whose parameters are the rows of extra. */
+static void colour_basis(const OrcTree* tr, const OrcOptions* opt, const float* dir, float* out) {
+    const int n = opt->basis_dim;
+    if (opt->format == ORC_FORMAT_SH) {
+        sh_basis(n, dir, out);
+    } else if (opt->format == ORC_FORMAT_SG) {
+        for (int i = 0; i < n; ++i) {
+            const float* p = tr->extra + (int64_t)i * tr->extra_cols;
+            out[i] = expf(p[0] * (dot3(dir, p + 1) - 1.f)) / n;
+        }
+    } else if (opt->format == ORC_FORMAT_ASG) {
+        for (int i = 0; i < n; ++i) {
+            const float* p = tr->extra + (int64_t)i * tr->extra_cols;
+            const float S = dot3(dir, p + 8), dx = dot3(dir, p + 2), dy = dot3(dir, p + 5);
+            const float a = -p[0] * dx * dx, b = p[1] * dy;
+            const float e = g_fc.sh_basis ? fmaf(-b, dy, a) : a - b * dy;
+            out[i] = S * expf(e) / n;
+        }
+    }
+}
+
 /* svox/csrc/rt_kernel.cu:89-93 */
 static inline float norm3(const float* d) {
     float a = d[0] * d[0], b = d[1] * d[1];
@@ -357,7 +389,7 @@ static int trace_ray(const OrcTree* tr, const float* origin, float* dir, const f
     if (st) st->hit = 1;
     for (int j = 0; j < out_dim; ++j) out[j] = 0.f;
     float pos[3], basis_fn[25];
-    if (opt->format == ORC_FORMAT_SH) sh_basis(opt->basis_dim, vdir, basis_fn);
+    colour_basis(tr, opt, vdir, basis_fn);
     float light = 1.f, t = tmin, cube_sz;
     const float d_rgb_pad = 1 + 2 * opt->rgb_padding;
     while (t < tmax) {
@@ -445,7 +477,7 @@ static int trace_ray_backward(const OrcTree* tr, const float* grad_output, const
     if (!ray_setup(tr, origin, dir, invdir, &delta_scale, &tmin, &tmax)) return 0;
     if (st) st->hit = 1;
     float pos[3], basis_fn[25];
-    if (opt->format == ORC_FORMAT_SH) sh_basis(opt->basis_dim, vdir, basis_fn);
+    colour_basis(tr, opt, vdir, basis_fn);
     float accum = 0.0f;
     double accum_abs = 0.0; /* sum of |terms| of accum: the scale of its rounding error */
     const float d_rgb_pad = 1 + 2 * opt->rgb_padding;
@@ -647,7 +679,7 @@ static int trace_ray_se_grad(const OrcTree* tr, const float* origin, float* dir,
         return 0;
     }
     float pos[3], basis_fn[25];
-    if (opt->format == ORC_FORMAT_SH) sh_basis(opt->basis_dim, vdir, basis_fn);
+    colour_basis(tr, opt, vdir, basis_fn);
     const float d_rgb_pad = 1 + 2 * opt->rgb_padding;
     const int sh = opt->format != ORC_FORMAT_RGBA;
     for (int j = 0; j < out_dim; ++j) color_out[j] = 0.f;

@@ -27,7 +27,8 @@ class _CTree(C.Structure):
     _fields_ = [("data", C.c_void_p), ("child", C.c_void_p), ("offset", C.c_void_p),
                 ("scaling", C.c_void_p), ("M", C.c_int64), ("N", C.c_int32), ("K", C.c_int32),
                 ("weight_accum", C.c_void_p), ("weight_accum_max", C.c_int32),
-                ("reserved_", C.c_int32)]
+                ("reserved_", C.c_int32), ("extra_data", C.c_void_p),
+                ("extra_rows", C.c_int32), ("extra_cols", C.c_int32)]
 
 
 class _CRays(C.Structure):
@@ -197,9 +198,16 @@ def _pack_tree(tree):
         if tuple(wa.shape) != tuple(tree.child.shape) or wa.device != dev:
             raise RuntimeError("_weight_accum must have the shape and device of child")
         wa_ptr = wa.data_ptr()
+    ex = tree.extra_data
+    ex_ptr = ex_rows = ex_cols = 0
+    if ex is not None and ex.numel():
+        _check_input(ex, "extra_data")
+        if ex.dim() != 2 or ex.device != dev:
+            raise RuntimeError("extra_data must be (basis_dim, C) on the device of data")
+        ex_ptr, (ex_rows, ex_cols) = ex.data_ptr(), ex.shape
     return _CTree(d.data_ptr(), tree.child.data_ptr(), tree.offset.data_ptr(),
                   tree.scaling.data_ptr(), d.shape[0], d.shape[1], d.shape[4], wa_ptr,
-                  1 if tree._weight_accum_max else 0, 0)
+                  1 if tree._weight_accum_max else 0, 0, ex_ptr, ex_rows, ex_cols)
 
 
 def _pack_rays(rays, dev):
@@ -424,8 +432,8 @@ def log_estimate(wait=False):
 
 def log_eligible(tree, opt):
     """Whether the logged forward / replay backward pair applies to this call."""
-    return (opt.format == FORMAT_SH and tree.data.shape[1] == 2
-            and tree.data.shape[4] == 3 * opt.basis_dim + 1
+    return (opt.format != FORMAT_RGBA and opt.basis_dim in (1, 4, 9, 16, 25)
+            and tree.data.shape[1] == 2 and tree.data.shape[4] == 3 * opt.basis_dim + 1
             and opt.sigma_thresh == 0.0 and opt.stop_thresh == 0.0
             and tree.data.dtype == torch.float32)
 

@@ -29,11 +29,13 @@ struct TreeArgs {
     int32_t K;
     float* weight_accum;      // forward render only (null: off)
     int32_t weight_accum_max;
+    int32_t extra_cols;       // row length of `extra`
+    const float* __restrict__ extra;   // lobe parameters of the SG / ASG colour bases
 };
 
 static inline TreeArgs tree_args(const svoxb_tree* t) {
     return TreeArgs{t->data, t->child, t->offset, t->scaling, t->M, t->N, t->K,
-                    t->weight_accum, t->weight_accum_max};
+                    t->weight_accum, t->weight_accum_max, t->extra_cols, t->extra_data};
 }
 
 // One sample's weight into the accumulator of its leaf (svox/csrc/rt_kernel.cu:298-304).

@@ -229,11 +229,11 @@ struct alignas(16) ScatterSmem {
     alignas(16) float rows[32 * Shape::STRIDE + 4];
 };
 
-template <int BD, int BLOCK, bool HESS>
+template <int BD, int BLOCK, bool HESS, bool LOBES>
 __global__ void __launch_bounds__(BLOCK)
-replay_scatter_kernel(int64_t n_slots, svoxb_render_options opt, float* __restrict__ grad_data,
-                      const int32_t* __restrict__ log, ReplayBins b, int flags, int part,
-                      int n_parts) {
+replay_scatter_kernel(int64_t n_slots, svoxb_render_options opt, TreeArgs lobes,
+                      float* __restrict__ grad_data, const int32_t* __restrict__ log,
+                      ReplayBins b, int flags, int part, int n_parts) {
     constexpr int K = 3 * BD + 1;
     using Shape = RecordShape<K>;
     using SM = ScatterSmem<K>;
@@ -292,7 +292,7 @@ replay_scatter_kernel(int64_t n_slots, svoxb_render_options opt, float* __restri
             const float f[3] = {__int_as_float(pa.y), __int_as_float(pa.z), __int_as_float(pa.w)};
             const float vdir[3] = {__int_as_float(pb.y), __int_as_float(pb.z), __int_as_float(pb.w)};
             float basis[BD];
-            sh_basis<BD>(vdir, basis);
+            colour_basis<BD, LOBES>(lobes, opt, vdir, basis);
 #pragma unroll
             for (int k = 0; k < BD; ++k)
                 if (k < opt.min_comp || k > opt.max_comp) basis[k] = 0.f;

@@ -37,13 +37,28 @@ static int out_dim_of(const svoxb_tree* t, const svoxb_render_options& o) {
     return o.format != SVOXB_FORMAT_RGBA ? (t->K - 1) / o.basis_dim : t->K - 1;
 }
 
+// The records hold three colour channels of basis_dim coefficients each and a density, and
+// basis_dim is one of the sizes the specialised kernels are compiled for.
+static bool basis3(const svoxb_tree* t, const svoxb_render_options& o) {
+    const int b = o.basis_dim;
+    return o.format != SVOXB_FORMAT_RGBA && t->K == 3 * b + 1 &&
+           (b == 1 || b == 4 || b == 9 || b == 16 || b == 25);
+}
+
 static int validate_options(const svoxb_tree* t, const svoxb_render_options& o) {
     if (!(o.step_size >= 0.f)) return SVOXB_ERR_OPTION;
-    if (o.format == SVOXB_FORMAT_SG || o.format == SVOXB_FORMAT_ASG) return SVOXB_ERR_FORMAT;
-    if (o.format != SVOXB_FORMAT_RGBA && o.format != SVOXB_FORMAT_SH) return SVOXB_ERR_FORMAT;
-    if (o.format == SVOXB_FORMAT_SH) {
+    if (o.format < SVOXB_FORMAT_RGBA || o.format > SVOXB_FORMAT_ASG) return SVOXB_ERR_FORMAT;
+    if (o.format != SVOXB_FORMAT_RGBA) {
         const int b = o.basis_dim;
-        if (b != 1 && b != 4 && b != 9 && b != 16 && b != 25) return SVOXB_ERR_FORMAT;
+        if (o.format == SVOXB_FORMAT_SH) {
+            if (b != 1 && b != 4 && b != 9 && b != 16 && b != 25) return SVOXB_ERR_FORMAT;
+        } else {
+            // the reference keeps the basis in an array of 25 (svox/csrc/rt_kernel.cu:253)
+            if (b < 1 || b > 25) return SVOXB_ERR_FORMAT;
+            if (!t->extra_data) return SVOXB_ERR_NULL;
+            if (t->extra_rows < b || t->extra_cols < (o.format == SVOXB_FORMAT_SG ? 4 : 11))
+                return SVOXB_ERR_SHAPE;
+        }
         if (o.min_comp < 0 || o.max_comp >= b) return SVOXB_ERR_OPTION;
         if (t->K - 1 < b) return SVOXB_ERR_SHAPE;
     } else if (t->K < 2) {
@@ -57,7 +72,8 @@ static int validate_options(const svoxb_tree* t, const svoxb_render_options& o) 
 
 template <class Kernel>
 static int persistent_grid(Kernel kernel, int block, size_t smem, int64_t n_gran, unsigned* grid) {
-    if (smem > 48 * 1024)
+    // the 48 KB a kernel gets without asking cover its static shared memory too (up to 4 KB here)
+    if (smem > 40 * 1024)
         SVOXB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)smem));
     int per_sm = 0;
@@ -159,6 +175,8 @@ static int launch_queue_fitted(const RenderCall& c, const Source& src, const Tre
     const size_t per_warp = c.backward ? sizeof(WarpQueue<K, kModeBackward>)
                             : c.log    ? sizeof(WarpQueue<K, kModeForwardLogged>)
                                        : sizeof(WarpQueue<K, kModeForward>);
+    // the lobe bases are compiled for the smallest block only
+    if constexpr (Source::kLobes) return launch_queue_block<BD, 256>(c, src, tr, top, top_bytes);
     int want = 640;
     // static shared memory: the ticket counter, and the bin histogram of the logged forward
     const size_t fixed = 64 + (c.log ? (size_t)kMaxBins * sizeof(int) : 0);
@@ -179,6 +197,7 @@ struct ReplayJob {
     int32_t* base = nullptr;     // pool allocation
     const int32_t* log = nullptr;
     svoxb_render_options opt{};
+    TreeArgs lobes{};            // for the lobe parameters of an SG / ASG basis
     int64_t n_slots = 0, n_rays = 0, chunks = 0;
     int K = 0, basis_dim = 0, n_parts = 1, shift = 0, n_bins = 1;
     bool hess = false;   // Gauss-Newton diagonal instead of the gradient
@@ -219,6 +238,7 @@ static int replay_begin(const RenderCall& c, const Source& src, int64_t chunks, 
     job->base = base;
     job->log = c.log;
     job->opt = c.opt;
+    job->lobes = tree_args(c.tree);
     job->n_slots = c.tree->M * 8;
     job->n_rays = c.Q;
     job->chunks = chunks;
@@ -256,12 +276,12 @@ static int replay_begin(const RenderCall& c, const Source& src, int64_t chunks, 
 // Scatter of one part.  With `reserve_sms` > 0 that many SMs are left without a block
 // (for a collective that runs beside the scatter); small records then use one 1024-thread
 // block per SM, so that the SMs left out are really empty.
-template <int BD, int BLOCK, bool HESS>
+template <int BD, int BLOCK, bool HESS, bool LOBES = false>
 static int replay_scatter_block(const ReplayJob& job, int part, float* grad, int reserve_sms,
                                 cudaStream_t stream) {
     constexpr int K = 3 * BD + 1;
     const size_t smem = (size_t)(BLOCK / 32) * sizeof(ScatterSmem<K>);
-    auto k = replay_scatter_kernel<BD, BLOCK, HESS>;
+    auto k = replay_scatter_kernel<BD, BLOCK, HESS, LOBES>;
     unsigned grid = 1;
     int st = persistent_grid(k, BLOCK, smem, job.chunks, &grid);
     if (st) return st;
@@ -271,7 +291,7 @@ static int replay_scatter_block(const ReplayJob& job, int part, float* grad, int
         const int64_t most = ((int64_t)sms - reserve_sms) * per_sm;
         if ((int64_t)grid > most) grid = (unsigned)(most > 1 ? most : 1);
     }
-    k<<<grid, BLOCK, smem, stream>>>(job.n_slots, job.opt, grad, job.log, job.bins,
+    k<<<grid, BLOCK, smem, stream>>>(job.n_slots, job.opt, job.lobes, grad, job.log, job.bins,
                                     kReplayHints, part, job.n_parts);
     const cudaError_t e = cudaGetLastError();
     return e != cudaSuccess ? set_cuda_error(e) : SVOXB_OK;
@@ -280,6 +300,10 @@ static int replay_scatter_block(const ReplayJob& job, int part, float* grad, int
 template <int BD>
 static int replay_scatter_bd(const ReplayJob& job, int part, float* grad, int reserve_sms,
                              cudaStream_t stream) {
+    if (job.opt.format != SVOXB_FORMAT_SH)
+        return job.hess ? replay_scatter_block<BD, 512, true, true>(job, part, grad, 0, stream)
+                        : replay_scatter_block<BD, 512, false, true>(job, part, grad, reserve_sms,
+                                                                     stream);
     if (job.hess) return replay_scatter_block<BD, 512, true>(job, part, grad, 0, stream);
     if constexpr (BD <= 9) {
         if (reserve_sms > 0)
@@ -403,6 +427,8 @@ static int launch_queue(const RenderCall& c, const Source& src) {
     TreeArgs tr = tree_args(c.tree);
     tr.child = scratch.annotated;
     const TopTable top{scratch.table, scratch.level, scratch.bricks};
+    if (c.opt.format != SVOXB_FORMAT_SH)
+        return launch_queue_fitted<BD>(c, WithLobes<Source>{src}, tr, top);
     return launch_queue_fitted<BD>(c, src, tr, top);
 }
 
@@ -433,7 +459,7 @@ template <int BLOCK, class Source>
 static int dispatch_layout(const RenderCall& c, const Source& src, const TopTable& top,
                            bool in_smem, size_t smem) {
     const svoxb_tree* t = c.tree;
-    const bool sh3 = c.opt.format == SVOXB_FORMAT_SH && t->K == 3 * c.opt.basis_dim + 1;
+    const bool sh3 = basis3(t, c.opt) && c.opt.format == SVOXB_FORMAT_SH;
     if (!sh3) return launch_generic<BLOCK>(c, src, top, in_smem, smem);
     const bool aligned = ((uintptr_t)t->data % 16 == 0) &&
                          (!c.backward || (uintptr_t)c.grad_data % 16 == 0);
@@ -466,11 +492,11 @@ static int render_dispatch(const RenderCall& c, const Source& src) {
     if (c.Q == 0) return SVOXB_OK;
     if (c.backward ? !c.grad_out : !c.out) return SVOXB_ERR_NULL;
 
-    // Default path: the queue kernels, for octrees with SH colour in three
-    // channels whose buffers allow the record's word size.
+    // Default path: the queue kernels, for octrees with three colour channels of 1, 4, 9, 16
+    // or 25 basis functions whose buffers allow the record's word size.
     {
         const svoxb_tree* t = c.tree;
-        const bool sh3 = c.opt.format == SVOXB_FORMAT_SH && t->K == 3 * c.opt.basis_dim + 1;
+        const bool sh3 = basis3(t, c.opt);
         const bool aligned = ((uintptr_t)t->data % 16 == 0) &&
                              (!c.backward || (uintptr_t)c.grad_data % 16 == 0);
         if (sh3 && t->N == 2 && (aligned || t->K % 4 != 0) &&
@@ -553,7 +579,7 @@ static int queue_eligible(const svoxb_tree* t, const svoxb_render_options* o) {
     int st = validate_tree(t);
     if (st) return st;
     if ((st = validate_options(t, *o))) return st;
-    if (o->format != SVOXB_FORMAT_SH || t->K != 3 * o->basis_dim + 1 || t->N != 2)
+    if (!basis3(t, *o) || t->N != 2)
         return SVOXB_ERR_FORMAT;
     if (t->K % 4 == 0 && (uintptr_t)t->data % 16 != 0) return SVOXB_ERR_FORMAT;
     if (t->M >= (1LL << 28)) return SVOXB_ERR_TOO_LARGE;
@@ -647,7 +673,7 @@ int svoxb_volume_render_image_backward(const svoxb_tree* tree, const svoxb_camer
 
 // Whether a call can take the logged forward / replay backward pair.
 static int log_eligible(const svoxb_tree* t, const svoxb_render_options* o, const float* grad) {
-    if (o->format != SVOXB_FORMAT_SH || t->K != 3 * o->basis_dim + 1 || t->N != 2)
+    if (!basis3(t, *o) || t->N != 2)
         return SVOXB_ERR_FORMAT;
     if (o->sigma_thresh != 0.f || o->stop_thresh != 0.f) return SVOXB_ERR_OPTION;
     if (t->M >= (1LL << 28)) return SVOXB_ERR_TOO_LARGE;
@@ -985,7 +1011,7 @@ int svoxb_reserve_sms(int n) {
     return before;
 }
 
-const char* svoxb_version(void) { return "0.2.0"; }
+const char* svoxb_version(void) { return "0.3.0"; }
 
 // Test hook (include/svox_b200_testing.h): key 5 = MB of gradient one replay bin spans,
 // key 7 = bricks below the render leaf table on / off.

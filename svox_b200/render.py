@@ -275,7 +275,8 @@ class VolumeRenderer(nn.Module):
         -> ``colors (B, 3), grad (shape of tree.data), diag_hessian (shape of tree.data)``.
         The diagonal is the squared norm of the Jacobian's columns, as in the reference
         (with ``density_softplus`` plus the reference's own second-order term for the density).
-        Octrees with SH colour in three channels (the route through the item log).
+        Octrees with three colour channels of 1, 4, 9, 16 or 25 basis functions (SH, SG or
+        ASG): the route through the item log.
         """
         self._require_cuda(True)
         return self._se_grad(_rays_spec_from_rays(rays), colors, False)
@@ -295,7 +296,8 @@ class VolumeRenderer(nn.Module):
         tree = self.tree._spec()
         if not _C.log_eligible(tree, opt):
             raise NotImplementedError(
-                "se_grad needs an octree (N = 2) with SH colour in three channels")
+                "se_grad needs an octree (N = 2) with three colour channels of 1, 4, 9, 16 or 25 "
+                "basis functions")
         with torch.no_grad():
             colors = colors.to(device=self.tree.data.device, dtype=self.tree.data.dtype)
             for _ in range(4):      # a log that was too small is enlarged and the render redone

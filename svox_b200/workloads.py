@@ -44,7 +44,8 @@ def _leaf_centers(tree):
     return view.corners_local + 0.5 * view.lengths_local[:, None]
 
 
-def shell_tree(init_refine, extra_levels, data_format, gen, sigma_range, shells, coef_std=0.5):
+def shell_tree(init_refine, extra_levels, data_format, gen, sigma_range, shells, coef_std=0.5,
+               extra_data=None):
     """Uniform tree refined ``extra_levels`` more inside spherical shells.
 
     ``shells`` is a list of (centre(3), r_lo, r_hi).  A leaf of the uniform
@@ -54,7 +55,7 @@ def shell_tree(init_refine, extra_levels, data_format, gen, sigma_range, shells,
     colour coefficients ~ N(0, coef_std) for the whole data tensor, then one
     U[lo, hi] density per in-shell leaf in leaf order; all other densities 0.
     """
-    tree = N3Tree(N=2, data_format=data_format, init_refine=init_refine)
+    tree = N3Tree(N=2, data_format=data_format, init_refine=init_refine, extra_data=extra_data)
 
     def in_any(centers):
         m = torch.zeros(centers.shape[0], dtype=torch.bool)

@@ -119,6 +119,52 @@ def sh25_rays():
     return _base(tree, "rays", rays=rays, grad_out=torch.randn(1024, 3, generator=gen))
 
 
+def _lobes(gen, n, anisotropic):
+    """Seeded lobe parameters (the tree's ``extra_data``): SG rows are [sharpness, axis xyz];
+    ASG rows are [bandwidth x, bandwidth y, frame x axis, y axis, z axis], the frame orthonormal."""
+    z = _unit(torch.randn(n, 3, generator=gen))
+    if not anisotropic:
+        return torch.cat([0.5 + 4.0 * torch.rand(n, 1, generator=gen), z], dim=1)
+    a = torch.randn(n, 3, generator=gen)
+    x = _unit(a - (a * z).sum(-1, keepdim=True) * z)
+    y = torch.cross(z, x, dim=-1)
+    return torch.cat([0.5 + 4.0 * torch.rand(n, 2, generator=gen), x, y, z], dim=1)
+
+
+def _lobe_case(fmt, seed, anisotropic, basis_dim, **kw):
+    gen = _g(seed)
+    tree = W.shell_tree(3, 2, f"{fmt}{basis_dim}", gen, (5.0, 50.0),
+                        [((0.5, 0.5, 0.5), 0.30, 0.35)], coef_std=3.0,
+                        extra_data=_lobes(gen, basis_dim, anisotropic))
+    rays = W.sphere_rays(2048, gen, 4.0, 0.2, 0.8)
+    return _base(tree, "rays", rays=rays, grad_out=torch.randn(2048, 3, generator=gen), **kw)
+
+
+def sg9_rays():
+    """Spherical-Gaussian colour, 9 lobes: a basis size the specialised kernels cover."""
+    return _lobe_case("SG", 115, False, 9)
+
+
+def sg5_rays():
+    """Spherical-Gaussian colour, 5 lobes (no specialised kernel), components 1..3 only."""
+    return _lobe_case("SG", 116, False, 5, render=dict(min_comp=1, max_comp=3))
+
+
+def asg4_rays():
+    """Anisotropic spherical-Gaussian colour, 4 lobes, density_softplus."""
+    return _lobe_case("ASG", 117, True, 4, render=dict(density_softplus=True))
+
+
+def asg7_image():
+    """Anisotropic spherical-Gaussian colour, 7 lobes, perspective image."""
+    gen = _g(118)
+    tree = W.shell_tree(3, 2, "ASG7", gen, (5.0, 50.0), [((0.5, 0.5, 0.5), 0.30, 0.35)],
+                        coef_std=3.0, extra_data=_lobes(gen, 7, True))
+    c2w = W.look_at_cameras(1, gen, 4.0)[0]
+    return _base(tree, "image", camera=dict(c2w=c2w, width=64, height=64, fx=200.0, fy=210.0),
+                 grad_out=torch.randn(64, 64, 3, generator=gen))
+
+
 def _aniso_tree(gen, fmt="SH4"):
     tree = N3Tree(N=2, data_format=fmt, init_refine=2, radius=[0.6, 0.8, 1.0],
                   center=[0.1, -0.2, 0.3])
@@ -227,7 +273,7 @@ def query_shell():
 CASES = {f.__name__: f for f in [
     c1_rays, shell_sh9_rays, c4_sample_rays, shell_sh16_image, opt_fast, opt_softplus_pad_bg,
     opt_comp_range, rgba_rays, sh1_rays, sh25_rays, aniso_rays, aniso_image, ndc_image, n3_rays,
-    query_c1, query_aniso, query_shell]}
+    query_c1, query_aniso, query_shell, sg9_rays, sg5_rays, asg4_rays, asg7_image]}
 
 
 

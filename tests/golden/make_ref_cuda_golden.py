@@ -36,7 +36,7 @@ The full-size cases (FULL_CASES, "--full") keep a strided sample of the outputs
 Usage: python tests/golden/make_ref_cuda_golden.py [out_dir] [case ...]
        python tests/golden/make_ref_cuda_golden.py [out_dir] --full
        python tests/golden/make_ref_cuda_golden.py [out_dir] --weights
-       python tests/golden/make_ref_cuda_golden.py [out_dir] --se-grad
+       python tests/golden/make_ref_cuda_golden.py [out_dir] --se-grad [case ...]
 """
 import os
 import sys
@@ -68,11 +68,11 @@ def weights(out_dir):
 
 
 SE_GRAD_CASES = ["c1_rays", "shell_sh9_rays", "shell_sh16_image", "opt_comp_range",
-                 "opt_softplus_pad_bg"]
+                 "opt_softplus_pad_bg", "sg9_rays", "asg4_rays"]
 
 
-def se_grad(out_dir):
-    for name in SE_GRAD_CASES:
+def se_grad(out_dir, names):
+    for name in names or SE_GRAD_CASES:
         case = CASES[name]()
         res = P.run_se_grad(case, "ref_cuda")
         blob = {"out": res["out"]}
@@ -89,7 +89,7 @@ def main():
     if "--weights" in sys.argv:
         return weights(out_dir)
     if "--se-grad" in sys.argv:
-        return se_grad(out_dir)
+        return se_grad(out_dir, [a for a in sys.argv[2:] if not a.startswith("--")])
     full = "--full" in sys.argv
     table = FULL_CASES if full else CASES
     names = [a for a in sys.argv[2:] if not a.startswith("--")] or list(table)

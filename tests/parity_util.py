@@ -165,7 +165,8 @@ def run_ref_cuda(case, device="cuda:0", backward=True, weight_op=None):
     tree = case["tree"].to(device)
     spec = ref.TreeSpec()
     spec.data, spec.child, spec.parent_depth = tree.data.data, tree.child, tree.parent_depth
-    spec.extra_data = torch.empty((0, 0), device=device)
+    spec.extra_data = tree.extra_data if tree.extra_data is not None else \
+        torch.empty((0, 0), device=device)
     spec.offset, spec.scaling = tree.offset, tree.invradius
     spec._weight_accum = torch.empty(0, device=device)
     spec._weight_accum_max = False
@@ -372,7 +373,8 @@ def run_se_grad(case, which, device="cuda:0"):
             assert ref is not None, "oracle/_ref is not built"
             spec = ref.TreeSpec()
             spec.data, spec.child, spec.parent_depth = t.data.data, t.child, t.parent_depth
-            spec.extra_data = torch.empty((0, 0), device=device)
+            spec.extra_data = t.extra_data if t.extra_data is not None else \
+                torch.empty((0, 0), device=device)
             spec.offset, spec.scaling = t.offset, t.invradius
             spec._weight_accum = torch.empty(0, device=device)
             spec._weight_accum_max = False

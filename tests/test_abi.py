@@ -64,7 +64,21 @@ def test_argument_errors_without_gpu(lib):
     opt = csrc.RenderOptions()
     opt.format, opt.basis_dim, opt.max_comp = csrc.FORMAT_SG, 1, 0
     o = opt._pack()
-    assert lib.svoxb_volume_render(C.byref(ok), C.byref(rays), C.byref(o), None, None) == 3
+    # a Gaussian basis without its lobe parameters, with too few of them, with too many lobes
+    assert lib.svoxb_volume_render(C.byref(ok), C.byref(rays), C.byref(o), None, None) == 1
+    lobes = csrc._CTree(16, 16, 16, 16, 1, 2, 4, 0, 0, 0, 16, 1, 3)
+    assert lib.svoxb_volume_render(C.byref(lobes), C.byref(rays), C.byref(o), None, None) == 2
+    lobes = csrc._CTree(16, 16, 16, 16, 1, 2, 4, 0, 0, 0, 16, 1, 4)
+    assert lib.svoxb_volume_render(C.byref(lobes), C.byref(rays), C.byref(o), None, None) == 0
+    opt.format = csrc.FORMAT_ASG
+    o = opt._pack()
+    assert lib.svoxb_volume_render(C.byref(lobes), C.byref(rays), C.byref(o), None, None) == 2
+    opt.format, opt.basis_dim, opt.max_comp = csrc.FORMAT_SG, 26, 25
+    o = opt._pack()
+    assert lib.svoxb_volume_render(C.byref(lobes), C.byref(rays), C.byref(o), None, None) == 3
+    opt.format = 7
+    o = opt._pack()
+    assert lib.svoxb_volume_render(C.byref(lobes), C.byref(rays), C.byref(o), None, None) == 3
     opt.format, opt.basis_dim, opt.max_comp = csrc.FORMAT_SH, 2, 1   # not a square
     o = opt._pack()
     assert lib.svoxb_volume_render(C.byref(ok), C.byref(rays), C.byref(o), None, None) == 3

@@ -59,7 +59,7 @@ def test_case_against_reference_fixture_and_oracle(name, cuda_device):
 
 
 @pytest.mark.parametrize("name", ["c1_rays", "shell_sh9_rays", "opt_fast", "shell_sh16_image",
-                                  "rgba_rays", "aniso_rays"])
+                                  "rgba_rays", "aniso_rays", "sg9_rays", "asg4_rays", "sg5_rays"])
 def test_two_march_backward_matches_single_march(name, cuda_device):
     # Without the forward output the kernel forms `accum` in a first march, as
     # the reference does; both routes give the same gradient.
@@ -73,7 +73,7 @@ def test_two_march_backward_matches_single_march(name, cuda_device):
 
 @pytest.mark.parametrize("name", ["c1_rays", "shell_sh9_rays", "shell_sh16_image", "aniso_rays",
                                   "aniso_image", "sh1_rays", "sh25_rays", "opt_comp_range",
-                                  "opt_softplus_pad_bg"])
+                                  "opt_softplus_pad_bg", "sg9_rays", "asg4_rays"])
 def test_replay_backward_matches_marching_backward(name, cuda_device):
     # With gradients enabled the forward logs its contributing samples and the
     # backward replays the log; the marching backward must give the same gradient.
@@ -146,7 +146,8 @@ def test_weight_accumulation_matches_oracle(name, op, cuda_device):
 
 
 @pytest.mark.parametrize("name", ["c1_rays", "shell_sh9_rays", "shell_sh16_image",
-                                  "opt_comp_range", "aniso_rays", "opt_softplus_pad_bg"])
+                                  "opt_comp_range", "aniso_rays", "opt_softplus_pad_bg",
+                                  "sg9_rays", "asg4_rays"])
 def test_se_grad_matches_oracle_and_reference_fixture(name, cuda_device):
     # VolumeRenderer.se_grad / se_grad_persp (svox/renderer.py:324-385): colour, gradient and
     # Gauss-Newton diagonal of the squared error against seeded colours.
@@ -225,7 +226,7 @@ def test_replay_in_parts_equals_replay_in_one_go(name, image, cuda_device):
 
 
 @pytest.mark.parametrize("name", ["shell_sh9_rays", "shell_sh16_image", "opt_fast", "aniso_image",
-                                  "rgba_rays"])
+                                  "rgba_rays", "sg9_rays"])
 def test_frozen_tree_renders_are_identical(name, cuda_device):
     # Inside renderer.frozen_tree() the render index is built once and reused; the renders
     # are bit-identical to the ones that rebuild it per call (RGBA has no index: plain path).

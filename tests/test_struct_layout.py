@@ -79,7 +79,7 @@ def test_integration_document_matches_header(name):
 
 def test_sizes_are_the_documented_ones():
     h = header_structs()
-    assert _layout(h["svoxb_tree"])[1] == 64
+    assert _layout(h["svoxb_tree"])[1] == 80
     assert _layout(h["svoxb_rays"])[1] == 32
     assert _layout(h["svoxb_camera"])[1] == 24
     assert _layout(h["svoxb_render_options"])[1] == 52     # RenderOptions: 13 x 4 bytes
