@@ -119,6 +119,21 @@ int svoxb_query_vertical_backward(const svoxb_tree* tree, const float* indices, 
                                   const float* grad_output, int32_t Kg, float* grad_data_out,
                                   int zero_first, void* stream);
 
+/* assign_vertical (svox/csrc/svox_kernel.cu:80-89,145-158): overwrite the first
+ * Kv floats (1 <= Kv <= K) of the record of each point's leaf with row q of
+ * values (Q, Kv).  data_out is the tree's own data array (writable).  Points
+ * that share a leaf race with each other, as in the reference: which row a
+ * float ends up with is then unspecified. */
+int svoxb_assign_vertical(const svoxb_tree* tree, const float* indices, int64_t Q,
+                          const float* values, int32_t Kv, float* data_out, void* stream);
+
+/* calc_corners (svox/csrc/svox_kernel.cu:91-115,184-203): lower corner, in
+ * tree-local [0,1)^3 coordinates, of each cell (node, i, j, k) of indexer
+ * (Q, 4) int64, found by walking parent_depth ((M, 2) int32: packed index of
+ * the parent cell, depth) up to the root.  out is (Q, 3). */
+int svoxb_calc_corners(const svoxb_tree* tree, const int32_t* parent_depth,
+                       const int64_t* indexer, int64_t Q, float* out, void* stream);
+
 /* volume_render (svox/csrc/rt_kernel.cu:1019-1036): out is (Q, out_dim),
  * out_dim = (K-1)/basis_dim, or K-1 for RGBA. */
 int svoxb_volume_render(const svoxb_tree* tree, const svoxb_rays* rays,

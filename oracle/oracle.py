@@ -141,6 +141,42 @@ def query_vertical(tree, points):
     return vals, ids
 
 
+def assign_vertical(tree, points, values):
+    """assign_single_kernel (svox/csrc/svox_kernel.cu:80-89): a copy of ``tree.data`` in which
+    the first Kv floats of the leaf of each point hold its row of ``values``; of several
+    points in one leaf the LAST one wins here (the reference leaves the winner open)."""
+    _, ids = query_vertical(tree, points)
+    v = _f32(values)
+    data = tree.data.copy().reshape(-1, tree.K)
+    data[ids, :v.shape[1]] = v        # numpy keeps the last of repeated indices
+    return data.reshape(tree.data.shape)
+
+
+def calc_corners(parent_depth, N, indexer):
+    """calc_corner_kernel (svox/csrc/svox_kernel.cu:91-115): per level, add the cell's
+    coordinates then divide by N, in float32, walking parent_depth[:, 0] (the packed index
+    of the parent cell) up to the root."""
+    pd = np.asarray(parent_depth)
+    idx = np.asarray(indexer, dtype=np.int64)
+    out = np.zeros((idx.shape[0], 3), np.float32)
+    fn = np.float32(N)
+    for q in range(idx.shape[0]):
+        node, c = int(idx[q, 0]), [int(x) for x in idx[q, 1:]]
+        r = np.zeros(3, np.float32)
+        while True:
+            r = (r + np.asarray(c, np.float32)) / fn
+            if node == 0:
+                break
+            packed = int(pd[node, 0])
+            c = [0, 0, 0]
+            for a in (2, 1, 0):
+                c[a] = packed % N
+                packed //= N
+            node = packed
+        out[q] = r
+    return out
+
+
 def query_vertical_backward(tree, points, grad_out):
     pts = _f32(points)
     g = _f32(grad_out)

@@ -287,6 +287,48 @@ def query_vertical_backward(tree, indices, grad_output):
     return grad
 
 
+def assign_vertical(tree, indices, values):
+    """Write row q of ``values`` (Q, Kv <= K) into the record of the leaf that holds point q
+    (in place, into ``tree.data``); svox_kernel.cu:80-89,145-158."""
+    lib = library()
+    ct = _pack_tree(tree)
+    _check_indices(indices)
+    _check_input(values, "values")
+    Q = indices.shape[0]
+    if values.dim() != 2 or values.shape[0] != Q or not 1 <= values.shape[1] <= ct.K:
+        raise RuntimeError("values must be (Q, Kv) with 1 <= Kv <= K")
+    with torch.cuda.device(indices.device):
+        st = lib.svoxb_assign_vertical(
+            C.byref(ct), C.c_void_p(indices.data_ptr()), C.c_int64(Q),
+            C.c_void_p(values.data_ptr()), C.c_int32(values.shape[1]),
+            C.c_void_p(tree.data.data_ptr()), _stream())
+    if st:
+        _raise(st, "assign_vertical")
+
+
+def calc_corners(tree, indexer):
+    """Lower corners (Q, 3), tree-local, of the cells ``indexer`` (Q, 4) int64 =
+    (node, i, j, k); svox_kernel.cu:91-115,184-203."""
+    lib = library()
+    ct = _pack_tree(tree)
+    _check_input(indexer, "indexer", torch.int64)
+    _check_input(tree.parent_depth, "parent_depth", torch.int32)
+    if indexer.dim() != 2 or indexer.shape[1] != 4:
+        raise RuntimeError("indexer must be (Q, 4)")
+    if tuple(tree.parent_depth.shape) != (ct.M, 2) or tree.parent_depth.device != indexer.device:
+        raise RuntimeError("parent_depth must be (M, 2) on the device of indexer")
+    Q = indexer.shape[0]
+    with torch.cuda.device(indexer.device):
+        out = torch.empty((Q, 3), dtype=tree.data.dtype, device=indexer.device)
+        st = lib.svoxb_calc_corners(
+            C.byref(ct), C.c_void_p(tree.parent_depth.data_ptr()),
+            C.c_void_p(indexer.data_ptr()), C.c_int64(Q), C.c_void_p(out.data_ptr()),
+            _stream())
+    if st:
+        _raise(st, "calc_corners")
+    return out
+
+
 def render_scratch(tree, opt):
     """The forward render's index of the tree (density-annotated child array, leaf table,
     bricks) as an int32 tensor, for ``volume_render[_image](..., prepared=...)``: valid until

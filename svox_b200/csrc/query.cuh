@@ -72,6 +72,9 @@ __device__ __forceinline__ int64_t locate_point(const TreeArgs& tr, const TopTab
 }
 
 // MODE 0: copy records out (forward).  MODE 1: scatter-add rows in (backward).
+// MODE 2: overwrite the first Kg floats of each point's record with its row of `grad_out`
+// (assign_single_kernel, svox/csrc/svox_kernel.cu:80-89; points that share a leaf race, as in
+// the reference).
 template <int MODE>
 __global__ void __launch_bounds__(kQueryBlock)
 query_kernel(TreeArgs tr, TopTable top, const float* __restrict__ pts, int64_t Q,
@@ -91,6 +94,21 @@ query_kernel(TreeArgs tr, TopTable top, const float* __restrict__ pts, int64_t Q
     if (wb >= Q) return;
     const int K = (MODE == 0) ? tr.K : Kg;
     const int nvalid = (int)((Q - wb) < 32 ? (Q - wb) : 32);
+    if (MODE == 2) {
+        // lanes walk the warp's (nvalid, Kg) block of rows in order: coalesced reads, and
+        // writes that are contiguous within each record
+        const int total = nvalid * K;
+        int p = 0, e = lane;
+        while (e >= K) { e -= K; ++p; }
+        for (int base = 0; base < total; base += 32) {        // warp-uniform trip count
+            const int j = base + lane;
+            const int64_t s = __shfl_sync(0xffffffffu, slot, p < nvalid ? p : nvalid - 1);
+            if (j < total && s >= 0) grad_data[s * tr.K + e] = __ldg(grad_out + wb * K + j);
+            e += 32;
+            while (e >= K) { e -= K; ++p; }
+        }
+        return;
+    }
     if (MODE == 1) {
         // Backward: add row p of the upstream gradient into the record of point p's leaf.  A
         // record is K floats at 4-byte alignment, so each is cut into at most 3 single floats
@@ -158,6 +176,39 @@ query_kernel(TreeArgs tr, TopTable top, const float* __restrict__ pts, int64_t Q
     }
 }
 
+// calc_corner_kernel (svox/csrc/svox_kernel.cu:91-115): the lower corner of cell (node, i, j, k)
+// in tree-local coordinates, by walking parent_depth up to the root with the reference's
+// add-then-divide per level (for N = 3 the roundings of that order are part of the result).
+// parent_depth is (M, 2): packed index of the parent cell, depth.
+__global__ void calc_corners_kernel(const int32_t* __restrict__ parent_depth, int64_t M, int N,
+                                    const int64_t* __restrict__ indexer, int64_t Q,
+                                    float* __restrict__ out) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= Q) return;
+    int64_t node = indexer[4 * i];
+    int c[3] = {(int)indexer[4 * i + 1], (int)indexer[4 * i + 2], (int)indexer[4 * i + 3]};
+    float r[3] = {0.f, 0.f, 0.f};
+    const float fn = (float)N;
+    for (int level = 0;; ++level) {
+        if (node < 0 || node >= M || level > 64) {   // not a tree: reported, never followed
+            report(SVOXB_ERR_TREE);
+            break;
+        }
+#pragma unroll
+        for (int a = 0; a < 3; ++a) r[a] = __fdiv_rn(__fadd_rn(r[a], (float)c[a]), fn);
+        if (node == 0) break;
+        int32_t packed = __ldg(parent_depth + 2 * node);
+        for (int a = 2; a >= 0; --a) {
+            c[a] = packed % N;
+            packed /= N;
+        }
+        node = packed;
+    }
+    out[3 * i + 0] = r[0];
+    out[3 * i + 1] = r[1];
+    out[3 * i + 2] = r[2];
+}
+
 static int launch_query(int mode, const svoxb_tree* tree, const float* indices, int64_t Q,
                         float* values_out, int64_t* ids_out, const float* grad_out,
                         float* grad_data, int Kg, cudaStream_t stream) {
@@ -173,6 +224,10 @@ static int launch_query(int mode, const svoxb_tree* tree, const float* indices, 
         query_kernel<0><<<grid, kQueryBlock, 0, stream>>>(tree_args(tree), tt, indices, Q,
                                                           values_out, ids_out, nullptr,
                                                           nullptr, 0);
+    else if (mode == 2)
+        query_kernel<2><<<grid, kQueryBlock, 0, stream>>>(tree_args(tree), tt, indices, Q,
+                                                          nullptr, nullptr, grad_out,
+                                                          grad_data, Kg);
     else
         query_kernel<1><<<grid, kQueryBlock, 0, stream>>>(tree_args(tree), tt, indices, Q,
                                                           nullptr, nullptr, grad_out,

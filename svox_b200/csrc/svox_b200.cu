@@ -554,6 +554,30 @@ int svoxb_query_vertical_backward(const svoxb_tree* tree, const float* indices, 
                         (cudaStream_t)stream);
 }
 
+int svoxb_assign_vertical(const svoxb_tree* tree, const float* indices, int64_t Q,
+                          const float* values, int32_t Kv, float* data_out, void* stream) {
+    int st = validate_tree(tree);
+    if (st) return st;
+    if (Q < 0 || Kv < 1 || Kv > tree->K) return SVOXB_ERR_SHAPE;
+    if (!data_out || (Q > 0 && !values)) return SVOXB_ERR_NULL;
+    return launch_query(2, tree, indices, Q, nullptr, nullptr, values, data_out, Kv,
+                        (cudaStream_t)stream);
+}
+
+int svoxb_calc_corners(const svoxb_tree* tree, const int32_t* parent_depth,
+                       const int64_t* indexer, int64_t Q, float* out, void* stream) {
+    int st = validate_tree(tree);
+    if (st) return st;
+    if (Q < 0) return SVOXB_ERR_SHAPE;
+    if (Q == 0) return SVOXB_OK;
+    if (!parent_depth || !indexer || !out) return SVOXB_ERR_NULL;
+    if ((Q + 255) / 256 > 0x7fffffffLL) return SVOXB_ERR_TOO_LARGE;
+    calc_corners_kernel<<<(unsigned)((Q + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        parent_depth, tree->M, tree->N, indexer, Q, out);
+    SVOXB_CUDA(cudaGetLastError());
+    return SVOXB_OK;
+}
+
 int svoxb_volume_render(const svoxb_tree* tree, const svoxb_rays* rays,
                         const svoxb_render_options* opt, float* out, void* stream) {
     if (!tree || !rays || !opt) return SVOXB_ERR_NULL;

@@ -102,6 +102,25 @@ class N3Tree(nn.Module):
         self.refine(repeats=init_refine)
 
     # ------------------------------------------------------------------
+    # Point assignment
+    def set(self, indices, values, cuda=True):
+        """Overwrite the leaf containing each point of ``indices`` ``(Q, 3)`` with its row of
+        ``values`` ``(Q, K)`` (svox/svox.py:159-206).  Points that share a leaf race, as in
+        the reference.  The tree must live on a CUDA device."""
+        assert len(indices.shape) == 2
+        assert not indices.requires_grad  # Grad wrt indices not supported
+        assert not values.requires_grad  # Grad wrt values not supported
+        if not cuda or not self.data.is_cuda:
+            raise RuntimeError(
+                "svox_b200 has no CPU assignment path: move the tree to a CUDA device "
+                "(tree.cuda()) and call with cuda=True")
+        dev, dt = self.data.device, self.data.dtype
+        indices = indices.to(device=dev, dtype=dt).contiguous()
+        values = values.to(device=dev, dtype=dt).contiguous()
+        self._data_epoch += 1
+        _C.assign_vertical(self._spec(), indices, values)
+
+    # ------------------------------------------------------------------
     # Point query (hot path)
     def forward(self, indices, cuda=True, want_node_ids=False, world=True):
         """Values (and packed leaf ids) of the leaves containing ``indices`` ``(Q, 3)``.
@@ -446,8 +465,12 @@ class N3Tree(nn.Module):
                 as_tuple=False).cpu()
         return self._last_all_leaves
 
-    def _calc_corners(self, nodes):
-        """Lower corner of each ``(node, u, v, w)`` cell in tree-local coordinates."""
+    def _calc_corners(self, nodes, cuda=True):
+        """Lower corner of each ``(node, u, v, w)`` cell in tree-local coordinates
+        (svox/svox.py:990-1012): the native kernel on a CUDA tree, tensor ops otherwise."""
+        if self.data.is_cuda and cuda:
+            nodes = nodes.to(device=self.data.device, dtype=torch.int64).contiguous()
+            return _C.calc_corners(self._spec(), nodes)
         nodes = nodes.to(self.parent_depth.device).long()
         out = torch.zeros(nodes.shape[0], 3, device=nodes.device, dtype=self.data.dtype)
         alive = torch.arange(nodes.shape[0], device=nodes.device)

@@ -16,6 +16,11 @@ reference's own ``N3Tree.save``:
 
     ref_py_saved_tree_<name>.npz   (the reference's checkpoint format, as written by it)
 
+and, next to each, ``ref_py_frontier_<name>.npz``: the reference's frontier queries, the
+corners and side lengths of every leaf (its tensor-op ``_calc_corners``), a point assignment
+``tree.set(points, values, cuda=False)`` (the rows of ``data`` it changed), and the selection
+of a merge whose result is ``ref_py_saved_tree_<name>_merged.npz``.
+
 tests/test_tree_structure.py loads those files with svox_b200.N3Tree.load,
 rebuilds the same trees with svox_b200 from the same recipe (RECIPES below)
 and compares node numbering and file contents.
@@ -81,6 +86,19 @@ def build_recipe(lib, recipe):
     return tree
 
 
+def assignment(recipe, n_leaves):
+    """Seeded inputs of the ``tree.set`` fixture: one point inside every third leaf is not
+    expressible without the tree, so points are uniform in the world box, few enough that
+    hardly any two share a leaf; the caller drops those that do."""
+    gen = torch.Generator().manual_seed(recipe["seed"] + 1000)
+    ctor = recipe["ctor"]
+    radius = torch.as_tensor(ctor.get("radius", 0.5), dtype=torch.float32).expand(3)
+    center = torch.as_tensor(ctor.get("center", [0.5, 0.5, 0.5]), dtype=torch.float32)
+    Q = max(8, n_leaves // 6)
+    pts = center + (torch.rand(Q, 3, generator=gen) * 2 - 1) * radius * 0.999
+    return pts, gen
+
+
 def coarsen(tree):
     """The merge both libraries perform on a recipe tree: every second frontier node whose
     largest last-channel value is below the median goes back into its parent (mean of the
@@ -105,6 +123,22 @@ def structure(ref):
         blob = dict(frontier=tree._frontier.numpy(), frontier_depth=tree.frontier_depth.numpy(),
                     mean=tree.reduce_frontier().numpy(), top=tree.max_frontier(dim=-1).numpy(),
                     diam=tree.diam_frontier().numpy())
+        # geometry of every leaf, and a point assignment (tree.set), by the reference's CPU path
+        view = tree[:]
+        blob["leaf_corners"] = view.corners_local.numpy()
+        blob["leaf_lengths"] = view.lengths_local.numpy()
+        pts, gen = assignment(recipe, tree.n_leaves)
+        _, ids = tree.forward(pts.clone(), cuda=False, want_node_ids=True)
+        _, first = np.unique(ids.numpy(), return_index=True)      # one point per leaf
+        pts = pts[np.sort(first)]
+        vals = torch.randn(pts.shape[0], tree.data_dim, generator=gen)
+        before = tree.data.data.clone()
+        tree.set(pts.clone(), vals, cuda=False)
+        blob["set_points"], blob["set_values"] = pts.numpy(), vals.numpy()
+        after = tree.data.data.reshape(-1, tree.data_dim)
+        rows = (after != before.reshape(-1, tree.data_dim)).any(dim=1).nonzero()[:, 0]
+        blob["set_rows"], blob["set_rows_data"] = rows.numpy(), after[rows].numpy().copy()
+        tree.data.data.copy_(before)
         blob["pick"] = coarsen(tree).numpy()
         tree.check_integrity()
         np.savez_compressed(os.path.join(HERE, f"ref_py_frontier_{name}.npz"), **blob)

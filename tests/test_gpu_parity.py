@@ -483,6 +483,59 @@ def test_c_abi_direct_call(cuda_device):
     assert torch.equal(vals, v2) and torch.equal(ids, i2)
 
 
+@pytest.mark.parametrize("name", ["octree", "n3"])
+def test_set_and_corner_kernels_like_the_reference(name, cuda_device):
+    # N3Tree.set -> assign_vertical and _calc_corners -> calc_corners
+    # (svox/csrc/svox_kernel.cu:80-115,145-158,184-203) against what the reference's own CPU
+    # code produced for the same recipe trees, bit for bit, and against the oracle.
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_ref_py_golden",
+                                                  os.path.join(GOLD, "make_ref_py_golden.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    from oracle import oracle as orc
+    f = np.load(os.path.join(GOLD, f"ref_py_frontier_{name}.npz"))
+    tree = gen.build_recipe(svox, gen.RECIPES[name])
+    before = tree.data.detach().numpy().reshape(-1, tree.data_dim).copy()
+    pd_cpu, leaves_cpu = tree.parent_depth.numpy().copy(), tree._all_leaves().numpy().copy()
+    tree = tree.to(cuda_device)
+    view = tree[:]
+    corners = view.corners_local
+    assert corners.is_cuda and np.array_equal(corners.cpu().numpy(), f["leaf_corners"])
+    # (the tensor-op route on a GPU divides by N through a reciprocal: close, not equal)
+    assert torch.allclose(corners, tree._calc_corners(tree._all_leaves(), cuda=False),
+                          rtol=0, atol=1e-6)
+    # interior cells as well as leaves, in any order
+    idx = torch.from_numpy(leaves_cpu[::5][::-1].copy())
+    idx[::2, 1:] = 0
+    got = tree._calc_corners(idx).cpu().numpy()
+    assert np.array_equal(got, orc.calc_corners(pd_cpu, tree.N, idx.numpy()))
+    assert tree._calc_corners(idx[:0]).shape == (0, 3)
+    csrc.check_device_status()
+
+    pts, vals = torch.from_numpy(f["set_points"]), torch.from_numpy(f["set_values"])
+    tree.set(pts, vals)
+    want = before.copy()
+    want[f["set_rows"]] = f["set_rows_data"]
+    assert np.array_equal(tree.data.detach().cpu().numpy().reshape(-1, tree.data_dim), want)
+    # a prefix of the record only (values narrower than the record), world transform included
+    rows50 = tree(pts[:50].to(cuda_device), want_node_ids=True)[1].cpu().numpy()
+    tree.set(pts[:50], 7.0 + vals[:50, :2].contiguous())
+    want[rows50, :2] = 7.0 + f["set_values"][:50, :2]
+    now = tree.data.detach().cpu().numpy().reshape(-1, tree.data_dim)
+    assert np.array_equal(now, want)
+    # points that share a leaf: every float of the leaf comes from one of their rows
+    many = pts[:1].repeat(64, 1)
+    rows = torch.randn(64, tree.data_dim)
+    tree.set(many, rows)
+    leaf = tree.data.detach().cpu().numpy().reshape(-1, tree.data_dim)[rows50[0]]
+    assert all(leaf[k] in rows[:, k].numpy() for k in range(tree.data_dim))
+    tree.set(pts[:0], vals[:0])
+    with pytest.raises(RuntimeError):
+        tree.set(pts, torch.zeros(pts.shape[0], tree.data_dim + 1))
+    csrc.check_device_status()
+
+
 def test_full_size_properties_config2_slice(cuda_device):
     """The query benchmark one level coarser (128^3 leaves) with 2^22 points: the
     size-independent invariants of the query."""

@@ -225,3 +225,29 @@ def test_frontier_merge_and_compaction_like_the_reference(name):
     t2._lock_tree_structure = True
     with pytest.raises(RuntimeError):
         t2.merge()
+
+
+@pytest.mark.parametrize("name", ["octree", "n3"])
+def test_leaf_geometry_and_assignment_oracle_like_the_reference(name):
+    # Corners and side lengths of every leaf (svox/svox.py:990-1012; for N = 3 the roundings of
+    # the per-level add-then-divide are part of the result) and a point assignment
+    # (svox/svox.py:159-206), as the reference's own CPU code produced them: the tensor-op
+    # path of this package and the oracle's restatements of the two kernels give the same bits.
+    from oracle import oracle as orc
+    gen = _recipes()
+    here = os.path.dirname(os.path.abspath(__file__))
+    f = np.load(os.path.join(here, "golden", f"ref_py_frontier_{name}.npz"))
+    tree = gen.build_recipe(svox, gen.RECIPES[name])
+    view = tree[:]
+    assert np.array_equal(view.corners_local.numpy(), f["leaf_corners"])
+    assert np.array_equal(view.lengths_local.numpy(), f["leaf_lengths"])
+    leaves = tree._all_leaves().numpy()
+    assert np.array_equal(orc.calc_corners(tree.parent_depth.numpy(), tree.N, leaves[::7]),
+                          f["leaf_corners"][::7])
+    ot = orc.Tree.from_n3tree(tree, world=True)
+    data = orc.assign_vertical(ot, f["set_points"], f["set_values"]).reshape(-1, tree.data_dim)
+    want = tree.data.detach().numpy().reshape(-1, tree.data_dim).copy()
+    want[f["set_rows"]] = f["set_rows_data"]
+    assert np.array_equal(data, want)
+    with pytest.raises(RuntimeError):
+        tree.set(torch.from_numpy(f["set_points"]), torch.from_numpy(f["set_values"]))
