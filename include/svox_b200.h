@@ -252,6 +252,23 @@ int svoxb_volume_render_image_hessdiag_replay(const svoxb_tree* tree, const svox
                                               float* hessdiag_out, int zero_first,
                                               void* stream);
 
+/* se_grad / se_grad_persp (svox/csrc/rt_kernel.cu:479-715,846-897,1111-1173)
+ * for any record layout with at most 4 output channels (the reference's bound,
+ * :1123): RGBA, N != 2, basis sizes without a specialised kernel.  One march per ray
+ * adds the gradient of 1/2 sum (fwd_out - color_ref)^2 w.r.t. data into
+ * grad_data_out and its Gauss-Newton diagonal into hessdiag_out (both shaped
+ * like data).  fwd_out is the output of svoxb_volume_render[_image] for the same
+ * inputs with both thresholds zero (the reference's kernel knows none);
+ * color_ref is shaped like it. */
+int svoxb_se_grad_march(const svoxb_tree* tree, const svoxb_rays* rays,
+                        const svoxb_render_options* opt, const float* fwd_out,
+                        const float* color_ref, float* grad_data_out, float* hessdiag_out,
+                        int zero_first, void* stream);
+int svoxb_se_grad_image_march(const svoxb_tree* tree, const svoxb_camera* cam,
+                              const svoxb_render_options* opt, const float* fwd_out,
+                              const float* color_ref, float* grad_data_out, float* hessdiag_out,
+                              int zero_first, void* stream);
+
 /* The replay backward in steps, for callers that overlap the all-reduce of the
  * gradient with its computation (no counterpart in the reference).  _begin
  * sorts the logged samples by leaf range (arguments as for

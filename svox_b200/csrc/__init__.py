@@ -592,6 +592,35 @@ def volume_render_hessdiag_replay(tree, rays_or_cam, opt, fwd_out, logpair, used
     return hess
 
 
+def se_grad_march(tree, rays_or_cam, opt, fwd_out, colors, image=False):
+    """-> (grad, hessdiag) of the squared error ``1/2 sum (fwd_out - colors)^2`` by marching
+    the rays once more: any record layout with at most four output channels.  ``fwd_out``: the
+    render of the same inputs with both thresholds zero."""
+    lib = library()
+    dev = tree.data.device
+    with torch.cuda.device(dev):
+        ct = _pack_tree(tree)
+        co = opt._pack()
+        _check_input(fwd_out, "fwd_out")
+        _check_input(colors, "colors")
+        if colors.numel() != fwd_out.numel():
+            raise RuntimeError("colors must have the shape of the render")
+        grad = torch.zeros_like(tree.data, memory_format=torch.contiguous_format)
+        hess = torch.zeros_like(grad)
+        if image:
+            cs = _pack_camera(rays_or_cam, dev)
+            fn = lib.svoxb_se_grad_image_march
+        else:
+            cs = _pack_rays(rays_or_cam, dev)
+            fn = lib.svoxb_se_grad_march
+        st = fn(C.byref(ct), C.byref(cs), C.byref(co), C.c_void_p(fwd_out.data_ptr()),
+                C.c_void_p(colors.data_ptr()), C.c_void_p(grad.data_ptr()),
+                C.c_void_p(hess.data_ptr()), C.c_int(0), _stream())
+    if st:
+        _raise(st, "se_grad_march")
+    return grad, hess
+
+
 def replay_part_ranges(M, K, n_parts):
     """Leaf-slot ranges [(begin, end)] of the ``n_parts`` parts of a replay backward for a tree
     of ``M`` nodes with ``K`` floats per record (whole bins; the same on every process)."""

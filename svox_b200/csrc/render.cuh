@@ -33,6 +33,7 @@ namespace svoxb {
 
 constexpr int kMaxSteps = 1 << 16;   // samples per ray before SVOXB_ERR_MARCH
 constexpr int kMaxGenericOut = 32;   // colour channels in the generic kernel
+constexpr int kMaxSeGradOut = 4;     // ... in se_grad, the reference's bound (rt_kernel.cu:1123)
 
 // SH constants (the published real SH normalisation factors, as float).
 __device__ constexpr float kC0 = 0.28209479177387814;
@@ -834,6 +835,117 @@ render_bwd_generic(TreeArgs tr, Source src, svoxb_render_options opt, TopTable t
                 float total_grad = 0.f;
                 for (int j = 0; j < out_dim; ++j) total_grad += __ldg(g + j);
                 accum += light * opt.background_brightness * total_grad;
+            }
+        }
+    }
+}
+
+// Gradient and Gauss-Newton diagonal of the squared error 1/2 (render - colour)^2 for any
+// record layout: what the reference's se_grad kernel adds up in its second and third march
+// (svox/csrc/rt_kernel.cu:566-709), with its per-channel running sums.  One march is enough
+// here because the colour the reference re-accumulates in its second march is the forward's
+// output (`fwd_out`, rendered without thresholds), which the caller already has.
+template <int BLOCK, class Source>
+__global__ void __launch_bounds__(BLOCK)
+render_se_grad_generic(TreeArgs tr, Source src, svoxb_render_options opt, TopTable topg,
+                       bool top_in_smem, const float* __restrict__ fwd_out,
+                       const float* __restrict__ color_ref, float* __restrict__ grad,
+                       float* __restrict__ hess, int64_t Q, int out_dim) {
+    extern __shared__ int32_t s_top[];
+    __shared__ unsigned s_next;
+    if (threadIdx.x == 0) s_next = 0;
+    const TopTable top = stage_top(topg, s_top, top_in_smem);
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int64_t n_gran = (Q + 31) >> 5;
+    const int K = tr.K;
+    const float d_rgb_pad = 1 + 2 * opt.rgb_padding;
+    const bool sh = opt.format != SVOXB_FORMAT_RGBA;
+
+    for (;;) {
+        const int64_t gran = next_granule(&s_next, lane);
+        if (gran >= n_gran) break;
+        const int64_t ray = gran * 32 + lane;
+        Ray r;
+        r.hit = false;
+        if (ray < Q) {
+            src.load(ray, tr, opt, r);
+            ray_setup(r, tr.scaling);
+        }
+        float basis[25];
+        if (r.hit && sh) colour_basis_any(tr, opt, r.vdir, basis);
+        float accum[kMaxSeGradOut], curr[kMaxSeGradOut], resid[kMaxSeGradOut];
+        for (int j = 0; j < out_dim; ++j) {
+            accum[j] = r.hit ? __ldg(fwd_out + ray * out_dim + j) : 0.f;
+            resid[j] = r.hit ? accum[j] - __ldg(color_ref + ray * out_dim + j) : 0.f;
+        }
+        float light = 1.f, t = r.tmin;
+        int it = 0;
+        // Warp-uniform loop: the vote makes the warp reconverge every step.
+        bool go = r.hit && t < r.tmax;
+        while (__any_sync(0xffffffffu, go)) {
+            if (go) {
+                Step s;
+                if (++it > kMaxSteps) {
+                    report(SVOXB_ERR_MARCH);
+                    go = false;
+                } else if (!march_step(tr, top, r, t, opt.step_size, s)) {
+                    go = false;
+                } else {
+                    const int64_t off = s.leaf.slot * K;
+                    const float* __restrict__ rec = tr.data + off;
+                    float sigma = __ldg(rec + (K - 1));
+                    const float raw_sigma = sigma;
+                    if (opt.density_softplus) sigma = softplus_m1(sigma);
+                    if (sigma > 0.0f) {
+                        const float att = expf(-s.delta_t * sigma * r.delta_scale);
+                        const float weight = light * (1.f - att);
+                        for (int ch = 0; ch < out_dim; ++ch) {
+                            float tmp;
+                            const int coff = sh ? ch * opt.basis_dim : ch;
+                            if (sh) {
+                                tmp = 0.0f;
+                                for (int i = opt.min_comp; i <= opt.max_comp; ++i)
+                                    tmp += basis[i] * __ldg(rec + coff + i);
+                            } else {
+                                tmp = __ldg(rec + ch);
+                            }
+                            const float sg = sigmoid_ref(tmp);
+                            const float grad_ci = weight * sg * (1.0 - sg) * d_rgb_pad;
+                            if (sh) {
+                                for (int i = opt.min_comp; i <= opt.max_comp; ++i) {
+                                    const float grad_wi = basis[i] * grad_ci;
+                                    atomicAdd(grad + off + coff + i, grad_wi * resid[ch]);
+                                    atomicAdd(hess + off + coff + i, grad_wi * grad_wi);
+                                }
+                            } else {
+                                atomicAdd(grad + off + ch, grad_ci * resid[ch]);
+                                atomicAdd(hess + off + ch, grad_ci * grad_ci);
+                            }
+                            curr[ch] = sg * d_rgb_pad - opt.rgb_padding;
+                            accum[ch] -= weight * curr[ch];
+                        }
+                        light *= att;
+                        float g = 0.f, h = 0.f;
+                        for (int j = 0; j < out_dim; ++j) {
+                            const float grad_sigma =
+                                s.delta_t * r.delta_scale * (curr[j] * light - accum[j]);
+                            if (opt.density_softplus) {
+                                const float sgm = sigmoid_ref(raw_sigma - 1);
+                                g += grad_sigma * resid[j] * sgm;
+                                h += grad_sigma * grad_sigma * sgm * sgm +
+                                     grad_sigma * (sgm * (1.f - sgm));
+                            } else {
+                                g += grad_sigma * resid[j];
+                                h += grad_sigma * grad_sigma;
+                            }
+                        }
+                        atomicAdd(grad + off + (K - 1), g);
+                        atomicAdd(hess + off + (K - 1), h);
+                    }
+                    t = __fadd_rn(t, s.delta_t);
+                    if (!(t < r.tmax)) go = false;
+                }
             }
         }
     }

@@ -860,6 +860,71 @@ int svoxb_volume_render_image_hessdiag_replay(const svoxb_tree* tree, const svox
 
 }  // extern "C"
 
+// se_grad by marching (any record layout the generic kernels take): gradient and
+// Gauss-Newton diagonal of the squared error from the forward's output.
+template <class Source>
+static int se_grad_march(const svoxb_tree* tree, const Source& src, int64_t Q,
+                         const svoxb_render_options* opt, const float* fwd_out,
+                         const float* color_ref, float* grad, float* hess, int zero_first,
+                         cudaStream_t stream) {
+    int st = validate_tree(tree);
+    if (st) return st;
+    if ((st = validate_options(tree, *opt))) return st;
+    if (Q < 0) return SVOXB_ERR_SHAPE;
+    if (!grad || !hess || (Q > 0 && (!fwd_out || !color_ref))) return SVOXB_ERR_NULL;
+    const int od = out_dim_of(tree, *opt);
+    if (od > kMaxSeGradOut) return SVOXB_ERR_FORMAT;
+    if (zero_first) {
+        if ((st = zero_grad(tree, grad, tree->K, stream))) return st;
+        if ((st = zero_grad(tree, hess, tree->K, stream))) return st;
+    }
+    if (Q == 0) return SVOXB_OK;
+    TopScratch scratch;
+    if ((st = scratch.build(tree, 5, stream))) return st;
+    const TopTable top{scratch.cells, scratch.level};
+    const bool in_smem = scratch.level > 0 && scratch.level <= 5;
+    const size_t smem = in_smem ? ((size_t)4 << (3 * scratch.level)) : 0;
+    const TreeArgs tr = tree_args(tree);
+    const int64_t n_gran = (Q + 31) / 32;
+    unsigned grid = 1;
+    auto run = [&](auto k, int block) {
+        int s2 = persistent_grid(k, block, smem, n_gran, &grid);
+        if (s2) return s2;
+        k<<<grid, block, smem, stream>>>(tr, src, *opt, top, in_smem, fwd_out, color_ref, grad,
+                                        hess, Q, od);
+        const cudaError_t e = cudaGetLastError();
+        return e != cudaSuccess ? set_cuda_error(e) : (int)SVOXB_OK;
+    };
+    return smem > 64 * 1024 ? run(render_se_grad_generic<1024, Source>, 1024)
+                            : run(render_se_grad_generic<256, Source>, 256);
+}
+
+extern "C" {
+
+int svoxb_se_grad_march(const svoxb_tree* tree, const svoxb_rays* rays,
+                        const svoxb_render_options* opt, const float* fwd_out,
+                        const float* color_ref, float* grad_data_out, float* hessdiag_out,
+                        int zero_first, void* stream) {
+    if (!tree || !rays || !opt) return SVOXB_ERR_NULL;
+    if (rays->Q > 0 && (!rays->origins || !rays->dirs || !rays->vdirs)) return SVOXB_ERR_NULL;
+    return se_grad_march(tree, RayBatch{rays->origins, rays->dirs, rays->vdirs}, rays->Q, opt,
+                         fwd_out, color_ref, grad_data_out, hessdiag_out, zero_first,
+                         (cudaStream_t)stream);
+}
+
+int svoxb_se_grad_image_march(const svoxb_tree* tree, const svoxb_camera* cam,
+                              const svoxb_render_options* opt, const float* fwd_out,
+                              const float* color_ref, float* grad_data_out, float* hessdiag_out,
+                              int zero_first, void* stream) {
+    if (!tree || !cam || !opt || !cam->c2w) return SVOXB_ERR_NULL;
+    if (cam->width < 0 || cam->height < 0) return SVOXB_ERR_SHAPE;
+    return se_grad_march(tree, PixelRays{cam->c2w, cam->fx, cam->fy, cam->width, cam->height},
+                         (int64_t)cam->width * cam->height, opt, fwd_out, color_ref,
+                         grad_data_out, hessdiag_out, zero_first, (cudaStream_t)stream);
+}
+
+}  // extern "C"
+
 template <class Source>
 static int replay_begin_checked(const svoxb_tree* tree, const Source& src, int64_t Q,
                                 const svoxb_render_options* opt, const float* grad_output,

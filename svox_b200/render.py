@@ -276,7 +276,9 @@ class VolumeRenderer(nn.Module):
         The diagonal is the squared norm of the Jacobian's columns, as in the reference
         (with ``density_softplus`` plus the reference's own second-order term for the density).
         Octrees with three colour channels of 1, 4, 9, 16 or 25 basis functions (SH, SG or
-        ASG): the route through the item log.
+        ASG) take the route through the item log; every other layout with at most four
+        output channels (RGBA, N != 2, other basis sizes) is marched twice (the forward,
+        then gradient and diagonal together).
         """
         self._require_cuda(True)
         return self._se_grad(_rays_spec_from_rays(rays), colors, False)
@@ -294,12 +296,16 @@ class VolumeRenderer(nn.Module):
         # the reference's kernel knows no thresholds (svox/csrc/rt_kernel.cu:537, 590)
         opt.sigma_thresh = opt.stop_thresh = 0.0
         tree = self.tree._spec()
-        if not _C.log_eligible(tree, opt):
-            raise NotImplementedError(
-                "se_grad needs an octree (N = 2) with three colour channels of 1, 4, 9, 16 or 25 "
-                "basis functions")
         with torch.no_grad():
             colors = colors.to(device=self.tree.data.device, dtype=self.tree.data.dtype)
+            if not _C.log_eligible(tree, opt):
+                # any other layout (RGBA, N != 2, other basis sizes): the forward, then one
+                # more march for gradient and diagonal
+                out = (_C.volume_render_image if image else _C.volume_render)(tree, src, opt)
+                grad, hess = _C.se_grad_march(tree, src, opt, out,
+                                              colors.reshape(out.shape).contiguous(),
+                                              image=image)
+                return out, grad, hess
             for _ in range(4):      # a log that was too small is enlarged and the render redone
                 out, log = _C.volume_render_logged(tree, src, opt, image=image)
                 used = _C.log_chunks_used(log[0])

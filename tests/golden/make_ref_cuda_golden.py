@@ -68,7 +68,8 @@ def weights(out_dir):
 
 
 SE_GRAD_CASES = ["c1_rays", "shell_sh9_rays", "shell_sh16_image", "opt_comp_range",
-                 "opt_softplus_pad_bg", "sg9_rays", "asg4_rays"]
+                 "opt_softplus_pad_bg", "sg9_rays", "asg4_rays", "rgba_rays", "n3_rays",
+                 "sg5_rays", "asg7_image"]
 
 
 def se_grad(out_dir, names):

@@ -200,7 +200,7 @@ def test_weight_accumulation_against_reference_cuda_fixture(name):
 
 
 @pytest.mark.parametrize("name", ["c1_rays", "opt_comp_range", "shell_sh16_image", "sg9_rays",
-                                  "asg4_rays"])
+                                  "asg4_rays", "rgba_rays", "n3_rays"])
 def test_se_grad_against_reference_cuda_fixture(name):
     # Fixtures: the reference's se_grad / se_grad_persp (CUDA) on seeded colours
     # (tests/golden/make_ref_cuda_golden.py --se-grad).
