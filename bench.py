@@ -8,18 +8,20 @@
 -- volume_render forward + MSE + backward into data.grad -- on the sparse-shell
 SH-degree-2 scene with 2^20 rays per step.  Under torchrun (N > 1) every rank
 holds the whole tree and renders a contiguous slice of the SAME 2^20 rays
-(strong scaling); the step ends with the NCCL all-reduce of data.grad.  Three
-ways of placing that all-reduce are timed and labelled in the JSON line:
+(strong scaling); the step ends with the all-reduce of data.grad.  Four
+ways of doing that all-reduce are timed and labelled in the JSON line:
 
   allreduce_after_backward   one all-reduce of the whole gradient after the backward
   allreduce_inside_backward  the backward hands finished leaf ranges to NCCL while it
                              still computes the next ones
+  allreduce_multicast        the gradient lies in symmetric memory and the NVSwitch sums it
+                             (multimem.ld_reduce / multimem.st, svoxb_allreduce_multimem)
   allreduce_under_next_step  the all-reduce of step i runs beside the forward and backward
                              of step i+1 (two gradient buffers; legitimate here because
                              nothing consumes the gradient between steps)
 
-``value`` is the better of the first two (the gradient of a step is complete
-when the step ends); the third is reported beside it.  At N > 1 the reduced
+``value`` is the best of the first three (the gradient of a step is complete
+when the step ends); the last is reported beside it.  At N > 1 the reduced
 gradient is also compared, outside the timed region, with the single-GPU
 gradient of the same 2^20 rays, and every rank's colours with the single-GPU
 render.  The other workloads are the point query (2^24 points, 256^3 leaves,
@@ -78,6 +80,9 @@ def parse():
     p.add_argument("--extra-levels", type=int, default=3)
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--multicast", action="store_true",
+                   help="train, N > 1: also time the variant that sums the gradient in the "
+                        "switch (needs multicast memory on every GPU)")
     p.add_argument("--no-ref-cuda", action="store_true")
     p.add_argument("--no-weak", action="store_true")
     p.add_argument("--overlap-parts", type=int, default=-1,
@@ -416,9 +421,29 @@ def run_train(a):
                 state["works"][k].wait()
                 state["works"][k] = None
 
+    # the gradient in symmetric memory, summed by the switch (on request: it moves fewer bytes
+    # than the ring from 4 GPUs on, but measured no faster there).  Every rank has to succeed,
+    # or none uses it.
+    multicast = None
+    if world >= 2 and a.multicast:
+        try:
+            multicast = D.MulticastGradient(tree)
+        except Exception as e:                      # no multicast memory on this box
+            multicast = None
+            if rank == 0:
+                print(f"[bench] no multicast gradient: {e!r}"[:300], file=sys.stderr)
+        have = torch.tensor([int(multicast is not None)], device=dev)
+        dist.all_reduce(have, op=dist.ReduceOp.MIN)
+        if not have.item():
+            multicast = None
+
     def set_variant(name):
         D.overlap_grad_allreduce(a.overlap_parts if name == "allreduce_inside_backward" else 0,
                                  reserve_sms=a.overlap_reserve)
+        if name == "allreduce_multicast":
+            multicast.enable()
+        else:
+            D.MulticastGradient.disable()
 
     # byte model: exact per-ray visit / contribution counts of this rank's rays
     vis, cf, cb = csrc.march_stats(tree._spec(), svox_b200.render._rays_spec_from_rays(rays),
@@ -439,6 +464,8 @@ def run_train(a):
     variants = {}
     names = ["allreduce_after_backward"] if world == 1 else \
         ["allreduce_after_backward", "allreduce_inside_backward"]
+    if multicast is not None:
+        names.insert(0, "allreduce_multicast")
     records = []
     clocks = None
     for name in names:
@@ -605,7 +632,7 @@ def run_train(a):
         # prefix, ray pack, bin, scatter (one launch per part), and the five launches of the
         # marching fallback, which return at once unless the log overflowed
         "gpu_launches": (5 + 3 + (a.overlap_parts if best == "allreduce_inside_backward" else 1)
-                         + 5) * a.steps,
+                         + 5 + (1 if best == "allreduce_multicast" else 0)) * a.steps,
         "clocks": clocks,
     }
     if check is not None:

@@ -363,6 +363,20 @@ const char* svoxb_last_cuda_error(void);
  * takes effect at the next launch; returns the previous value; n < 0 only queries. */
 int svoxb_reserve_sms(int n);
 
+/* Multi-GPU: sum of the gradient over all GPUs, in place, through NVSwitch
+ * multicast memory (no counterpart in the reference, which is single-GPU).
+ * Every rank holds its n_floats values in a buffer that is bound, at the same
+ * offset on every GPU, into one multicast object; `multicast` is this
+ * process's address of that object's range (e.g. the multicast_ptr of a
+ * torch.distributed._symmetric_memory allocation).  Rank `rank` of `world`
+ * sums its 1/world slice inside the switch (multimem.ld_reduce) and writes
+ * the sums to all GPUs (multimem.st).  The kernel waits for nobody: the
+ * caller orders it between two barriers across the ranks on the same stream
+ * (all gradients complete before; all slices written after).  n_floats a
+ * multiple of 4, the address 16-byte aligned. */
+int svoxb_allreduce_multimem(float* multicast, int64_t n_floats, int rank, int world,
+                             void* stream);
+
 /* Library version, "major.minor.patch". */
 const char* svoxb_version(void);
 

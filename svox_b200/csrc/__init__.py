@@ -621,6 +621,15 @@ def se_grad_march(tree, rays_or_cam, opt, fwd_out, colors, image=False):
     return grad, hess
 
 
+def allreduce_multimem(multicast_ptr, n_floats, rank, world):
+    """Sum ``n_floats`` floats over the GPUs of a multicast object, in place, on the current
+    stream (see ``svoxb_allreduce_multimem``); the caller provides the barriers around it."""
+    st = library().svoxb_allreduce_multimem(C.c_void_p(int(multicast_ptr)), C.c_int64(n_floats),
+                                            C.c_int(rank), C.c_int(world), _stream())
+    if st:
+        _raise(st, "allreduce_multimem")
+
+
 def replay_part_ranges(M, K, n_parts):
     """Leaf-slot ranges [(begin, end)] of the ``n_parts`` parts of a replay backward for a tree
     of ``M`` nodes with ``K`` floats per record (whole bins; the same on every process)."""

@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 SRC = os.path.join(HERE, "svox_b200.cu")
 LIB = os.path.join(HERE, "libsvox_b200.so")
-DEPS = ["svox_b200.cu", "common.cuh", "arith.cuh", "host.cuh", "query.cuh", "render.cuh", "render_queue.cuh", "render_replay.cuh", "noalloc.cuh",
+DEPS = ["svox_b200.cu", "common.cuh", "arith.cuh", "host.cuh", "query.cuh", "render.cuh", "render_queue.cuh", "render_replay.cuh", "noalloc.cuh", "collective.cuh",
         os.path.join("..", "..", "include", "svox_b200.h")]
 
 

@@ -7,6 +7,7 @@
 #include "render.cuh"
 #include "render_queue.cuh"
 #include "render_replay.cuh"
+#include "collective.cuh"
 #include <new>
 
 namespace svoxb {
@@ -1098,6 +1099,24 @@ int svoxb_reserve_sms(int n) {
     const int before = g_reserved_sms;
     if (n >= 0) g_reserved_sms = n;
     return before;
+}
+
+int svoxb_allreduce_multimem(float* multicast, int64_t n_floats, int rank, int world,
+                             void* stream) {
+    if (!multicast) return SVOXB_ERR_NULL;
+    if (world < 1 || rank < 0 || rank >= world || n_floats < 0) return SVOXB_ERR_OPTION;
+    if ((uintptr_t)multicast % 16 != 0 || n_floats % 4 != 0) return SVOXB_ERR_SHAPE;
+    const int64_t words = n_floats / 4;
+    const int64_t first = words * rank / world, last = words * (rank + 1) / world;
+    if (last <= first) return SVOXB_OK;
+    int sms = sm_count() - g_reserved_sms;
+    if (sms < 1) sms = 1;
+    int64_t grid = (last - first + kReduceBlock - 1) / kReduceBlock;
+    if (grid > 2 * sms) grid = 2 * sms;
+    multimem_allreduce_kernel<<<(unsigned)grid, kReduceBlock, 0, (cudaStream_t)stream>>>(
+        multicast, first, last);
+    SVOXB_CUDA(cudaGetLastError());
+    return SVOXB_OK;
 }
 
 const char* svoxb_version(void) { return "0.3.0"; }

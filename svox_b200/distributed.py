@@ -12,7 +12,7 @@ import torch.distributed as dist
 from .render import Rays
 
 __all__ = ["shard_bounds", "shard_rays", "shard_rows", "allreduce_grad", "broadcast_tree",
-           "gather_rows", "overlap_grad_allreduce"]
+           "gather_rows", "overlap_grad_allreduce", "MulticastGradient"]
 
 
 def _rank_world(rank, world):
@@ -87,6 +87,58 @@ def overlap_grad_allreduce(n_parts=8, group=None, reserve_sms=16):
                          int(reserve_sms) if n_parts > 1 else 0)   # one part: nothing overlaps
 
 
+class MulticastGradient:
+    """``tree.data.grad`` kept in symmetric memory and summed across the GPUs of one NVSwitch
+    domain by the switch itself (``svoxb_allreduce_multimem``) instead of an NCCL ring.
+
+    While ``enabled``, the renderer's training step accumulates its gradient into this
+    buffer (a fresh view of it per step, which autograd adopts as ``data.grad`` without a
+    copy), and ``allreduce_grad(tree)`` sums it in place: a barrier across the ranks, the
+    kernel, a second barrier, all on the current stream; the host waits for nothing.
+    One gradient is alive at a time: drop ``data.grad`` (``zero_grad(set_to_none=True)``)
+    before the next step's forward.  Every rank must construct it, in the same order.
+    Raises ``RuntimeError`` where the GPUs offer no multicast memory.
+    """
+    active = None
+
+    def __init__(self, tree, group=None):
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.shape = tuple(tree.data.shape)
+        n = tree.data.numel()
+        self.n, self.padded = n, (n + 3) // 4 * 4
+        self.flat = symm.empty(self.padded, dtype=torch.float32, device=tree.data.device)
+        self.handle = symm.rendezvous(self.flat, self.group)
+        if not self.handle.multicast_ptr:
+            raise RuntimeError("these GPUs offer no multicast memory")
+        self.flat.zero_()
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+
+    def view(self, like=None):
+        return self.flat[:self.n].view(self.shape)
+
+    def enable(self):
+        from . import render
+        render.GRAD_BUFFER = self.view
+        MulticastGradient.active = self
+
+    @staticmethod
+    def disable():
+        from . import render
+        render.GRAD_BUFFER = None
+        MulticastGradient.active = None
+
+    def owns(self, t):
+        return t is not None and t.untyped_storage().data_ptr() == \
+            self.flat.untyped_storage().data_ptr()
+
+    def allreduce_(self):
+        from . import csrc
+        self.handle.barrier(channel=0)      # every rank's gradient is complete
+        csrc.allreduce_multimem(self.handle.multicast_ptr, self.padded, self.rank, self.world)
+        self.handle.barrier(channel=1)      # every rank's slice of sums has been written
+
+
 def allreduce_grad(tree, group=None, async_op=False):
     """Sum ``tree.data.grad`` over all ranks (the one collective of a training step).
 
@@ -106,6 +158,14 @@ def allreduce_grad(tree, group=None, async_op=False):
             "allreduce_grad: several backward passes were reduced inside the backward and "
             "accumulated into data.grad; call allreduce_grad after each backward, or switch "
             "overlap_grad_allreduce off when accumulating gradients")
+    mc = MulticastGradient.active
+    if mc is not None:
+        if tree.data.grad is None:
+            mc.flat.zero_()
+            tree.data.grad = mc.view()
+        if mc.owns(tree.data.grad):
+            mc.allreduce_()
+            return None
     if tree.data.grad is None:
         tree.data.grad = torch.zeros_like(tree.data)
     return dist.all_reduce(tree.data.grad, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
