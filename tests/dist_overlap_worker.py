@@ -1,5 +1,6 @@
-"""Worker of test_multi_gpu_overlap (one process per GPU under torchrun): the gradient
-summed range by range inside the backward equals the gradient summed by one all-reduce."""
+"""Worker of the multi-GPU tests (one process per GPU under torchrun): the gradient summed
+range by range inside the backward, and the gradient summed by the switch in symmetric memory,
+equal the gradient summed by one all-reduce."""
 import datetime
 import os
 import sys
@@ -40,8 +41,27 @@ def main():
     D.overlap_grad_allreduce(0)
     scale = plain.abs().max().item()
     err = (over - plain).abs().max().item() / scale
+    # the gradient in symmetric memory, summed by the switch (where the GPUs offer multicast
+    # memory; asked for with SVOXB_TEST_MULTICAST=1)
+    err_mc = 0.0
+    if os.environ.get("SVOXB_TEST_MULTICAST") == "1":
+        try:
+            mc = D.MulticastGradient(tree)
+        except Exception as e:                      # no multicast memory here
+            mc = None
+            print(f"rank {dist.get_rank()}: no multicast gradient ({e!r})"[:200], flush=True)
+        have = torch.tensor([int(mc is not None)], device=dev)
+        dist.all_reduce(have, op=dist.ReduceOp.MIN)
+        if have.item():
+            mc.enable()
+            summed = step()
+            assert mc.owns(tree.data.grad)
+            D.MulticastGradient.disable()
+            err_mc = (summed - plain).abs().max().item() / scale
+            if dist.get_rank() == 0:
+                print(f"multicast_vs_plain max_rel_err {err_mc:.3e}", flush=True)
     svox_b200.csrc.check_device_status()
-    ok = torch.tensor([1 if err < 1e-5 else 0], device=dev)
+    ok = torch.tensor([1 if max(err, err_mc) < 1e-5 else 0], device=dev)
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     if dist.get_rank() == 0:
         print(f"overlap_vs_plain max_rel_err {err:.3e} ok {int(ok.item())}", flush=True)

@@ -575,3 +575,23 @@ def test_multi_gpu_overlapped_allreduce_matches_plain(cuda_device):
                          capture_output=True, text=True, timeout=600, env=env)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     assert "ok 1" in res.stdout
+
+
+def test_multi_gpu_multicast_allreduce_matches_plain(cuda_device):
+    # Two ranks: data.grad kept in symmetric memory and summed through NVSwitch multicast
+    # (svoxb_allreduce_multimem) equals the one summed by NCCL.  No rank leaves early here,
+    # and NCCL's own use of multicast stays off.
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import subprocess
+    import sys
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", SVOXB_TEST_MULTICAST="1")
+    worker = os.path.join(os.path.dirname(__file__), "dist_overlap_worker.py")
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
+                          "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                          "--master-port", "29534", worker],
+                         capture_output=True, text=True, timeout=600, env=env)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    assert "ok 1" in res.stdout
+    if "no multicast gradient" not in res.stdout:
+        assert "multicast_vs_plain" in res.stdout
