@@ -56,14 +56,14 @@ METRICS = {
     "image5": "Mrays/s render_persp forward (SH deg 3, three shells at 1024^3, 1920x1080 views)",
 }
 # DRAM bytes (read + write) of one launch of the dominant kernel of the training step (the
-# logged forward march), from an ncu capture of a 2^17-ray launch (1.938 GB read + 0.353 GB
+# logged forward march), from an ncu capture of a 2^17-ray launch (1.450 GB read + 0.353 GB
 # written) scaled by 8 to the 2^20-ray launch: its traffic grows with the rays.  The backward's
 # does not (the gradient is read and written once whatever the number of rays), so it has no
 # scaled figure.  Printed only together with `traffic_source`, which names the capture.
-NCU_TRAFFIC = {"forward": 8 * (1.938027e9 + 0.352580e9), "backward": None}
+NCU_TRAFFIC = {"forward": 8 * (1.449616e9 + 0.352721e9), "backward": None}
 NCU_TRAFFIC_SOURCE = ("ncu --set full of render_queue_kernel<9,640,ForwardLogged> at 2^17 rays "
                       "x 8 (profiles/training_step_rays131072_ncu_full.md); valid for the "
-                      "kernel as of library version " + "0.2.0")
+                      "kernel as of library version " + "0.3.0")
 
 
 def parse():
