@@ -80,6 +80,8 @@ def parse():
     p.add_argument("--extra-levels", type=int, default=3)
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--no-other-workloads", action="store_true",
+                   help="train, N = 1: leave out the query / image workloads' digest")
     p.add_argument("--multicast", action="store_true",
                    help="train, N > 1: also time the variant that sums the gradient in the "
                         "switch (needs multicast memory on every GPU)")
@@ -653,11 +655,40 @@ def run_train(a):
     csrc.check_device_status()
     if check is not None and not check["ok"]:
         line["error"] = "multi-GPU gradient check failed"
+    if rank == 0 and world == 1 and not a.no_other_workloads:
+        # the other configurations of the benchmark, each in a process of its own on this GPU
+        del tree, rays, targets, renderer, state
+        torch.cuda.empty_cache()
+        line["other_workloads"] = other_workloads(a)
     if rank == 0:
         print(json.dumps(line), flush=True)
     H.done()
     if check is not None and not check["ok"]:
         sys.exit(1)
+
+
+def other_workloads(a):
+    """Point query and the two forward image renders at their full sizes, run as
+    ``bench.py --workload ...`` child processes; -> a digest of each one's JSON line."""
+    out = {}
+    for w in ("query", "image3", "image5"):
+        cmd = [sys.executable, os.path.abspath(__file__), "--workload", w, "--steps", "5",
+               "--warmup", "3", "--no-cpu-baseline"]
+        try:
+            res = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+            rows = [ln for ln in res.stdout.splitlines() if ln.startswith("{")]
+            d = json.loads(rows[-1])
+            keep = {k: d[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "warmup")}
+            keep["workload"] = d["config"]["workload"]
+            keep["roofline"] = {k: d["roofline"].get(k) for k in
+                                ("kernel", "achieved", "peak", "unit", "frac", "ms_per_launch")}
+            for extra in ("roofline_backward", "variants", "e2e"):
+                if extra in d:
+                    keep[extra] = d[extra]
+            out[w] = keep
+        except Exception as e:          # reported, and the headline line still goes out
+            out[w] = {"error": repr(e)[:300]}
+    return out
 
 
 # ---------------------------------------------------------------------------
