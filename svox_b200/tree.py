@@ -402,6 +402,108 @@ class N3Tree(nn.Module):
         self._invalidate()
         return True
 
+    # ------------------------------------------------------------------
+    # Copies and channel layout (svox/svox.py:286-430)
+    def partial(self, data_sel=None, data_format=None, dtype=None, device=None):
+        """Copy of the tree that keeps only the channels ``data_sel`` of every record (all by
+        default), e.g. ``tree.partial(-1)`` for the densities alone.  As in the reference the
+        copy carries THIS tree's ``data_format`` object; ``data_format`` only has to name a
+        format the new channel count is valid for (``"RGBA"`` accepts any)."""
+        device = self.data.device if device is None else device
+        dtype = self.data.dtype if dtype is None else dtype
+        channels = None
+        if data_sel is not None:
+            channels = torch.arange(self.data_dim)[data_sel].reshape(-1)
+        other = N3Tree(N=self.N,
+                       data_dim=self.data_dim if channels is None else channels.numel(),
+                       data_format=data_format or str(self.data_format),
+                       depth_limit=self.depth_limit, geom_resize_fact=self.geom_resize_fact,
+                       dtype=dtype, device=device)
+
+        def moved(x):
+            return x.detach().to(device=device, copy=True)
+
+        for name in ("invradius", "offset", "child", "parent_depth", "_n_internal", "_n_free"):
+            setattr(other, name, moved(getattr(self, name)))
+        other.extra_data = None if self.extra_data is None else moved(self.extra_data)
+        other.data_format = self.data_format
+        values = self.data.data if channels is None else \
+            self.data.data[..., channels.to(self.data.device)]
+        other.data = nn.Parameter(moved(values).to(dtype).contiguous())
+        other._invalidate()
+        return other
+
+    def clone(self, device=None):
+        """Deep copy, optionally onto another device."""
+        return self.partial(device=device)
+
+    def expand(self, data_format, data_dim=None, remap=None):
+        """Change the record layout to ``data_format`` (more or fewer basis functions per
+        colour channel).  ``remap`` lists, for the smaller of the two layouts, the channel of
+        the larger one that each of its channels corresponds to; by default colour channel c's
+        basis function i stays basis function i and the density stays last.  New channels are
+        zero.  Replaces the ``data`` parameter: optimizers have to be rebuilt."""
+        assert isinstance(data_format, str), "Please specify valid data format"
+        old_format, old_dim = self.data_format, self.data_dim
+        self.data_format = DataFormat(data_format)
+        self.data_dim = data_dim
+        self._maybe_auto_data_dim()
+        small, large = sorted((old_dim, self.data_dim))
+        if remap is None:
+            fmt_small, fmt_large = (old_format, self.data_format) if old_dim <= self.data_dim \
+                else (self.data_format, old_format)
+            if old_format is None or self.data_format.format == DataFormat.RGBA:
+                remap = torch.cat([torch.arange(small - 1), torch.tensor([large - 1])])
+            else:
+                assert self.data_format.basis_dim >= 1, \
+                    "Please manually specify data_dim for expand()"
+                n_small = max(fmt_small.basis_dim, 1)
+                n_large = max(fmt_large.basis_dim, 1)
+                fn = torch.arange(n_small)
+                remap = torch.cat([fn, n_large + fn, 2 * n_large + fn, torch.tensor([large - 1])])
+        remap = torch.as_tensor(remap, device=self.data.device)
+        old = self.data.data
+        new = torch.zeros((*old.shape[:-1], self.data_dim), dtype=old.dtype, device=old.device)
+        if self.data_dim < old_dim:
+            new[:] = old[..., remap]
+        else:
+            new[..., remap] = old
+        self.data = nn.Parameter(new)
+        self._invalidate()
+
+    def shrink(self, data_format, data_dim=None, remap=None):
+        """Alias of :meth:`expand`, which goes both ways."""
+        self.expand(data_format, data_dim, remap)
+
+    # In-place arithmetic on all leaves
+    def __iadd__(self, val):
+        self[:] += val
+        return self
+
+    def __isub__(self, val):
+        self[:] -= val
+        return self
+
+    def __imul__(self, val):
+        self[:] *= val
+        return self
+
+    def __itruediv__(self, val):
+        self[:] /= val
+        return self
+
+    __idiv__ = __itruediv__
+
+    def _make_val_tensor(self, val):
+        """``val`` as a ``(1 or B, data_dim)`` tensor on the tree's device."""
+        t = torch.as_tensor(val, dtype=self.data.dtype, device=self.data.device)
+        while t.dim() < 2:
+            t = t[None]
+        if t.shape[-1] == 1:
+            return t.expand(-1, self.data_dim).contiguous()
+        assert t.shape[-1] == self.data_dim
+        return t
+
     def shrink_to_fit(self):
         """Drop unused capacity and the nodes freed by ``merge``: the surviving nodes move up
         in order, links and parent slots are renumbered.  Re-creates the ``data`` parameter

@@ -18,8 +18,9 @@ reference's own ``N3Tree.save``:
 
 and, next to each, ``ref_py_frontier_<name>.npz``: the reference's frontier queries, the
 corners and side lengths of every leaf (its tensor-op ``_calc_corners``), a point assignment
-``tree.set(points, values, cuda=False)`` (the rows of ``data`` it changed), and the selection
-of a merge whose result is ``ref_py_saved_tree_<name>_merged.npz``.
+``tree.set(points, values, cuda=False)`` (the rows of ``data`` it changed), the first records of
+``tree.clone().expand(...)`` and ``tree.partial(-1)``, and the selection of a merge whose result
+is ``ref_py_saved_tree_<name>_merged.npz``.
 
 tests/test_tree_structure.py loads those files with svox_b200.N3Tree.load,
 rebuilds the same trees with svox_b200 from the same recipe (RECIPES below)
@@ -70,6 +71,10 @@ RECIPES = {
                          center=[0.0, 0.5, -1.0]),
                refines=[(0.0, 0.30, 1)], seed=202),
 }
+
+
+# the layout each recipe tree is expanded to for the `expand_*` entries of the frontier fixture
+EXPANDED = {"octree": "SH9", "n3": "SH1"}
 
 
 def build_recipe(lib, recipe):
@@ -139,6 +144,13 @@ def structure(ref):
         rows = (after != before.reshape(-1, tree.data_dim)).any(dim=1).nonzero()[:, 0]
         blob["set_rows"], blob["set_rows_data"] = rows.numpy(), after[rows].numpy().copy()
         tree.data.data.copy_(before)
+        # a copy with another record layout (clone + expand), and the densities alone (partial)
+        wider = tree.clone()
+        wider.expand(EXPANDED[name])
+        blob["expand_rows"] = wider.data.data.reshape(-1, wider.data_dim)[:64].numpy().copy()
+        blob["expand_sum"] = wider.data.data.double().sum().numpy()
+        blob["partial_rows"] = tree.partial(-1, data_format="RGBA").data.data.reshape(-1)[:64] \
+            .numpy().copy()
         blob["pick"] = coarsen(tree).numpy()
         tree.check_integrity()
         np.savez_compressed(os.path.join(HERE, f"ref_py_frontier_{name}.npz"), **blob)

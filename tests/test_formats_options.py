@@ -101,3 +101,31 @@ def test_spec_validation_rejects_cpu_tensors():
     tree = svox.N3Tree(data_format="SH1")
     with pytest.raises(RuntimeError, match="CUDA tensor"):
         csrc.query_vertical(tree._spec(), torch.rand(4, 3))
+
+
+def test_host_side_sh_basis_matches_the_oracle():
+    # svox_b200.sh (the counterpart of svox/sh.py) against the oracle's restatement of the
+    # kernel-side basis (svox/csrc/rt_kernel.cu:141-181): same polynomials, same order, float
+    # round-off apart (the oracle follows the device code's fused multiply-adds).
+    import ctypes as C
+    import numpy as np
+    import torch
+    from oracle import oracle as orc
+    from svox_b200 import sh
+    gen = torch.Generator().manual_seed(7)
+    dirs = torch.randn(257, 3, generator=gen)
+    dirs = dirs / dirs.norm(dim=-1, keepdim=True)
+    lib = orc.lib()
+    for deg in range(5):
+        n = (deg + 1) ** 2
+        mine = sh.eval_sh_bases(deg, dirs).numpy()
+        assert mine.shape == (257, n)
+        want = np.empty((257, n), np.float32)
+        for i in range(257):
+            d = np.ascontiguousarray(dirs[i].numpy(), dtype=np.float32)
+            lib.orc_sh_basis(C.c_int(n), d.ctypes.data_as(C.c_void_p),
+                             want[i].ctypes.data_as(C.c_void_p))
+        assert np.abs(mine - want).max() <= 2e-6
+        coef = torch.randn(257, 3, n, generator=gen)
+        assert torch.allclose(sh.eval_sh(deg, coef, dirs),
+                              (coef * torch.from_numpy(mine)[:, None, :]).sum(-1))

@@ -251,3 +251,33 @@ def test_leaf_geometry_and_assignment_oracle_like_the_reference(name):
     assert np.array_equal(data, want)
     with pytest.raises(RuntimeError):
         tree.set(torch.from_numpy(f["set_points"]), torch.from_numpy(f["set_values"]))
+
+
+@pytest.mark.parametrize("name", ["octree", "n3"])
+def test_clone_expand_partial_like_the_reference(name):
+    # clone / expand / shrink / partial (svox/svox.py:286-430) on the recipe trees against what
+    # the reference's own methods produced, plus the round trip and the in-place operators.
+    gen = _recipes()
+    here = os.path.dirname(os.path.abspath(__file__))
+    f = np.load(os.path.join(here, "golden", f"ref_py_frontier_{name}.npz"))
+    tree = gen.build_recipe(svox, gen.RECIPES[name])
+    before = tree.data.detach().clone()
+    wider = tree.clone()
+    wider.expand(gen.EXPANDED[name])
+    assert torch.equal(tree.data.detach(), before)              # the clone owns its data
+    rows = wider.data.detach().reshape(-1, wider.data_dim)
+    assert np.array_equal(rows[:64].numpy(), f["expand_rows"])
+    assert float(rows.double().sum()) == float(f["expand_sum"])
+    assert repr(wider.data_format) == gen.EXPANDED[name]
+    wider.shrink(repr(tree.data_format), data_dim=tree.data_dim)
+    assert torch.equal(wider.data.detach(), before)             # expand, then shrink: unchanged
+    sigma = tree.partial(-1, data_format="RGBA")
+    assert sigma.data_dim == 1 and torch.equal(sigma.child, tree.child)
+    assert np.array_equal(sigma.data.detach().reshape(-1)[:64].numpy(), f["partial_rows"])
+    assert torch.equal(sigma.data.detach()[..., 0], before[..., -1])
+    leaves = tree[:].values.detach().clone()
+    tree += 1.5
+    tree *= 2.0
+    tree -= 0.25
+    tree /= 4.0
+    assert torch.allclose(tree[:].values.detach(), ((leaves + 1.5) * 2.0 - 0.25) / 4.0)
