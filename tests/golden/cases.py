@@ -332,6 +332,14 @@ def c3_full_image():
     return _full_view(W.config3, 800, 800, 1111.0, attrs=dict(stop_thresh=1e-2))
 
 
+def c3_full_image_grad():
+    """The same 800x800 view without thresholds and with a seeded N(0,1) upstream gradient:
+    the image backward (logged forward + replay backward over pixel rays) at full size."""
+    case = _full_view(W.config3, 800, 800, 1111.0)
+    case["grad_out"] = torch.randn(800, 800, 3, generator=_g(122))
+    return case
+
+
 def c5_full_image():
     """First view of the large multi-view benchmark: three shells refined to 1024^3, SH16
     (12 GB of data, element offsets beyond 2^31), 1920x1080, step 5e-4, fast=True."""
@@ -342,7 +350,7 @@ def c5_full_image():
 # strided sample of the outputs: the colours of every FULL_OUT_STRIDE-th ray, every
 # FULL_PIXEL_STRIDE-th pixel (row-major), the leaf ids of every FULL_ID_STRIDE-th point.
 FULL_CASES = {f.__name__: f for f in [c4_full_rays, c2_full_query, c3_full_image,
-                                      c5_full_image]}
+                                      c5_full_image, c3_full_image_grad]}
 FULL_OUT_STRIDE = 16
 FULL_PIXEL_STRIDE = 97
 FULL_ID_STRIDE = 4096

@@ -137,3 +137,27 @@ def test_image_full_size(name, cuda_device):
         assert (np.abs(want - 1.0).max(axis=1) > 1e-3).mean() > 0.02   # the sample sees the scene
     finally:
         case["tree"].to("cpu")
+
+
+def test_image_backward_full_size(cuda_device):
+    # The 800x800 view of the 512^3 shell tree (SH16, K = 49) with gradients: logged forward and
+    # replay backward over pixel rays at full size, against the reference's
+    # volume_render_image[_backward] and the oracle.
+    case = FULL_CASES["c3_full_image_grad"]()
+    z = _gold("c3_full_image_grad")
+    assert z is not None
+    mine = P.run_product(case, cuda_device)
+    flat = mine["out"].reshape(-1, 3)
+    assert np.abs(flat[::FULL_PIXEL_STRIDE] - z["out"]).max() <= RGB_TOL
+    orc = P.run_oracle(case)
+    assert np.abs(mine["out"] - orc["out"]).max() <= RGB_TOL
+    idx = z["grad_idx"]
+    scale = orc["grad_abs"].reshape(-1)[idx]
+    P.assert_grad_matches_reference(mine["grad"].reshape(-1)[idx], z["grad_val"], scale,
+                                    "image backward")
+    assert P.grad_excess(mine["grad"], orc["grad"], orc["grad_abs"], 1e-3) <= 1.0
+    total = float(z["grad_abs_sum"])
+    assert abs(np.abs(mine["grad"]).sum() - total) <= 1e-5 * total
+    march = P.run_product(case, cuda_device, item_log=False)
+    P.assert_grad_matches_reference(march["grad"].reshape(-1)[idx], z["grad_val"], scale,
+                                    "marching image backward")
