@@ -12,7 +12,7 @@ extern "C" {
 #endif
 
 /* key 5: MB of gradient that one leaf-range bin of the replay backward spans
- *        (1..1024, default 16);
+ *        (1..1024, default 32);
  * key 7: bricks below the render leaf table (1 = on, the default; 0 = off).
  * Process-wide; an index built by svoxb_render_scratch_build is invalid after
  * key 7 changes.  Unknown keys return SVOXB_ERR_OPTION. */

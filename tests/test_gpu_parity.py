@@ -117,7 +117,7 @@ def test_bricks_and_bin_size_do_not_change_results(name, cuda_device):
         P.assert_grad_matches_reference(base["grad"], fine["grad"], orc["grad_abs"])
     finally:
         lib.svoxb_test_knob(7, 1)
-        lib.svoxb_test_knob(5, 16)
+        lib.svoxb_test_knob(5, 32)
 
 
 @pytest.mark.parametrize("name", ["c1_rays", "shell_sh9_rays", "shell_sh16_image", "opt_fast",
