@@ -310,7 +310,9 @@ static int replay_scatter_bd(const ReplayJob& job, int part, float* grad, int re
         if (reserve_sms > 0)
             return replay_scatter_block<BD, 1024, false>(job, part, grad, reserve_sms, stream);
     }
-    return replay_scatter_block<BD, 512, false>(job, part, grad, reserve_sms, stream);
+    // 256-thread blocks: measured 2.83 ms of backward per training step against 2.94 with 512
+    // (more, smaller blocks keep the window of packets in flight narrower)
+    return replay_scatter_block<BD, 256, false>(job, part, grad, reserve_sms, stream);
 }
 
 static int replay_scatter(const ReplayJob& job, int part, float* grad, int reserve_sms,
