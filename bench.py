@@ -147,6 +147,15 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
+    def ensure(self, step, n=2, limit_s=3.0):
+        """Short timed regions can end before nvidia-smi delivers its first sample: keep the
+        GPU under the same load (extra, untimed steps) until ``n`` samples have arrived."""
+        t0 = time.perf_counter()
+        while self.proc is not None and len(self.rows) < n and \
+                time.perf_counter() - t0 < limit_s:
+            step()
+            torch.cuda.synchronize()
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -470,6 +479,8 @@ def run_train(a):
         names.insert(0, "allreduce_multicast")
     records = []
     clocks = None
+    if rank == 0:
+        H.sampler.start()        # sampled through the warm-up and timed steps of every variant
     for name in names:
         set_variant(name)
         for _ in range(warm):
@@ -477,13 +488,13 @@ def run_train(a):
         last = name == names[-1]
         if last:
             csrc.set_timing(records)
-            if rank == 0:
-                H.sampler.start()
         ms = H.timed(step, a.steps)
         if last:
-            clocks = H.sampler.stop() if rank == 0 else None
             csrc.set_timing(None)
         variants[name] = {"ms_per_step": ms, "value": Q / ms / 1e3}
+    if world == 1:
+        H.sampler.ensure(step)   # (single process only: extra steps on one rank of several
+    clocks = H.sampler.stop() if rank == 0 else None     #  would leave its collectives alone)
     torch.cuda.synchronize()
     per_call = {}
     for name, ea, eb in records:
@@ -721,13 +732,17 @@ def run_query(a):
         return vals
 
     warm = max(a.warmup, 3)
+    if rank == 0:
+        H.sampler.start()        # sampled through the warm-up and the timed steps
     for _ in range(warm):
         step()
     del rec[:]
-    if rank == 0:
-        H.sampler.start()
     ms_step = H.timed(step, a.steps)
+    n_timed = len(rec)
+    if rank == 0:
+        H.sampler.ensure(step)
     clocks = H.sampler.stop() if rank == 0 else None
+    del rec[n_timed:]
     torch.cuda.synchronize()
     ms_fwd = float(np.mean([e[0].elapsed_time(e[1]) for e in rec]))
     ms_bwd = float(np.mean([e[1].elapsed_time(e[2]) for e in rec]))
@@ -828,16 +843,17 @@ def run_image(a):
     per_view = w * h * 12 + 8 * vis.sum().item() + 4 * (K - 1) * cf.sum().item()
     del pr
     out = {}
+    if rank == 0:
+        H.sampler.start()        # sampled through the warm-up and timed steps of both variants
     for name, fn in (("plain", step), ("frozen_tree", step_frozen)):
         for _ in range(warm):
             fn()
-        if name == "plain" and rank == 0:
-            H.sampler.start()
         ms = H.timed(fn, a.steps)
-        if name == "plain":
-            clocks = H.sampler.stop() if rank == 0 else None
         out[name] = {"ms_per_step": ms, "value": n_px / ms / 1e3,
                      "ms_per_view": ms / max(hi - lo, 1)}
+    if rank == 0:
+        H.sampler.ensure(step)
+    clocks = H.sampler.stop() if rank == 0 else None
     ms_step = out["plain"]["ms_per_step"]
     e2e = None
     if not a.no_e2e:

@@ -265,8 +265,42 @@ def query_vertical(tree, indices):
     return values, node_ids
 
 
-def query_vertical_backward(tree, indices, grad_output):
-    """-> gradient w.r.t. data, (M, N, N, N, Kg); svox_kernel.cu:160-182."""
+_side_streams = {}
+
+
+def zero_beside(buf):
+    """Clear ``buf`` on a side stream of its device, after the work already queued on the
+    current stream (the memory's previous users); -> the event after which it is zero.  The
+    fill then runs beside whatever the current stream does next."""
+    dev = buf.device
+    side = _side_streams.get(dev)
+    if side is None:
+        side = _side_streams[dev] = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        buf.zero_()
+        done = torch.cuda.Event()
+        done.record(side)
+    # should the tensor be dropped before anyone waited for the fill: its memory must not be
+    # handed out again while the side stream still writes to it
+    if buf.untyped_storage().size() and not _is_symmetric(buf):
+        buf.record_stream(side)
+    return done
+
+
+def _is_symmetric(buf):
+    """Symmetric-memory allocations do not come from the caching allocator."""
+    try:
+        from ..distributed import MulticastGradient
+    except ImportError:         # torch.distributed not built
+        return False
+    mc = MulticastGradient.active
+    return mc is not None and mc.owns(buf)
+
+
+def query_vertical_backward(tree, indices, grad_output, zeroed=None):
+    """-> gradient w.r.t. data, (M, N, N, N, Kg); svox_kernel.cu:160-182.  ``zeroed``: a zero
+    tensor of that shape to add the rows into (else one is made and cleared here)."""
     lib = library()
     ct = _pack_tree(tree)
     _check_indices(indices)
@@ -276,12 +310,17 @@ def query_vertical_backward(tree, indices, grad_output):
         raise RuntimeError("grad_output must be (Q, K)")
     Kg = grad_output.shape[1]
     with torch.cuda.device(indices.device):
-        grad = torch.empty((ct.M, ct.N, ct.N, ct.N, Kg), dtype=grad_output.dtype,
-                           device=grad_output.device)
+        shape = (ct.M, ct.N, ct.N, ct.N, Kg)
+        if zeroed is not None:
+            _check_input(zeroed, "zeroed")
+            if tuple(zeroed.shape) != shape:
+                raise RuntimeError("zeroed must be (M, N, N, N, Kg)")
+        grad = zeroed if zeroed is not None else \
+            torch.empty(shape, dtype=grad_output.dtype, device=grad_output.device)
         st = lib.svoxb_query_vertical_backward(
             C.byref(ct), C.c_void_p(indices.data_ptr()), C.c_int64(Q),
             C.c_void_p(grad_output.data_ptr()), C.c_int32(Kg), C.c_void_p(grad.data_ptr()),
-            C.c_int(1), _stream())
+            C.c_int(0 if zeroed is not None else 1), _stream())
     if st:
         _raise(st, "query_vertical_backward")
     return grad

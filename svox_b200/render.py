@@ -31,9 +31,6 @@ FORCE_TWO_MARCHES = False
 GRAD_PARTS = None
 
 
-_side_streams = {}
-
-
 # Where the training step's gradient is accumulated: None = a fresh tensor per step; else a
 # callable ``like -> tensor`` of that shape (svox_b200.distributed.MulticastGradient hands out
 # views of its symmetric-memory buffer, so that the gradient can be summed across GPUs where
@@ -44,18 +41,9 @@ GRAD_BUFFER = None
 def _zeroed_beside(like):
     """A zero tensor shaped like ``like`` whose fill runs on a side stream; -> (tensor, event
     after which it is zero)."""
-    dev = like.device
-    side = _side_streams.get(dev)
-    if side is None:
-        side = _side_streams[dev] = torch.cuda.Stream(device=dev)
     buf = GRAD_BUFFER(like) if GRAD_BUFFER is not None else \
         torch.empty_like(like, memory_format=torch.contiguous_format)
-    side.wait_stream(torch.cuda.current_stream(dev))     # the memory's previous users are done
-    with torch.cuda.stream(side):
-        buf.zero_()
-        done = torch.cuda.Event()
-        done.record(side)
-    return buf, done
+    return buf, _C.zero_beside(buf)
 
 
 def _claim(ctx):
