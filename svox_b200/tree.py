@@ -36,12 +36,6 @@ class _QueryVerticalFunction(autograd.Function):
 
     @staticmethod
     def forward(ctx, data, tree_spec, indices):
-        ctx.grad_buffer = None
-        if data.requires_grad and torch.is_grad_enabled():
-            # the gradient is as large as ``data``: its zero-fill runs on a second stream
-            # beside the query instead of in front of the backward
-            buf = torch.empty_like(data, memory_format=torch.contiguous_format)
-            ctx.grad_buffer = (buf, _C.zero_beside(buf))
         out, node_ids = _C.query_vertical(tree_spec, indices)
         ctx.mark_non_differentiable(node_ids)
         ctx.tree_spec = tree_spec
@@ -50,17 +44,12 @@ class _QueryVerticalFunction(autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_out, dummy):
-        if not ctx.needs_input_grad[0]:
-            return None, None, None
-        zeroed = None
-        if ctx.grad_buffer is not None:
-            buf, done = ctx.grad_buffer
-            ctx.grad_buffer = None
-            if buf.shape[-1] == grad_out.shape[-1]:
-                torch.cuda.current_stream(buf.device).wait_event(done)
-                zeroed = buf
-        return _C.query_vertical_backward(ctx.tree_spec, ctx.saved_tensors[0],
-                                          grad_out.contiguous(), zeroed=zeroed), None, None
+        # (clearing the gradient buffer on a second stream beside the forward query, as the
+        # renderer does, was measured: no gain, both are bound by DRAM)
+        if ctx.needs_input_grad[0]:
+            return _C.query_vertical_backward(ctx.tree_spec, ctx.saved_tensors[0],
+                                              grad_out.contiguous()), None, None
+        return None, None, None
 
 
 class N3Tree(nn.Module):
