@@ -58,9 +58,12 @@ METRICS = {
 # DRAM bytes (read + write) of one launch of the dominant kernel of the training step (the
 # logged forward march), from an ncu capture of a 2^17-ray launch (1.450 GB read + 0.353 GB
 # written) scaled by 8 to the 2^20-ray launch: its traffic grows with the rays.  The backward's
-# does not (the gradient is read and written once whatever the number of rays), so it has no
-# scaled figure.  Printed only together with `traffic_source`, which names the capture.
-NCU_TRAFFIC = {"forward": 8 * (1.449616e9 + 0.352721e9), "backward": None}
+# does not (the gradient is read and written once whatever the number of rays), so its figure
+# comes from a one-pass capture (DRAM bytes and duration only) of the two replay kernels at
+# full size: bin pass 3.583 GB read + 2.227 GB written, scatter 3.167 GB + 0.900 GB.
+# Printed only together with `traffic_source`, which names the capture.
+NCU_TRAFFIC = {"forward": 8 * (1.449616e9 + 0.352721e9),
+               "backward": 3.583350e9 + 2.226789e9 + 3.167486e9 + 0.900214e9}
 NCU_TRAFFIC_SOURCE = ("ncu --set full of render_queue_kernel<9,640,ForwardLogged> at 2^17 rays "
                       "x 8 (profiles/training_step_rays131072_ncu_full.md); valid for the "
                       "kernel as of library version " + "0.3.0")
@@ -635,7 +638,7 @@ def run_train(a):
                               "bytes_of_this_design_per_launch": replay_bytes / world,
                               "model_frac": bwd_bytes / world / ms_bwd / 1e6 / peak,
                               "algorithmic_bytes_per_launch": bwd_bytes / world,
-                              "traffic": None,
+                              "traffic": NCU_TRAFFIC["backward"] if traffic_ok else None,
                               "ms_per_launch": ms_bwd},
         "roofline_step": {"algorithmic_bytes": fwd_bytes + bwd_bytes,
                           "achieved": (fwd_bytes + bwd_bytes) / ms_step / 1e6,
