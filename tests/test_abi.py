@@ -79,6 +79,12 @@ def test_argument_errors_without_gpu(lib):
     opt.format = 7
     o = opt._pack()
     assert lib.svoxb_volume_render(C.byref(lobes), C.byref(rays), C.byref(o), None, None) == 3
+    # the no-allocation entry point is for SH colour only: a lobe basis is refused before
+    # anything is launched
+    opt.format, opt.basis_dim, opt.max_comp = csrc.FORMAT_SG, 1, 0
+    o = opt._pack()
+    assert lib.svoxb_volume_render_noalloc(C.byref(lobes), C.byref(rays), C.byref(o), None,
+                                           None) == 3
     opt.format, opt.basis_dim, opt.max_comp = csrc.FORMAT_SH, 2, 1   # not a square
     o = opt._pack()
     assert lib.svoxb_volume_render(C.byref(ok), C.byref(rays), C.byref(o), None, None) == 3
